@@ -1,0 +1,427 @@
+"""Benchmark of the brute.bit1 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--gemm-impl auto|popc|b1|i8]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload: the large square binary GEMM, M = N = K = 16384 bit1 operands
+(uint64-packed, uniform random bits from a seeded generator), int32 output
+C = K - 2*popcount(a ^ b). One step = one pass of the GEMM. With N GPUs the rows
+of B (output features) are split into N equal blocks, one per rank, with no
+data-path collective (total work fixed: strong scaling). One JSON line is printed
+by rank 0. Besides the contract keys it carries `roofline`, `cpu_baseline`,
+`e2e`, `clocks`, `gpu_launches`, and an `extra` object with the bandwidth ops
+(pack / unpack / popcount / bitwise GB/s), the binarised MLP and binary attention.
+
+`--impl reference` times the CPU implementation of the same GEMM (the C
+restatement of the reference's Highway path in oracle/, all host threads) on a
+bounded sample of the workload; the reference's own extension cannot be built
+offline (its Highway submodule is empty).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M = N = K = 16384
+METRIC = "binary_gemm_tops"
+UNIT = "TOPS (1 bit-MAC = 1 op)"
+WORKLOAD = "xnor-popcount GEMM M=N=K=16384 bit1, uint64-packed, int32 out (BASELINE config 3)"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gemm-impl", default="auto", choices=["auto", "popc", "b1", "i8"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--size", type=int, default=16384, help="M=N=K (profiling runs use smaller sizes)")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm (oracle port of the reference's CPU path)
+# ---------------------------------------------------------------------------
+def cpu_gemm_sample(size: int, target_s: float = 10.0):
+    """Time the CPU GEMM on rows [0:r) x [0:r) of the workload, full K."""
+    import numpy as np
+    from oracle import c_oracle as co
+    co.build()
+    rng = np.random.default_rng(1234)
+    kp = size // 64
+    probe = min(1024, size)
+    A = rng.integers(-2 ** 63, 2 ** 63 - 1, size=(probe, kp), dtype=np.int64)
+    B = rng.integers(-2 ** 63, 2 ** 63 - 1, size=(probe, kp), dtype=np.int64)
+    co.xnor_gemm(A[:64], B[:64], size)                      # warm the thread pool
+    t0 = time.perf_counter()
+    co.xnor_gemm(A, B, size)
+    t_probe = max(time.perf_counter() - t0, 1e-6)
+    rate = probe * probe * size / t_probe
+    rows = int(min(size, max(probe, (target_s * rate / size) ** 0.5)))
+    rows = max(256, rows // 256 * 256)
+    return co, rng, rows, kp
+
+
+def run_reference_arm(args):
+    import numpy as np
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    size = args.size
+    # each step is a bounded sample sized so that steps + warmup end within a few minutes
+    total_calls = max(1, args.steps + args.warmup)
+    co, rng, rows, kp = cpu_gemm_sample(size, target_s=min(10.0, 120.0 / total_calls))
+    A = rng.integers(-2 ** 63, 2 ** 63 - 1, size=(rows, kp), dtype=np.int64)
+    B = rng.integers(-2 ** 63, 2 ** 63 - 1, size=(rows, kp), dtype=np.int64)
+    for _ in range(args.warmup):
+        co.xnor_gemm(A, B, size)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        co.xnor_gemm(A, B, size)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    tops = rows * rows * size / dt / 1e12
+    sample = f"rows [0:{rows}) of A against rows [0:{rows}) of B, full K={size} ({rows}x{rows}x{size} bit-MACs per step)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": {"workload": WORKLOAD if size == 16384 else f"xnor-popcount GEMM M=N=K={size}", "sample": sample},
+        "cpu_baseline": {"value": tops, "unit": UNIT, "cores": co.num_threads(), "kind": "port", "sample": sample,
+                         "host_cpus": os.cpu_count(), "vpopcntdq": co.has_vpopcntdq()},
+        "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """Reads (never sets) SM clocks and throttle reasons of one GPU through NVML."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = int(get(self.h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(timeout=2)
+        med = int(statistics.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def time_steps(fn, steps, warmup, flush, stream_sync):
+    """Per-step CUDA events on the launching stream, L2 flushed between steps
+    (outside the timed spans). Returns the list of step times in ms."""
+    import torch
+    for _ in range(warmup):
+        flush()
+        fn()
+    stream_sync()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s, e in evs:
+        flush()
+        s.record()
+        fn()
+        e.record()
+    stream_sync()
+    return [s.elapsed_time(e) for s, e in evs]
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import brute_b200  # noqa: F401  (fails loudly if the CUDA library is missing)
+    from brute_b200 import _lib as L
+    from brute_b200.kernels import shard_bounds
+    ops = torch.ops.brute
+    impl = {"auto": L.GEMM_AUTO, "popc": L.GEMM_POPC, "b1": L.GEMM_MMA_B1, "i8": L.GEMM_TCGEN05}[args.gemm_impl]
+    size = args.size
+    m = n = k = size
+    kp = k // 64
+    peaks = measured_peaks()
+
+    # identical operands on every rank from the seed; each rank keeps its block of B's rows
+    g = torch.Generator(device=dev).manual_seed(1234)
+    A = torch.randint(-2 ** 63, 2 ** 63 - 1, (m, kp), generator=g, dtype=torch.int64, device=dev)
+    Bfull = torch.randint(-2 ** 63, 2 ** 63 - 1, (n, kp), generator=g, dtype=torch.int64, device=dev)
+    lo, hi = shard_bounds(n, world, rank)
+    B = Bfull[lo:hi].contiguous()
+    del Bfull
+    n_loc = hi - lo
+
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # 2x the 126 MB L2
+
+    def flush():
+        flush_buf.zero_()
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    holder = {}
+
+    def step():
+        holder["C"] = ops.xnor_popcount_matmul_impl(A, B, k, impl)
+
+    sampler = ClockSampler(local_rank)
+    sync()
+    sampler.start()
+    times = time_steps(step, args.steps, args.warmup, flush, sync)
+    clocks = sampler.stop()
+    status = L.load().brute_b200_device_status()
+    if status != 0:
+        raise SystemExit(f"GEMM kernel reported status {status}: {L.strerror(status)}")
+    total_ms = sum(times)
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    macs_all = float(m) * n * k
+    value = macs_all / (ms_per_step * 1e-3) / 1e12
+
+    # roofline of the dominant kernel (this rank's launch)
+    my_ms = sum(times) / args.steps
+    my_macs = float(m) * n_loc * k
+    if args.gemm_impl in ("auto", "i8"):
+        # tcgen05 kind::i8: 2 int8 ops per bit-MAC; int8 dense runs at twice the bf16 rate on B200
+        achieved = 2 * my_macs / (my_ms * 1e-3) / 1e12
+        peak = 2 * peaks["bf16_tflops"]
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s (int8, 2 per bit-MAC)",
+                "frac": achieved / peak, "traffic": None,
+                "peak_source": f"2 x bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json",
+                "algorithmic_bytes_per_launch": 8 * kp * (m + n_loc) + 4 * m * n_loc}
+    else:
+        alg = 8 * kp * (m + n_loc) + 4 * m * n_loc
+        achieved = alg / (my_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                "note": "CUDA-core / mma.sync paths are instruction bound; HBM figure shown for reference"}
+
+    # ---- end to end through the public op with HOST buffers (pinned), every step:
+    #      H2D of both operands, the op, D2H of the int32 result
+    e2e = None
+    if rank == 0 or world > 1:
+        hA = A.cpu().pin_memory()
+        hB = B.cpu().pin_memory()
+        hC = torch.empty((m, n_loc), dtype=torch.int32).pin_memory()
+        dA = torch.empty_like(A)
+        dB = torch.empty_like(B)
+
+        def e2e_step():
+            dA.copy_(hA, non_blocking=True)
+            dB.copy_(hB, non_blocking=True)
+            c = ops.xnor_popcount_matmul_impl(dA, dB, k, impl)
+            hC.copy_(c, non_blocking=True)
+
+        e_steps = max(3, min(args.steps, 5))
+        e_times = time_steps(e2e_step, e_steps, 1, flush, sync)
+        te = torch.tensor([sum(e_times)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e_ms = float(te.item()) / e_steps
+        e2e = {"value": macs_all / (e_ms * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": int(hA.numel() * 8 + hB.numel() * 8),
+               "d2h_bytes_per_step": int(hC.numel() * 4), "ms_per_step": e_ms, "steps": e_steps}
+        # the copied-back result is the device result
+        assert torch.equal(hC[:8], holder["C"][:8].cpu())
+
+    extra = {}
+    if world > 1:
+        # optional all-gather of the C blocks (NCCL), timed apart from the GEMM
+        c_loc = holder["C"]
+        gathered = torch.empty((world, m, n_loc), dtype=torch.int32, device=dev)
+        g_times = time_steps(lambda: dist.all_gather_into_tensor(gathered, c_loc), 3, 1, lambda: None, sync)
+        tg = torch.tensor([sum(g_times) / 3], dtype=torch.float64, device=dev)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        extra["all_gather_C_ms"] = float(tg.item())
+        extra["tops_with_gather"] = macs_all / ((ms_per_step + float(tg.item())) * 1e-3) / 1e12
+        del gathered
+
+    if rank == 0 and not args.no_extra and size == 16384:
+        extra.update(secondary_workloads(dev, peaks, flush, sync))
+
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import numpy as np
+        co, rng, rows, _ = cpu_gemm_sample(size, target_s=10.0)
+        a_np = rng.integers(-2 ** 63, 2 ** 63 - 1, size=(rows, kp), dtype=np.int64)
+        b_np = rng.integers(-2 ** 63, 2 ** 63 - 1, size=(rows, kp), dtype=np.int64)
+        t0 = time.perf_counter()
+        c_np = co.xnor_gemm(a_np, b_np, k)
+        dt = time.perf_counter() - t0
+        # the same sample on the GPU must give the same integers
+        c_gpu = ops.xnor_popcount_matmul_impl(torch.from_numpy(a_np).to(dev), torch.from_numpy(b_np).to(dev), k, impl)
+        assert np.array_equal(c_gpu.cpu().numpy(), c_np), "GPU result differs from the CPU baseline's"
+        cpu_base = {"value": rows * rows * k / dt / 1e12, "unit": UNIT, "cores": co.num_threads(), "kind": "port",
+                    "sample": f"{rows}x{rows} outputs, full K={k}, {dt:.2f} s", "host_cpus": os.cpu_count(),
+                    "vpopcntdq": co.has_vpopcntdq()}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": {"workload": WORKLOAD if size == 16384 else f"xnor-popcount GEMM M=N=K={size}",
+                       "sharding": f"B rows (output features) split in {world} block(s), A replicated, no collective",
+                       "gemm_impl": args.gemm_impl, "l2": "flushed between steps (256 MiB memset outside the timed spans)",
+                       "timing": "per-step CUDA events on the launching stream, max over ranks of the sum"},
+            "roofline": roof, "cpu_baseline": cpu_base, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": args.steps, "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def secondary_workloads(dev, peaks, flush, sync):
+    """Bandwidth ops at 2^30 bits, the [4096, 4097] bool case, the binarised MLP and
+    binary attention: algorithmic GB/s or rate, fraction of the measured HBM peak."""
+    import torch
+    import brute_b200 as brute
+    ops = torch.ops.brute
+    out = {}
+    hbm = peaks["hbm_gbs"]
+
+    def bw(name, fn, alg_bytes, steps=10):
+        ts = time_steps(fn, steps, 3, flush, sync)
+        ms = statistics.median(ts)
+        gbs = alg_bytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "GB/s": gbs, "frac_of_hbm": gbs / hbm, "algorithmic_bytes": alg_bytes}
+
+    n = 1 << 30
+    g = torch.Generator(device=dev).manual_seed(1235)
+    x = torch.randn(n, generator=g, device=dev)
+    bw("pack_sign_f32_2^30", lambda: ops.pack_sign(x, 1), 4 * n + n // 8)
+    p = ops.pack_sign(x, 1)
+    del x
+    q = torch.randint(-2 ** 63, 2 ** 63 - 1, (n // 64,), generator=g, dtype=torch.int64, device=dev)
+    bw("unpack_bool_2^30", lambda: ops.unpack_bool(p, [n]), n // 8 + n)
+    xb = ops.unpack_bool(p, [n])
+    bw("pack_bool_2^30", lambda: ops.pack_bool(xb), n + n // 8)
+    del xb
+    bw("unpack_pm1_f32_2^30", lambda: ops.unpack_bits(p, [n]), n // 8 + 4 * n, steps=5)
+    bw("popcount_total_2^30", lambda: ops.packed_popcount(p), n // 8)
+    bw("hamming_total_2^30", lambda: ops.bit1_hamming_total(p, q), 2 * n // 8)
+    bw("word_popcount_2^30", lambda: ops.popcount(p), n // 8 + n // 16)
+    bw("xor_2^30", lambda: ops.bitwise_packed(p, q, 2, n), 3 * n // 8)
+    bw("not_2^30", lambda: ops.bit1_not_packed(p, n), 2 * n // 8)
+    del p, q
+    xb = torch.rand((4096, 4097), generator=g, device=dev) < 0.3
+    bw("pack_bool_4096x4097", lambda: ops.pack_bool(xb), 4096 * 4097 + 4096 * 65 * 8)
+    pb = ops.pack_bool(xb)
+    bw("unpack_bool_4096x4097", lambda: ops.unpack_bool(pb, [4096, 4097]), 4096 * 4097 + 4096 * 65 * 8)
+    bw("not_4096x4097", lambda: ops.bit1_not_packed(pb, 4097), 2 * 4096 * 65 * 8)
+    del xb, pb
+
+    # binarised MLP, batch 8192, 4096 -> 16384 -> 4096 (BASELINE config 4)
+    xs = brute.pack_sign(torch.randn((8192, 4096), generator=g, device=dev), ge0=True)
+    w1 = brute.pack_sign(torch.randn((16384, 4096), generator=g, device=dev), ge0=True)
+    w2 = brute.pack_sign(torch.randn((4096, 16384), generator=g, device=dev), ge0=True)
+    s1 = torch.rand(16384, generator=g, device=dev) + 0.5
+    s2 = torch.rand(4096, generator=g, device=dev) + 0.5
+
+    def mlp():
+        return brute.binary_linear(brute.binary_linear(xs, w1, s1), w2, s2)
+    ts = time_steps(mlp, 10, 3, flush, sync)
+    ms = statistics.median(ts)
+    macs = 2 * 8192.0 * 4096 * 16384
+    out["mlp_8192x4096x16384x4096"] = {"ms": ms, "tops": macs / (ms * 1e-3) / 1e12}
+    del xs, w1, w2
+
+    # binary attention B=8 H=32 S=4096 D=128 causal (BASELINE config 5)
+    Bq, H, S, D = 8, 32, 4096, 128
+    qb = brute.pack_sign(torch.randn((Bq, H, S, D), generator=g, device=dev), ge0=True)
+    kb = brute.pack_sign(torch.randn((Bq, H, S, D), generator=g, device=dev), ge0=True)
+    v = torch.randn((Bq, H, S, D), generator=g, device=dev).to(torch.bfloat16)
+    ts = time_steps(lambda: brute.binary_attention(qb, kb, v, causal=True), 5, 2, flush, sync)
+    ms = statistics.median(ts)
+    pairs = Bq * H * S * (S + 1) / 2
+    out["attention_8x32x4096x128_causal"] = {
+        "ms": ms, "score_bitmac_tops": pairs * D / (ms * 1e-3) / 1e12,
+        "pv_tflops": 2 * pairs * D / (ms * 1e-3) / 1e12,
+        "algorithmic_bytes": 2 * Bq * H * S * 16 + 2 * Bq * H * S * D * 2}
+    return out
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,254 @@
+// Fused binary attention forward.
+//
+//   score(i,j) = (D - 2*popcount(q_i ^ k_j)) * scale      (integer popcount scores)
+//   P = softmax_j(score) in fp32 (online, blockwise), optional causal mask
+//   O = P @ V, V and O in bf16, fp32 accumulation on the tensor cores
+//
+// One CTA owns 128 query rows of one (batch, head); 8 warps of 16 rows. K (packed
+// words) and V (bf16) stream through shared memory in 64-key tiles with a
+// two-deep cp.async pipeline. Each thread computes the scores that land in ITS
+// lanes of the m16n8k16 A-fragment directly with XOR + POPC from the packed Q
+// words it keeps in registers, so P never leaves registers between the score
+// stage and the P@V MMA. V fragments come from ldmatrix.trans on a 16-byte
+// XOR-swizzled tile.
+#include "common.cuh"
+
+namespace bb {
+
+constexpr int AT_BM = 128, AT_BN = 64, AT_THREADS = 256;
+
+__device__ __forceinline__ void at_cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void at_cp_async8(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" :: "r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// D = 64*W. V tile row = D bf16 = 2*D bytes = D/8 chunks of 16 bytes; chunk c of
+// row r is stored at chunk (c ^ (r & 7)).
+template <int W>
+__global__ void __launch_bounds__(AT_THREADS)
+k_binary_attention_fwd(const uint64_t* __restrict__ Qp, const uint64_t* __restrict__ Kp,
+                       const __nv_bfloat16* __restrict__ V, __nv_bfloat16* __restrict__ O,
+                       int64_t S, int causal, float scale_log2, int64_t q_tiles) {
+    constexpr int D = 64 * W;
+    constexpr int VROW = D * 2;                 // bytes per V row
+    constexpr int VCH = D / 8;                  // 16-byte chunks per V row
+    constexpr int NT = D / 8;                   // n8 tiles of the output
+    __shared__ __align__(16) uint64_t Ks[2][AT_BN * W];
+    __shared__ __align__(128) uint8_t Vs[2][AT_BN * VROW];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    // heavy (late) query tiles first: under a causal mask they have the most keys
+    const int64_t qt = q_tiles - 1 - (int64_t)blockIdx.x;
+    const int64_t bh = blockIdx.y;
+    const int64_t q0 = qt * AT_BM;
+    const uint64_t* Qb = Qp + bh * S * W;
+    const uint64_t* Kb = Kp + bh * S * W;
+    const __nv_bfloat16* Vb = V + bh * S * D;
+    __nv_bfloat16* Ob = O + bh * S * D;
+
+    const int64_t row_lo = q0 + warp * 16 + g, row_hi = row_lo + 8;
+    uint64_t q[2][W];
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+        q[0][w] = row_lo < S ? __ldg(Qb + row_lo * W + w) : 0ull;
+        q[1][w] = row_hi < S ? __ldg(Qb + row_hi * W + w) : 0ull;
+    }
+
+    const int64_t kend = causal ? (q0 + AT_BM < S ? q0 + AT_BM : S) : S;   // keys [0, kend)
+    const int64_t ntiles = (kend + AT_BN - 1) / AT_BN;
+    const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(&Ks[0][0]);
+    const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(&Vs[0][0]);
+
+    auto load_tile = [&](int buf, int64_t tile) {
+        const int64_t k0 = tile * AT_BN;
+        // K: 64 keys x W words
+        if (tid < AT_BN * W) {
+            const int key = tid / W, w = tid % W;
+            const bool ok = k0 + key < S;
+            at_cp_async8(ks_base + (buf * AT_BN * W + tid) * 8, Kb + (ok ? (k0 + key) * W + w : 0), ok ? 8 : 0);
+        }
+        // V: 64 rows x VCH chunks
+#pragma unroll
+        for (int it = 0; it < (AT_BN * VCH) / AT_THREADS; ++it) {
+            const int idx = tid + it * AT_THREADS;
+            const int row = idx / VCH, ch = idx % VCH;
+            const bool ok = k0 + row < S;
+            const int sch = (ch & ~7) | ((ch ^ row) & 7);
+            at_cp_async16(vs_base + buf * AT_BN * VROW + row * VROW + sch * 16,
+                          Vb + (ok ? (k0 + row) * D + ch * 8 : 0), ok ? 16 : 0);
+        }
+    };
+
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+
+    if (ntiles > 0) load_tile(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    for (int64_t tile = 0; tile < ntiles; ++tile) {
+        const int buf = (int)(tile & 1);
+        if (tile + 1 < ntiles) load_tile(buf ^ 1, tile + 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+
+        const int64_t k0 = tile * AT_BN;
+        // a warp whose rows all precede this tile has nothing to add
+        const bool active = !(causal && k0 > q0 + warp * 16 + 15);
+        if (active) {
+            // ---- scores: s[h][kb][c], h = row half, kb = 16-key block, c: 0,1 -> cols 2t,2t+1; 2,3 -> 2t+8,2t+9
+            float s[2][4][4];
+            const bool need_mask = (causal && k0 + AT_BN - 1 > q0 + warp * 16) || (k0 + AT_BN > S);
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int key = kb * 16 + 2 * t + (c & 1) + ((c >> 1) << 3);
+                    int h0 = 0, h1 = 0;
+#pragma unroll
+                    for (int w = 0; w < W; ++w) {
+                        const uint64_t kw = Ks[buf][key * W + w];
+                        h0 += __popcll(q[0][w] ^ kw);
+                        h1 += __popcll(q[1][w] ^ kw);
+                    }
+                    float s0 = (float)(D - 2 * h0) * scale_log2;
+                    float s1 = (float)(D - 2 * h1) * scale_log2;
+                    if (need_mask) {
+                        const int64_t kidx = k0 + key;
+                        if (kidx >= S || (causal && kidx > row_lo)) s0 = -INFINITY;
+                        if (kidx >= S || (causal && kidx > row_hi)) s1 = -INFINITY;
+                    }
+                    s[0][kb][c] = s0;
+                    s[1][kb][c] = s1;
+                }
+            }
+            // ---- online softmax (log2 domain)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) mx = fmaxf(mx, s[h][kb][c]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float mnew = fmaxf(mrow[h], mx);
+                // mnew stays -inf only if every key so far was masked for this row
+                const float msafe = mnew == -INFINITY ? 0.f : mnew;
+                const float alpha = exp2f(mrow[h] - msafe);
+                float sum = 0.f;
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float p = exp2f(s[h][kb][c] - msafe);
+                        s[h][kb][c] = p;
+                        sum += p;
+                    }
+                lrow[h] = lrow[h] * alpha + sum;
+                mrow[h] = mnew;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) { o[j][2 * h] *= alpha; o[j][2 * h + 1] *= alpha; }
+            }
+            // ---- O += P @ V
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                const uint32_t a0 = pack_bf16x2(s[0][kb][0], s[0][kb][1]);
+                const uint32_t a1 = pack_bf16x2(s[1][kb][0], s[1][kb][1]);
+                const uint32_t a2 = pack_bf16x2(s[0][kb][2], s[0][kb][3]);
+                const uint32_t a3 = pack_bf16x2(s[1][kb][2], s[1][kb][3]);
+                const int vrow = kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                for (int j = 0; j < NT; j += 2) {
+                    const int ch = j + (lane >> 4);
+                    const int sch = (ch & ~7) | ((ch ^ vrow) & 7);
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(vs_base + buf * AT_BN * VROW + vrow * VROW + sch * 16, b0, b1, b2, b3);
+                    mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+                    mma_bf16_16816(o[j + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+        __syncthreads();   // everyone is done with `buf` before it is refilled
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    // ---- finalise: divide by the row sums, stage through shared memory, 16-byte stores
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = lrow[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int r = warp * 16 + g + 8 * h;         // row within the CTA tile
+        if (AT_BM * VROW <= 2 * AT_BN * VROW) {
+            uint8_t* srow = &Vs[0][0] + r * VROW;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int sch = (j & ~7) | ((j ^ r) & 7);
+                *reinterpret_cast<uint32_t*>(srow + sch * 16 + t * 4) =
+                    pack_bf16x2(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < (AT_BM * VCH) / AT_THREADS; ++it) {
+        const int idx = tid + it * AT_THREADS;
+        const int r = idx / VCH, ch = idx % VCH;
+        const int sch = (ch & ~7) | ((ch ^ r) & 7);
+        if (q0 + r < S) {
+            const uint4 v = *reinterpret_cast<const uint4*>(&Vs[0][0] + r * VROW + sch * 16);
+            *reinterpret_cast<uint4*>(Ob + (q0 + r) * D + ch * 8) = v;
+        }
+    }
+}
+
+}  // namespace bb
+
+using namespace bb;
+
+extern "C" int brute_b200_binary_attention_fwd(const uint64_t* Qp, const uint64_t* Kp_,
+                                               const void* V, void* O,
+                                               int64_t B, int64_t H, int64_t S, int64_t D,
+                                               int causal, float scale, void* stream) {
+    BB_REQUIRE(B >= 0 && H >= 0 && S >= 0, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(D == 64 || D == 128, BRUTE_ERR_UNSUPPORTED);
+    if (B * H == 0 || S == 0) return BRUTE_OK;
+    BB_REQUIRE(Qp && Kp_ && V && O, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(Qp) && aligned8(Kp_) && aligned16(V) && aligned16(O), BRUTE_ERR_MISALIGNED);
+    BB_REQUIRE(B * H <= 65535, BRUTE_ERR_UNSUPPORTED);
+    BB_REQUIRE(scale == scale, BRUTE_ERR_INVALID_ARG);
+    const int64_t q_tiles = (S + AT_BM - 1) / AT_BM;
+    const dim3 grid((unsigned)q_tiles, (unsigned)(B * H));
+    const float scale_log2 = scale * 1.4426950408889634f;
+    cudaStream_t st = as_stream(stream);
+    auto* v = static_cast<const __nv_bfloat16*>(V);
+    auto* o = static_cast<__nv_bfloat16*>(O);
+    if (D == 128) k_binary_attention_fwd<2><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, scale_log2, q_tiles);
+    else          k_binary_attention_fwd<1><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, scale_log2, q_tiles);
+    return launch_status();
+}

@@ -1,0 +1,137 @@
+// xnor-popcount GEMM entry points: argument checks and the choice of
+// instruction path (CUDA-core POPC, legacy b1 mma.sync, tcgen05 kind::i8).
+#include "common.cuh"
+#include "gemm_popc.cuh"
+#include "gemm_mma_b1.cuh"
+#include "gemm_tcgen05.cuh"
+
+#include <cstdlib>
+#include <cstring>
+
+namespace bb {
+
+struct GemmArgs {
+    const uint64_t* A; const uint64_t* B;
+    int64_t M, N, Kp, K;
+    // plain output
+    int32_t* C; int64_t ldc;
+    // fused scale + sign + pack output
+    const float* scale; uint64_t* out; int mode;
+    bool pack;
+};
+
+static int run_popc(const GemmArgs& g, cudaStream_t st) {
+    const dim3 grid((unsigned)((g.N + PG_BN - 1) / PG_BN), (unsigned)((g.M + PG_BM - 1) / PG_BM));
+    BB_REQUIRE(grid.y <= 65535, BRUTE_ERR_UNSUPPORTED);
+    if (!g.pack) {
+        EpilogueInt32 ep{g.C, g.ldc, g.M, g.N};
+        k_xnor_gemm_popc<<<grid, PG_THREADS, 0, st>>>(g.A, g.B, g.M, g.N, g.Kp, (int32_t)g.K, ep);
+    } else {
+        EpilogueScaleSignPack ep{g.scale, g.out, (g.N + 63) / 64, g.M, g.N, g.mode};
+        k_xnor_gemm_popc<<<grid, PG_THREADS, 0, st>>>(g.A, g.B, g.M, g.N, g.Kp, (int32_t)g.K, ep);
+    }
+    return launch_status();
+}
+
+static bool mma_b1_accepts(const GemmArgs& g) {
+    return g.Kp > 0 && (g.Kp % 2) == 0 && aligned16(g.A) && aligned16(g.B) &&
+           (g.M + MB_BM - 1) / MB_BM <= 65535;
+}
+
+static int run_mma_b1(const GemmArgs& g, cudaStream_t st) {
+    BB_REQUIRE(mma_b1_accepts(g), BRUTE_ERR_UNSUPPORTED);
+    static bool attr_set[2] = {false, false};
+    const dim3 grid((unsigned)((g.N + MB_BN - 1) / MB_BN), (unsigned)((g.M + MB_BM - 1) / MB_BM));
+    auto* A8 = reinterpret_cast<const uint8_t*>(g.A);
+    auto* B8 = reinterpret_cast<const uint8_t*>(g.B);
+    if (!g.pack) {
+        if (!attr_set[0]) {
+            cudaFuncSetAttribute(k_xnor_gemm_mma_b1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MB_SMEM);
+            attr_set[0] = true;
+        }
+        k_xnor_gemm_mma_b1<false><<<grid, MB_THREADS, MB_SMEM, st>>>(
+            A8, B8, g.M, g.N, g.Kp * 8, (int32_t)g.K, g.C, g.ldc, nullptr, nullptr, 0, 0);
+    } else {
+        if (!attr_set[1]) {
+            cudaFuncSetAttribute(k_xnor_gemm_mma_b1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MB_SMEM);
+            attr_set[1] = true;
+        }
+        k_xnor_gemm_mma_b1<true><<<grid, MB_THREADS, MB_SMEM, st>>>(
+            A8, B8, g.M, g.N, g.Kp * 8, (int32_t)g.K, nullptr, 0, g.scale,
+            reinterpret_cast<uint32_t*>(g.out), 2 * ((g.N + 63) / 64), g.mode);
+    }
+    return launch_status();
+}
+
+static int env_impl() {
+    // BRUTE_GEMM_IMPL overrides AUTO so that profiler runs can compare the pipes.
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    const char* e = std::getenv("BRUTE_GEMM_IMPL");
+    int v = BRUTE_GEMM_AUTO;
+    if (e) {
+        if (!std::strcmp(e, "popc")) v = BRUTE_GEMM_POPC;
+        else if (!std::strcmp(e, "b1") || !std::strcmp(e, "mma_b1")) v = BRUTE_GEMM_MMA_B1;
+        else if (!std::strcmp(e, "i8") || !std::strcmp(e, "tcgen05")) v = BRUTE_GEMM_TCGEN05;
+    }
+    cached = v;
+    return v;
+}
+
+static int dispatch(const GemmArgs& g, int impl, cudaStream_t st) {
+    if (impl == BRUTE_GEMM_AUTO) impl = env_impl();
+    if (impl == BRUTE_GEMM_AUTO) {
+        // Small problems do not fill the tensor-core tiles; the CUDA-core path
+        // has no shape rules at all.
+        if (tc5_accepts(g.A, g.B, g.M, g.N, g.Kp) && g.M * g.N >= 128 * 256) impl = BRUTE_GEMM_TCGEN05;
+        else if (mma_b1_accepts(g) && g.M * g.N >= 64 * 64) impl = BRUTE_GEMM_MMA_B1;
+        else impl = BRUTE_GEMM_POPC;
+    }
+    switch (impl) {
+        case BRUTE_GEMM_POPC:   return run_popc(g, st);
+        case BRUTE_GEMM_MMA_B1: return run_mma_b1(g, st);
+        case BRUTE_GEMM_TCGEN05:
+            return tc5_run(g.A, g.B, g.M, g.N, g.Kp, g.K, g.C, g.ldc, g.scale, g.out, g.mode, g.pack, st);
+        default: return BRUTE_ERR_INVALID_ARG;
+    }
+}
+
+}  // namespace bb
+
+using namespace bb;
+
+extern "C" int brute_b200_xnor_gemm(const uint64_t* A, const uint64_t* B, int32_t* C,
+                                    int64_t M, int64_t N, int64_t Kp, int64_t K, int64_t ldc,
+                                    int impl, void* stream) {
+    BB_REQUIRE(M >= 0 && N >= 0 && Kp >= 0 && K >= 0 && K <= 64 * Kp, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(K < (1ll << 30) && M < (1ll << 31) && N < (1ll << 31), BRUTE_ERR_UNSUPPORTED);
+    BB_REQUIRE(impl >= BRUTE_GEMM_AUTO && impl <= BRUTE_GEMM_TCGEN05, BRUTE_ERR_INVALID_ARG);
+    if (M == 0 || N == 0) return BRUTE_OK;
+    BB_REQUIRE(C != nullptr && ldc >= N, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE((reinterpret_cast<uintptr_t>(C) & 3u) == 0, BRUTE_ERR_MISALIGNED);
+    BB_REQUIRE(Kp == 0 || (A != nullptr && B != nullptr), BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(A) && aligned8(B), BRUTE_ERR_MISALIGNED);
+    GemmArgs g{A, B, M, N, Kp, K, C, ldc, nullptr, nullptr, 0, false};
+    if (Kp == 0) return run_popc(g, as_stream(stream));     // C = K (= 0) everywhere
+    return dispatch(g, impl, as_stream(stream));
+}
+
+extern "C" int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B,
+                                                    const float* scale, uint64_t* out,
+                                                    int64_t M, int64_t N, int64_t Kp, int64_t K,
+                                                    int mode, int impl, void* stream) {
+    BB_REQUIRE(M >= 0 && N >= 0 && Kp >= 0 && K >= 0 && K <= 64 * Kp, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(K < (1ll << 30) && M < (1ll << 31) && N < (1ll << 31), BRUTE_ERR_UNSUPPORTED);
+    BB_REQUIRE(mode == BRUTE_SIGN_GT0 || mode == BRUTE_SIGN_GE0, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(impl >= BRUTE_GEMM_AUTO && impl <= BRUTE_GEMM_TCGEN05, BRUTE_ERR_INVALID_ARG);
+    if (M == 0 || N == 0) return BRUTE_OK;
+    BB_REQUIRE(scale != nullptr && out != nullptr, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(out) && (reinterpret_cast<uintptr_t>(scale) & 3u) == 0, BRUTE_ERR_MISALIGNED);
+    BB_REQUIRE(Kp == 0 || (A != nullptr && B != nullptr), BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(A) && aligned8(B), BRUTE_ERR_MISALIGNED);
+    GemmArgs g{A, B, M, N, Kp, K, nullptr, 0, scale, out, mode, true};
+    if (Kp == 0) return run_popc(g, as_stream(stream));
+    return dispatch(g, impl, as_stream(stream));
+}
+
+namespace bb { int tc5_status_bridge() { return tc5_device_status(); } }

@@ -1,0 +1,415 @@
+// xnor-popcount GEMM on the 5th-generation tensor cores (tcgen05.mma kind::i8).
+//
+// sm_100a has no binary tcgen05 kind, so the bits are expanded to int8 ON CHIP:
+// bit 1 -> -1 (0xFF), bit 0 -> +1 (0x01) for both operands, which leaves every
+// product unchanged ((-a)(-b) = ab), so the int32 accumulator holds the +-1 dot
+// product over the padded K and C = acc - (64*Kp - K). Only PACKED operands
+// ever cross HBM/L2 (8x less operand traffic than an int8 GEMM), the expansion
+// is paid per CTA in shared memory.
+//
+// Per CTA (one 128 x 256 tile of C, accumulator = 256 TMEM columns):
+//   warp 8      TMA producer: packed A [128 rows x 64 B] and B [256 rows x 64 B]
+//               boxes (512 bits of K) into a 3-deep ring, SWIZZLE_64B.
+//   warps 0..7  expanders: per 128-bit k-block, each thread turns three 64-bit
+//               half rows into 3 x 64 int8 and stores them in the canonical
+//               K-major SWIZZLE_128B operand layout (3-deep ring), then
+//               fence.proxy.async + mbarrier arrive.
+//   warp 9      MMA issuer: 4 x tcgen05.mma (M128 N256 K32) per k-block,
+//               tcgen05.commit frees the operand slot; owns the TMEM allocation.
+//   warps 0..7  epilogue: tcgen05.ld 32x32b, K-correction, 128-bit stores (or the
+//               fused scale/sign/pack of the binarised MLP).
+// The order of the 128 k-positions inside a k-block is permuted by the
+// expansion (byte 4j+i of a 32-byte group holds bit 8i+j); A and B share the
+// permutation, which a dot product cannot see.
+//
+// Every mbarrier wait is bounded (about one second); a wait that gives up sets
+// the device status word and an abort flag, the CTA drains its copies, frees
+// its TMEM and returns, and CTAs that start later return at once.
+#pragma once
+#include "common.cuh"
+#include <cuda.h>
+
+namespace bb {
+
+constexpr int TC_BM = 128, TC_BN = 256;
+constexpr int TC_PSTAGES = 3, TC_ESTAGES = 3;
+constexpr int TC_PK = 64;                               // packed bytes of K per TMA stage and row
+constexpr int TC_KB_PER_STAGE = 4;                      // 128-bit k-blocks per packed stage
+constexpr int TC_P_A = TC_BM * TC_PK, TC_P_B = TC_BN * TC_PK;
+constexpr int TC_P_STAGE = TC_P_A + TC_P_B;             // 24 KB
+constexpr int TC_E_A = TC_BM * 128, TC_E_B = TC_BN * 128;
+constexpr int TC_E_STAGE = TC_E_A + TC_E_B;             // 48 KB
+constexpr int TC_EXP_WARPS = 8;
+constexpr int TC_THREADS = (TC_EXP_WARPS + 2) * 32;     // 320
+constexpr int TC_TMEM_COLS = 256;
+constexpr int TC_SMEM = TC_ESTAGES * TC_E_STAGE + TC_PSTAGES * TC_P_STAGE + 256 + 1024;
+constexpr uint64_t TC_WAIT_NS = 1000000000ull;          // bound of every in-kernel wait
+
+__device__ int g_tc_status = 0;                         // 0 ok; else which wait gave up
+
+// ---- PTX wrappers --------------------------------------------------------
+__device__ __forceinline__ uint64_t tc_globaltimer() {
+    uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait. Returns false after TC_WAIT_NS or when another role of this CTA
+// has already given up; `code` names the waiting role in the status word.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = tc_globaltimer();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if (((++spins) & 0xFFu) == 0) {
+            if (*abort_flag) return false;
+            if (tc_globaltimer() - t0 > TC_WAIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(&g_tc_status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        :: "r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, SWIZZLE_128B shared-memory operand descriptor: 8-row atoms of 1024
+// bytes stacked along M/N (stride byte offset 1024), descriptor version 1.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// kind::i8, D = s32, A = B = signed int8, both K-major, M = 128, N = 256
+constexpr uint32_t TC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
+                              ((uint32_t)(TC_BM >> 4) << 24);
+
+// 4 bits of h (bits j, 8+j, 16+j, 24+j) -> 4 bytes, 0xFF for a set bit, 0x01 otherwise
+__device__ __forceinline__ uint32_t tc_expand4(uint32_t h, int j) {
+    uint32_t m;
+    asm("prmt.b32 %0, %1, 0, 0xBA98;" : "=r"(m) : "r"(h << (7 - j)));   // msb of each byte replicated
+    return m | 0x01010101u;
+}
+
+// 64 bits (one half of a 128-bit k-block of one row) -> 64 int8 into 4 chunks of
+// the 128-byte operand row. `half` selects chunks 4*half .. 4*half+3.
+__device__ __forceinline__ void tc_expand_half(uint2 bits, uint32_t row_saddr, int row, int half) {
+    const uint32_t h[2] = {bits.x, bits.y};
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const uint32_t w0 = tc_expand4(h[q], 4 * c + 0), w1 = tc_expand4(h[q], 4 * c + 1);
+            const uint32_t w2 = tc_expand4(h[q], 4 * c + 2), w3 = tc_expand4(h[q], 4 * c + 3);
+            const int chunk = 4 * half + 2 * q + c;
+            const uint32_t dst = row_saddr + (uint32_t)(((chunk ^ (row & 7)) << 4));
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" :: "r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        }
+    }
+}
+
+template <bool PACK>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    int64_t M, int64_t N, int32_t nkb /* 128-bit k-blocks */, int32_t kcorr /* 64*Kp - K */,
+                    int32_t* __restrict__ C, int64_t ldc,
+                    const float* __restrict__ scale, uint32_t* __restrict__ out32, int64_t halves_per_row, int mode) {
+    extern __shared__ uint8_t tc_smem_raw[];
+    __shared__ int s_skip;
+    if (threadIdx.x == 0) s_skip = *(volatile int*)&g_tc_status;
+    __syncthreads();
+    if (s_skip != 0) return;                            // an earlier CTA gave up: do not queue behind it
+
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(tc_smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = tc_smem_raw + (base - raw);
+    const uint32_t e_ring = base;                                    // TC_ESTAGES x 48 KB
+    const uint32_t p_ring = base + TC_ESTAGES * TC_E_STAGE;          // TC_PSTAGES x 24 KB
+    const uint32_t bars = p_ring + TC_PSTAGES * TC_P_STAGE;
+    uint8_t* gp_ring = gbase + TC_ESTAGES * TC_E_STAGE;
+    uint8_t* gbars = gp_ring + TC_PSTAGES * TC_P_STAGE;
+    // barrier slots (8 bytes each)
+    auto p_full  = [&](int s) { return bars + 8u * s; };
+    auto p_empty = [&](int s) { return bars + 8u * (TC_PSTAGES + s); };
+    auto e_full  = [&](int s) { return bars + 8u * (2 * TC_PSTAGES + s); };
+    auto e_empty = [&](int s) { return bars + 8u * (2 * TC_PSTAGES + TC_ESTAGES + s); };
+    const uint32_t acc_full = bars + 8u * (2 * TC_PSTAGES + 2 * TC_ESTAGES);
+    const uint32_t drain_bar = acc_full + 8u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (2 * TC_PSTAGES + 2 * TC_ESTAGES + 2));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (2 * TC_PSTAGES + 2 * TC_ESTAGES + 2) + 4);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t m0 = (int64_t)blockIdx.y * TC_BM, n0 = (int64_t)blockIdx.x * TC_BN;
+    const int32_t nstages = (nkb + TC_KB_PER_STAGE - 1) / TC_KB_PER_STAGE;
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_PSTAGES; ++s) { mbar_init(p_full(s), 1); mbar_init(p_empty(s), TC_EXP_WARPS); }
+        for (int s = 0; s < TC_ESTAGES; ++s) { mbar_init(e_full(s), TC_EXP_WARPS); mbar_init(e_empty(s), 1); }
+        mbar_init(acc_full, 1);
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async_smem();
+    }
+    if (warp == TC_EXP_WARPS + 1) {      // TMEM allocation: one full warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"((uint32_t)__cvta_generic_to_shared((const void*)tmem_slot)), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == TC_EXP_WARPS) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            bool ok = true;
+            int32_t issued = 0;
+            for (int32_t st = 0; st < nstages && ok; ++st) {
+                const int s = st % TC_PSTAGES;
+                ok = mbar_wait(p_empty(s), ((st / TC_PSTAGES) & 1) ^ 1, abort_flag, 1);
+                if (!ok) break;
+                mbar_expect_tx(p_full(s), TC_P_STAGE);
+                tma_load_2d(p_ring + s * TC_P_STAGE, &tmA, st * TC_PK, (int32_t)m0, p_full(s));
+                tma_load_2d(p_ring + s * TC_P_STAGE + TC_P_A, &tmB, st * TC_PK, (int32_t)n0, p_full(s));
+                issued = st + 1;
+            }
+            if (!ok) {
+                // drain: wait (bounded) for the copies already issued before the CTA may exit
+                const int32_t first = issued > TC_PSTAGES ? issued - TC_PSTAGES : 0;
+                for (int32_t st = first; st < issued; ++st) {
+                    const uint64_t t0 = tc_globaltimer();
+                    while (!mbar_try(p_full(st % TC_PSTAGES), (st / TC_PSTAGES) & 1) &&
+                           tc_globaltimer() - t0 < TC_WAIT_NS) {}
+                }
+            }
+        }
+    } else if (warp == TC_EXP_WARPS + 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            bool ok = true;
+            for (int32_t i = 0; i < nkb && ok; ++i) {
+                const int r = i % TC_ESTAGES;
+                ok = mbar_wait(e_full(r), (i / TC_ESTAGES) & 1, abort_flag, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t adesc = tc_smem_desc(e_ring + r * TC_E_STAGE);
+                const uint64_t bdesc = tc_smem_desc(e_ring + r * TC_E_STAGE + TC_E_A);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)      // 32 bytes of K per instruction: +2 in the encoded address
+                    tc_mma_i8(tmem, adesc + 2u * k, bdesc + 2u * k, TC_IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(e_empty(r));
+            }
+            if (ok) tc_commit(acc_full);
+            // all MMAs issued so far are complete once this commit lands
+            tc_commit(drain_bar);
+            const uint64_t t0 = tc_globaltimer();
+            while (!mbar_try(drain_bar, 0) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
+        }
+    } else {
+        // ================= expanders, then epilogue =================
+        const int erow = tid >> 1, half = tid & 1;       // rows erow (A), erow and erow+128 (B)
+        bool ok = true;
+        for (int32_t i = 0; i < nkb && ok; ++i) {
+            const int32_t st = i / TC_KB_PER_STAGE, kb = i % TC_KB_PER_STAGE;
+            const int s = st % TC_PSTAGES;
+            if (kb == 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(p_full(s), (st / TC_PSTAGES) & 1, abort_flag, 3));
+                if (!ok) break;
+            }
+            // packed 8 bytes of (row, k-block, half) under SWIZZLE_64B
+            const uint8_t* ps = gp_ring + s * TC_P_STAGE;
+            auto packed = [&](const uint8_t* tile, int row) {
+                return *reinterpret_cast<const uint2*>(tile + row * TC_PK + (((kb ^ (row >> 1)) & 3) << 4) + half * 8);
+            };
+            const uint2 a  = packed(ps, erow);
+            const uint2 b0 = packed(ps + TC_P_A, erow);
+            const uint2 b1 = packed(ps + TC_P_A, erow + 128);
+            if (kb == TC_KB_PER_STAGE - 1 || i == nkb - 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_empty(s));
+            }
+            const int r = i % TC_ESTAGES;
+            ok = __all_sync(0xffffffffu, mbar_wait(e_empty(r), ((i / TC_ESTAGES) & 1) ^ 1, abort_flag, 4));
+            if (!ok) break;
+            const uint32_t ea = e_ring + r * TC_E_STAGE, eb = ea + TC_E_A;
+            tc_expand_half(a,  ea + erow * 128, erow, half);
+            tc_expand_half(b0, eb + erow * 128, erow, half);
+            tc_expand_half(b1, eb + (erow + 128) * 128, erow + 128, half);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(e_full(r));
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, 5));
+        if (ok) {
+            tc_fence_after();
+            const int quarter = warp & 3, chalf = warp >> 2;
+            const int64_t m = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                const int col = chalf * 128 + cc * 32;
+                uint32_t v[32];
+                tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col, v);
+                tc_wait_ld();
+                const int64_t n = n0 + col;
+                if (!PACK) {
+                    if (m < M) {
+                        int32_t* dst = C + m * ldc + n;
+                        if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<int4*>(dst + j) = make_int4((int32_t)v[j] - kcorr, (int32_t)v[j + 1] - kcorr,
+                                                                             (int32_t)v[j + 2] - kcorr, (int32_t)v[j + 3] - kcorr);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (n + j < N) dst[j] = (int32_t)v[j] - kcorr;
+                        }
+                    }
+                } else {
+                    uint32_t bits = 0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (n + j < N) {
+                            const float y = __ldg(scale + n + j) * (float)((int32_t)v[j] - kcorr);
+                            const bool b = mode == BRUTE_SIGN_GE0 ? (y >= 0.0f) : (y > 0.0f);
+                            bits |= (b ? 1u : 0u) << j;
+                        }
+                    }
+                    const int64_t hidx = n >> 5;
+                    if (m < M && hidx < halves_per_row) out32[m * halves_per_row + hidx] = bits;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TC_EXP_WARPS + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"((uint32_t)TC_TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------
+typedef CUresult (*PFN_tmapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                        CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static PFN_tmapEncodeTiled tc5_encode_fn() {
+    static PFN_tmapEncodeTiled fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_tmapEncodeTiled>(p);
+    }
+    return fn;
+}
+
+// Packed operand [rows, kbytes] as a 2-D byte tensor, box = [box_rows, 64 bytes].
+static bool tc5_make_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t kbytes, int box_rows) {
+    PFN_tmapEncodeTiled enc = tc5_encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)kbytes};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_PK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Shapes the tcgen05 path takes: row pitch a multiple of 16 bytes (TMA global
+// stride rule), 16-byte aligned bases, tile counts within the grid limits.
+static bool tc5_accepts(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp) {
+    return Kp > 0 && (Kp % 2) == 0 && aligned16(A) && aligned16(B) && M > 0 && N > 0 &&
+           (M + TC_BM - 1) / TC_BM <= 65535 && Kp * 8 < (1ll << 31);
+}
+
+static int tc5_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp, int64_t K,
+                   int32_t* C, int64_t ldc, const float* scale, uint64_t* out, int mode, bool pack,
+                   cudaStream_t st) {
+    BB_REQUIRE(tc5_accepts(A, B, M, N, Kp), BRUTE_ERR_UNSUPPORTED);
+    CUtensorMap tmA, tmB;
+    BB_REQUIRE(tc5_make_map(&tmA, A, M, Kp * 8, TC_BM) && tc5_make_map(&tmB, B, N, Kp * 8, TC_BN), BRUTE_ERR_DRIVER);
+    static bool attr_set[2] = {false, false};
+    const dim3 grid((unsigned)((N + TC_BN - 1) / TC_BN), (unsigned)((M + TC_BM - 1) / TC_BM));
+    const int32_t nkb = (int32_t)(Kp / 2);
+    const int32_t kcorr = (int32_t)(64 * Kp - K);
+    if (!pack) {
+        if (!attr_set[0]) {
+            if (cudaFuncSetAttribute(k_xnor_gemm_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess)
+                return BRUTE_ERR_LAUNCH;
+            attr_set[0] = true;
+        }
+        k_xnor_gemm_tcgen05<false><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, kcorr, C, ldc, nullptr, nullptr, 0, 0);
+    } else {
+        if (!attr_set[1]) {
+            if (cudaFuncSetAttribute(k_xnor_gemm_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess)
+                return BRUTE_ERR_LAUNCH;
+            attr_set[1] = true;
+        }
+        k_xnor_gemm_tcgen05<true><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, kcorr, nullptr, 0, scale,
+                                                                    reinterpret_cast<uint32_t*>(out), 2 * ((N + 63) / 64), mode);
+    }
+    return launch_status();
+}
+
+static int tc5_device_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return BRUTE_ERR_LAUNCH;
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+        return BRUTE_ERR_DEVICE_WAIT;
+    }
+    return BRUTE_OK;
+}
+
+}  // namespace bb

@@ -1,0 +1,341 @@
+// pack / unpack between 1-byte (or float) elements and 64-bit packed words.
+//
+// All four kernels are HBM-bound streaming kernels. Work is cut into warp
+// tasks "(row, chunk of the row)" so that a warp always reads or writes one
+// contiguous span with 128-bit accesses; rows whose byte address is not a
+// multiple of 16 (e.g. 4097 bools per row) keep 128-bit ALIGNED accesses and
+// shift the bits instead. Shapes whose last dimension is a multiple of 64 are
+// flattened to a single row by the launchers, since their packed rows are
+// contiguous too.
+#include "common.cuh"
+
+namespace bb {
+
+// ===========================================================================
+// pack_bool
+// ===========================================================================
+
+// Load the 16 bytes at the 16-byte-aligned address p, reading only bytes
+// inside [lo, hi); bytes outside read as 0.
+__device__ __forceinline__ uint4 load16_guarded(uintptr_t p, uintptr_t lo, uintptr_t hi) {
+    if (p >= lo && p + 16 <= hi) return ldg_stream(reinterpret_cast<const void*>(p));
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        uintptr_t q = p + i;
+        if (q >= lo && q < hi)
+            w[i >> 2] |= (uint32_t)(*reinterpret_cast<const uint8_t*>(q)) << (8 * (i & 3));
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+struct PackLoad {
+    uint4 lo, hi;      // aligned group of this lane; lane 31 also holds the next one
+    int64_t r, g;      // row, 16-byte group index within the row
+    uint32_t m;        // misalignment of the row start (bytes, 0..15)
+};
+
+__device__ __forceinline__ PackLoad pack_bool_load(const uint8_t* in, int64_t ld, int64_t cpr,
+                                                   int64_t task, uintptr_t buf_lo, uintptr_t buf_hi,
+                                                   int lane) {
+    PackLoad t;
+    t.r = task / cpr;
+    const int64_t c = task - t.r * cpr;
+    t.g = c * 32 + lane;
+    const uintptr_t rowp = reinterpret_cast<uintptr_t>(in) + (uintptr_t)(t.r * ld);
+    const uintptr_t row_end = rowp + (uintptr_t)ld;
+    t.m = (uint32_t)(rowp & 15u);
+    const uintptr_t ab = rowp + (uintptr_t)(t.g * 16) - t.m;
+    t.lo = make_uint4(0u, 0u, 0u, 0u);
+    t.hi = make_uint4(0u, 0u, 0u, 0u);
+    if (ab < row_end) t.lo = load16_guarded(ab, buf_lo, buf_hi);
+    if (t.m != 0 && lane == 31 && ab + 16 < row_end) t.hi = load16_guarded(ab + 16, buf_lo, buf_hi);
+    return t;
+}
+
+__device__ __forceinline__ void pack_bool_finish(const PackLoad& t, uint64_t* out, int64_t ld,
+                                                 int64_t wpr, int lane) {
+    const uint32_t lob = nonzero_bytes_to_bits16(t.lo);
+    uint32_t hib = __shfl_down_sync(0xffffffffu, lob, 1);
+    if (lane == 31) hib = nonzero_bytes_to_bits16(t.hi);
+    uint32_t bits = ((lob | (hib << 16)) >> t.m) & 0xFFFFu;
+    const int64_t valid = ld - t.g * 16;
+    if (valid <= 0) bits = 0;
+    else if (valid < 16) bits &= (1u << (int)valid) - 1u;
+    // 4 neighbouring lanes hold the four 16-bit quarters of one word
+    uint32_t half = bits << (16 * (lane & 1));
+    half |= __shfl_xor_sync(0xffffffffu, half, 1);
+    const uint32_t other = __shfl_xor_sync(0xffffffffu, half, 2);
+    if ((lane & 3) == 0) {
+        const int64_t w = t.g >> 2;
+        if (w < wpr) out[t.r * wpr + w] = (uint64_t)half | ((uint64_t)other << 32);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_pack_bool(const uint8_t* __restrict__ in, uint64_t* __restrict__ out,
+            int64_t rows, int64_t ld, int64_t wpr, int64_t cpr, int64_t tasks) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const uintptr_t buf_lo = reinterpret_cast<uintptr_t>(in);
+    const uintptr_t buf_hi = buf_lo + (uintptr_t)(rows * ld);
+    int64_t task = warp;
+    // two tasks per trip: both loads are in flight before either is consumed
+    for (; task + nwarps < tasks; task += 2 * nwarps) {
+        PackLoad a = pack_bool_load(in, ld, cpr, task, buf_lo, buf_hi, lane);
+        PackLoad b = pack_bool_load(in, ld, cpr, task + nwarps, buf_lo, buf_hi, lane);
+        pack_bool_finish(a, out, ld, wpr, lane);
+        pack_bool_finish(b, out, ld, wpr, lane);
+    }
+    if (task < tasks) {
+        PackLoad a = pack_bool_load(in, ld, cpr, task, buf_lo, buf_hi, lane);
+        pack_bool_finish(a, out, ld, wpr, lane);
+    }
+}
+
+// ===========================================================================
+// pack_sign: float / bf16 / f16 -> bits in one pass
+// ===========================================================================
+
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+
+__device__ __forceinline__ bool sign_bit(float x, int mode) {
+    return mode == BRUTE_SIGN_GE0 ? (x >= 0.0f) : (x > 0.0f);   // NaN -> false
+}
+
+// One element per lane and load: fully coalesced scalar loads, one ballot per
+// 32 elements. Warp task = 256 elements of one row = 4 output words.
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_pack_sign_ballot(const T* __restrict__ in, uint64_t* __restrict__ out,
+                   int64_t ld, int64_t wpr, int64_t cpr, int64_t tasks, int mode) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t task = warp; task < tasks; task += nwarps) {
+        const int64_t r = task / cpr;
+        const int64_t c = task - r * cpr;
+        const T* rowp = in + r * ld;
+        const int64_t base = c * 256 + lane;
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t i = base + 32 * j;
+            x[j] = (i < ld) ? to_f32<T>(__ldcs(rowp + i)) : -1.0f;
+        }
+        uint32_t b[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = __ballot_sync(0xffffffffu, sign_bit(x[j], mode));
+        if (lane < 4) {
+            const uint32_t lo = lane == 0 ? b[0] : lane == 1 ? b[2] : lane == 2 ? b[4] : b[6];
+            const uint32_t hi = lane == 0 ? b[1] : lane == 1 ? b[3] : lane == 2 ? b[5] : b[7];
+            const int64_t w = c * 4 + lane;
+            if (w < wpr) out[r * wpr + w] = (uint64_t)lo | ((uint64_t)hi << 32);
+        }
+    }
+}
+
+// 16-bit source types, two elements per 32-bit load (row starts 4-byte
+// aligned): each lane yields 2 bits, a warp-wide OR-reduction builds the word.
+// Warp task = 512 elements = 8 output words.
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_pack_sign_pair16(const T* __restrict__ in, uint64_t* __restrict__ out,
+                   int64_t ld, int64_t wpr, int64_t cpr, int64_t tasks, int mode) {
+    static_assert(sizeof(T) == 2, "pair kernel is for 16-bit element types");
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t task = warp; task < tasks; task += nwarps) {
+        const int64_t r = task / cpr;
+        const int64_t c = task - r * cpr;
+        const T* rowp = in + r * ld;
+        const int64_t base = c * 512 + 2 * lane;
+        uint32_t raw[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t i = base + 64 * j;
+            raw[j] = 0xBF80BF80u;   // two negative values (-1.0 in bf16; negative in f16)
+            if (i + 1 < ld)  raw[j] = __ldcs(reinterpret_cast<const uint32_t*>(rowp + i));
+            else if (i < ld) raw[j] = (raw[j] & 0xFFFF0000u) |
+                                      (uint32_t)__ldcs(reinterpret_cast<const uint16_t*>(rowp + i));
+        }
+        uint64_t mine = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            T e0, e1;
+            const uint16_t u0 = (uint16_t)(raw[j] & 0xFFFFu), u1 = (uint16_t)(raw[j] >> 16);
+            e0 = *reinterpret_cast<const T*>(&u0);
+            e1 = *reinterpret_cast<const T*>(&u1);
+            const uint32_t two = (sign_bit(to_f32<T>(e0), mode) ? 1u : 0u) |
+                                 (sign_bit(to_f32<T>(e1), mode) ? 2u : 0u);
+            const uint32_t v = two << (2 * (lane & 15));
+            const uint32_t lo = __reduce_or_sync(0xffffffffu, lane < 16 ? v : 0u);
+            const uint32_t hi = __reduce_or_sync(0xffffffffu, lane >= 16 ? v : 0u);
+            if (lane == j) mine = (uint64_t)lo | ((uint64_t)hi << 32);
+        }
+        if (lane < 8) {
+            const int64_t w = c * 8 + lane;
+            if (w < wpr) out[r * wpr + w] = mine;
+        }
+    }
+}
+
+// ===========================================================================
+// unpack (bool bytes and +-1 floats)
+// ===========================================================================
+
+// 16 consecutive bits of row `rowp` starting at bit `col` (col >= 0 and the 16
+// bits lie inside the row's words).
+__device__ __forceinline__ uint32_t row_bits16(const uint64_t* rowp, int64_t col, int64_t wpr) {
+    const int64_t w = col >> 6;
+    const int sh = (int)(col & 63);
+    uint64_t x = __ldg(rowp + w) >> sh;
+    if (sh > 48 && w + 1 < wpr) x |= __ldg(rowp + w + 1) << (64 - sh);
+    return (uint32_t)x & 0xFFFFu;
+}
+
+// ELEM = bytes per output element (1: bool byte, 4: float +-1). A lane owns one
+// 16-byte ALIGNED group of the output, i.e. EPG = 16/ELEM elements.
+template <int ELEM>
+__global__ void __launch_bounds__(256)
+k_unpack(const uint64_t* __restrict__ in, uint8_t* __restrict__ out,
+         int64_t ll, int64_t wpr, int64_t cpr, int64_t tasks) {
+    constexpr int EPG = 16 / ELEM;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t task = warp; task < tasks; task += nwarps) {
+        const int64_t r = task / cpr;
+        const int64_t c = task - r * cpr;
+        const int64_t g = c * 32 + lane;
+        const uint64_t* rowp = in + r * wpr;
+        uint8_t* orow = out + r * ll * ELEM;
+        const int m = (int)(reinterpret_cast<uintptr_t>(orow) & 15u) / ELEM;   // elements
+        const int64_t col0 = g * EPG - m;            // first element of this lane's group
+        if (col0 >= ll || col0 + EPG <= 0) continue;
+        if (col0 >= 0 && col0 + EPG <= ll) {
+            const uint32_t bits = row_bits16(rowp, col0, wpr);
+            uint4 v;
+            if (ELEM == 1) {
+                v.x = bits4_to_bytes01(bits);       v.y = bits4_to_bytes01(bits >> 4);
+                v.z = bits4_to_bytes01(bits >> 8);  v.w = bits4_to_bytes01(bits >> 12);
+            } else {
+                // +1.0f = 0x3F800000, -1.0f = 0xBF800000: only the sign bit differs
+                v.x = 0xBF800000u ^ ((bits & 1u) << 31);        v.y = 0xBF800000u ^ ((bits & 2u) << 30);
+                v.z = 0xBF800000u ^ ((bits & 4u) << 29);        v.w = 0xBF800000u ^ ((bits & 8u) << 28);
+            }
+            stg_stream(orow + col0 * ELEM, v);
+        } else {
+            // ragged edge of a row: element-wise
+#pragma unroll
+            for (int i = 0; i < EPG; ++i) {
+                const int64_t col = col0 + i;
+                if (col < 0 || col >= ll) continue;
+                const uint32_t bit = (uint32_t)(__ldg(rowp + (col >> 6)) >> (col & 63)) & 1u;
+                if (ELEM == 1) orow[col] = (uint8_t)bit;
+                else reinterpret_cast<float*>(orow)[col] = bit ? 1.0f : -1.0f;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+static inline void flatten_rows(int64_t& rows, int64_t& len) {
+    // rows of a multiple of 64 bits pack back to back: treat as one long row
+    if (len % 64 == 0 || rows == 1) { len *= rows; rows = 1; }
+}
+
+}  // namespace bb
+
+using namespace bb;
+
+extern "C" int brute_b200_pack_bool(const uint8_t* in, uint64_t* out,
+                                    int64_t rows, int64_t ld, void* stream) {
+    BB_REQUIRE(rows >= 0 && ld >= 0, BRUTE_ERR_INVALID_ARG);
+    if (rows == 0 || ld == 0) return BRUTE_OK;
+    BB_REQUIRE(in != nullptr && out != nullptr, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(out), BRUTE_ERR_MISALIGNED);
+    flatten_rows(rows, ld);
+    const int64_t wpr = (ld + 63) / 64;
+    const int64_t cpr = (wpr + 7) / 8;      // 32 groups of 16 bytes = 8 words per warp task
+    const int64_t tasks = rows * cpr;
+    const int grid = stream_grid(tasks, 8, 8);
+    k_pack_bool<<<grid, 256, 0, as_stream(stream)>>>(in, out, rows, ld, wpr, cpr, tasks);
+    return launch_status();
+}
+
+template <typename T>
+static int launch_pack_sign(const T* in, uint64_t* out, int64_t rows, int64_t ld, int mode,
+                            cudaStream_t st) {
+    const int64_t wpr = (ld + 63) / 64;
+    const bool pair_ok = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0 &&
+                         (rows == 1 || (ld & 1) == 0);
+    if (pair_ok) {
+        const int64_t cpr = (wpr + 7) / 8, tasks = rows * cpr;
+        if constexpr (sizeof(T) == 2)
+            k_pack_sign_pair16<T><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(in, out, ld, wpr, cpr, tasks, mode);
+    } else {
+        const int64_t cpr = (wpr + 3) / 4, tasks = rows * cpr;
+        k_pack_sign_ballot<T><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(in, out, ld, wpr, cpr, tasks, mode);
+    }
+    return launch_status();
+}
+
+extern "C" int brute_b200_pack_sign(const void* in, int dtype, uint64_t* out,
+                                    int64_t rows, int64_t ld, int mode, void* stream) {
+    BB_REQUIRE(rows >= 0 && ld >= 0, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(mode == BRUTE_SIGN_GT0 || mode == BRUTE_SIGN_GE0, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(dtype == BRUTE_DT_F32 || dtype == BRUTE_DT_BF16 || dtype == BRUTE_DT_F16,
+               BRUTE_ERR_UNSUPPORTED);
+    if (rows == 0 || ld == 0) return BRUTE_OK;
+    BB_REQUIRE(in != nullptr && out != nullptr, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(out), BRUTE_ERR_MISALIGNED);
+    const uintptr_t esz = dtype == BRUTE_DT_F32 ? 4 : 2;
+    BB_REQUIRE((reinterpret_cast<uintptr_t>(in) & (esz - 1)) == 0, BRUTE_ERR_MISALIGNED);
+    flatten_rows(rows, ld);
+    cudaStream_t st = as_stream(stream);
+    switch (dtype) {
+        case BRUTE_DT_F32:  return launch_pack_sign(static_cast<const float*>(in), out, rows, ld, mode, st);
+        case BRUTE_DT_BF16: return launch_pack_sign(static_cast<const __nv_bfloat16*>(in), out, rows, ld, mode, st);
+        default:            return launch_pack_sign(static_cast<const __half*>(in), out, rows, ld, mode, st);
+    }
+}
+
+template <int ELEM>
+static int launch_unpack(const uint64_t* in, void* out, int64_t rows, int64_t ll, cudaStream_t st) {
+    const int64_t wpr = (ll + 63) / 64;     // words per packed row, from the UNflattened length
+    int64_t frows = rows, fll = ll;
+    int64_t fwpr = wpr;
+    if (ll % 64 == 0 || rows == 1) { fll = ll * rows; frows = 1; fwpr = wpr * rows; }
+    constexpr int EPG = 16 / ELEM;
+    // groups per row: the row may start up to EPG-1 elements into its first group
+    const int64_t gpr = (fll + 2 * EPG - 2) / EPG;
+    const int64_t cpr = (gpr + 31) / 32;
+    const int64_t tasks = frows * cpr;
+    k_unpack<ELEM><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(
+        in, static_cast<uint8_t*>(out), fll, fwpr, cpr, tasks);
+    return launch_status();
+}
+
+extern "C" int brute_b200_unpack_bool(const uint64_t* in, uint8_t* out,
+                                      int64_t rows, int64_t ll, void* stream) {
+    BB_REQUIRE(rows >= 0 && ll >= 0, BRUTE_ERR_INVALID_ARG);
+    if (rows == 0 || ll == 0) return BRUTE_OK;
+    BB_REQUIRE(in != nullptr && out != nullptr, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(in), BRUTE_ERR_MISALIGNED);
+    return launch_unpack<1>(in, out, rows, ll, as_stream(stream));
+}
+
+extern "C" int brute_b200_unpack_pm1_f32(const uint64_t* in, float* out,
+                                         int64_t rows, int64_t ll, void* stream) {
+    BB_REQUIRE(rows >= 0 && ll >= 0, BRUTE_ERR_INVALID_ARG);
+    if (rows == 0 || ll == 0) return BRUTE_OK;
+    BB_REQUIRE(in != nullptr && out != nullptr, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(in) && (reinterpret_cast<uintptr_t>(out) & 3u) == 0, BRUTE_ERR_MISALIGNED);
+    return launch_unpack<4>(in, out, rows, ll, as_stream(stream));
+}

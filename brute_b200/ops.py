@@ -1,0 +1,381 @@
+"""``torch.ops.brute.*`` — the reference's dispatcher namespace, bound to the sm_100a library.
+
+The eleven schemas are the reference's, verbatim (cbrute/ext.cpp:44-66), so any
+caller of ``torch.ops.brute.<op>`` keeps working. Each CUDA implementation does
+what the reference driver does on the host side (cbrute/cuda/ops_cuda.cu:
+validate, make contiguous, allocate the output on the input's device) and then
+calls the C ABI on the caller's current stream, inside a device guard (the
+reference installs none). Only the CUDA dispatch key is implemented: there is no
+CPU kernel and no fallback, an op on a CPU tensor fails in the dispatcher.
+
+Ops beyond the reference's eleven carry new names and never change the eleven:
+``pack_sign``, ``bitwise_packed``, ``select_packed``, ``row_any``, ``row_all``,
+``xnor_popcount_matmul_impl``, ``xnor_matmul_scale_sign_pack``,
+``binary_attention``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+
+_lib = L.load()
+
+_DEF = torch.library.Library("brute", "DEF")
+
+# -- the reference's schemas, verbatim (cbrute/ext.cpp:46-65) -----------------
+_DEF.define("pack_bool(Tensor input) -> Tensor")
+_DEF.define("unpack_bits(Tensor packed, int[] logical_shape) -> Tensor")
+_DEF.define("unpack_bool(Tensor packed, int[] logical_shape) -> Tensor")
+_DEF.define("xnor_popcount_matmul(Tensor A, Tensor B, int K) -> Tensor")
+_DEF.define("signed_bundle(Tensor W, Tensor V, int D) -> Tensor")
+_DEF.define("popcount(Tensor x) -> Tensor")
+_DEF.define("packed_popcount(Tensor x) -> Tensor")
+_DEF.define("hamming_distance(Tensor A, Tensor B) -> Tensor")
+_DEF.define("bit1_hamming_total(Tensor A, Tensor B) -> Tensor")
+_DEF.define("bit1_not_packed(Tensor A, int last_dim_bits) -> Tensor")
+_DEF.define("randomize_bits(Tensor(a!) out) -> Tensor(a!)")
+# -- additions ------------------------------------------------------------------
+_DEF.define("pack_sign(Tensor input, int mode) -> Tensor")
+_DEF.define("bitwise_packed(Tensor A, Tensor B, int op, int last_dim_bits) -> Tensor")
+_DEF.define("select_packed(Tensor cond, Tensor A, Tensor B) -> Tensor")
+_DEF.define("row_any(Tensor A) -> Tensor")
+_DEF.define("row_all(Tensor A, int last_dim_bits) -> Tensor")
+_DEF.define("xnor_popcount_matmul_impl(Tensor A, Tensor B, int K, int impl) -> Tensor")
+_DEF.define("xnor_matmul_scale_sign_pack(Tensor A, Tensor B, Tensor scale, int K, int mode) -> Tensor")
+_DEF.define("binary_attention(Tensor Qp, Tensor Kp, Tensor V, bool causal, float scale) -> Tensor")
+
+_PACK_WIDTH = 64
+_SIGN_DTYPES = {torch.float32: L.DT_F32, torch.bfloat16: L.DT_BF16, torch.float16: L.DT_F16}
+_POPCOUNT_BYTES = {torch.uint8: 1, torch.bool: 1, torch.int8: 1, torch.int16: 2,
+                   torch.int32: 4, torch.int64: 8}
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _words(n_bits: int) -> int:
+    return (n_bits + _PACK_WIDTH - 1) // _PACK_WIDTH
+
+
+# ---------------------------------------------------------------------------
+# pack / unpack
+# ---------------------------------------------------------------------------
+def pack_bool(input: torch.Tensor) -> torch.Tensor:
+    _check(input.dim() >= 1, "pack_bool: input must have >= 1 dim")
+    _check(input.dtype == torch.bool, "pack_bool: input must be torch.bool")
+    inp = input.contiguous()
+    ld = inp.size(-1)
+    shape = list(inp.shape)
+    shape[-1] = _words(ld)
+    # every word of the output is written by the kernel: no zero fill needed
+    out = torch.empty(shape, dtype=torch.int64, device=inp.device)
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(inp.device):
+        L.check(_lib.brute_b200_pack_bool(inp.data_ptr(), out.data_ptr(), inp.numel() // ld, ld,
+                                          _stream(inp)), "pack_bool")
+    return out
+
+
+def pack_sign(input: torch.Tensor, mode: int) -> torch.Tensor:
+    _check(input.dim() >= 1, "pack_sign: input must have >= 1 dim")
+    _check(input.dtype in _SIGN_DTYPES, "pack_sign: input must be float32, bfloat16 or float16")
+    inp = input.contiguous()
+    ld = inp.size(-1)
+    shape = list(inp.shape)
+    shape[-1] = _words(ld)
+    out = torch.empty(shape, dtype=torch.int64, device=inp.device)
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(inp.device):
+        L.check(_lib.brute_b200_pack_sign(inp.data_ptr(), _SIGN_DTYPES[inp.dtype], out.data_ptr(),
+                                          inp.numel() // ld, ld, int(mode), _stream(inp)), "pack_sign")
+    return out
+
+
+def _unpack_args(packed: torch.Tensor, logical_shape, name: str):
+    p = packed.contiguous()
+    shape = [int(s) for s in logical_shape]
+    _check(len(shape) >= 1, f"{name}: logical_shape must have >= 1 dim")
+    return p, shape, shape[-1]
+
+
+def _unpack_geometry_ok(p: torch.Tensor, shape, ll: int) -> bool:
+    rows = 1
+    for s in shape[:-1]:
+        rows *= s
+    return p.size(-1) == _words(ll) and p.numel() == rows * _words(ll)
+
+
+def unpack_bool(packed: torch.Tensor, logical_shape) -> torch.Tensor:
+    p, shape, ll = _unpack_args(packed, logical_shape, "unpack_bool")
+    out = torch.empty(shape, dtype=torch.bool, device=p.device)
+    if ll == 0 or p.numel() == 0:
+        return out
+    _check(p.dtype == torch.int64, "unpack_bool: packed must be torch.int64")
+    _check(_unpack_geometry_ok(p, shape, ll), "unpack_bool: packed shape does not match logical_shape")
+    with torch.cuda.device(p.device):
+        L.check(_lib.brute_b200_unpack_bool(p.data_ptr(), out.data_ptr(), p.numel() // p.size(-1), ll,
+                                            _stream(p)), "unpack_bool")
+    return out
+
+
+def unpack_bits(packed: torch.Tensor, logical_shape) -> torch.Tensor:
+    p, shape, ll = _unpack_args(packed, logical_shape, "unpack_bits")
+    out = torch.empty(shape, dtype=torch.float32, device=p.device)
+    if ll == 0 or p.numel() == 0:
+        return out
+    _check(p.dtype == torch.int64, "unpack_bits: packed must be torch.int64")
+    _check(_unpack_geometry_ok(p, shape, ll), "unpack_bits: packed shape does not match logical_shape")
+    with torch.cuda.device(p.device):
+        L.check(_lib.brute_b200_unpack_pm1_f32(p.data_ptr(), out.data_ptr(), p.numel() // p.size(-1), ll,
+                                               _stream(p)), "unpack_bits")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------
+def _gemm_args(A: torch.Tensor, B: torch.Tensor, K: int, name: str):
+    _check(A.dim() == 2 and B.dim() == 2, f"{name}: inputs must be 2-D")
+    _check(A.size(1) == B.size(1), f"{name}: packed K mismatch")
+    _check(A.dtype == torch.int64 and B.dtype == torch.int64, f"{name}: inputs must be int64 packed buffers")
+    _check(A.device == B.device, f"{name}: inputs must be on the same device")
+    _check(0 <= int(K) <= 64 * A.size(1), f"{name}: K out of range for the packed width")
+    return A.contiguous(), B.contiguous()
+
+
+def xnor_popcount_matmul_impl(A: torch.Tensor, B: torch.Tensor, K: int, impl: int) -> torch.Tensor:
+    Ac, Bc = _gemm_args(A, B, K, "xnor_popcount_matmul")
+    M, N, Kp = Ac.size(0), Bc.size(0), Ac.size(1)
+    C = torch.empty((M, N), dtype=torch.int32, device=Ac.device)
+    if M == 0 or N == 0:
+        return C
+    with torch.cuda.device(Ac.device):
+        L.check(_lib.brute_b200_xnor_gemm(Ac.data_ptr(), Bc.data_ptr(), C.data_ptr(), M, N, Kp, int(K), N,
+                                          int(impl), _stream(Ac)), "xnor_popcount_matmul")
+    return C
+
+
+def xnor_popcount_matmul(A: torch.Tensor, B: torch.Tensor, K: int) -> torch.Tensor:
+    return xnor_popcount_matmul_impl(A, B, K, L.GEMM_AUTO)
+
+
+def xnor_matmul_scale_sign_pack(A, B, scale, K: int, mode: int) -> torch.Tensor:
+    Ac, Bc = _gemm_args(A, B, K, "xnor_matmul_scale_sign_pack")
+    M, N, Kp = Ac.size(0), Bc.size(0), Ac.size(1)
+    _check(scale.dtype == torch.float32 and scale.numel() == N and scale.device == Ac.device,
+           "xnor_matmul_scale_sign_pack: scale must be float32 [N] on the inputs' device")
+    sc = scale.contiguous()
+    out = torch.empty((M, _words(N)), dtype=torch.int64, device=Ac.device)
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(Ac.device):
+        L.check(_lib.brute_b200_xnor_gemm_scale_sign_pack(
+            Ac.data_ptr(), Bc.data_ptr(), sc.data_ptr(), out.data_ptr(), M, N, Kp, int(K), int(mode),
+            L.GEMM_AUTO, _stream(Ac)), "xnor_matmul_scale_sign_pack")
+    return out
+
+
+def signed_bundle(W, V, D: int) -> torch.Tensor:
+    raise RuntimeError("signed_bundle: not built in brute_b200 (outside the bit1 GEMM/pack/popcount/attention path)")
+
+
+# ---------------------------------------------------------------------------
+# popcount / hamming
+# ---------------------------------------------------------------------------
+def popcount(x: torch.Tensor) -> torch.Tensor:
+    p = x.contiguous()
+    _check(p.dtype in _POPCOUNT_BYTES, f"popcount: unsupported dtype {p.dtype}")
+    out = torch.empty(p.shape, dtype=torch.int32, device=p.device)
+    if p.numel() == 0:
+        return out
+    with torch.cuda.device(p.device):
+        L.check(_lib.brute_b200_popcount_elems(p.data_ptr(), out.data_ptr(), p.numel(),
+                                               _POPCOUNT_BYTES[p.dtype], _stream(p)), "popcount")
+    return out
+
+
+def packed_popcount(x: torch.Tensor) -> torch.Tensor:
+    p = x.contiguous()
+    out = torch.empty((), dtype=torch.int64, device=p.device)      # zeroed by the call itself
+    with torch.cuda.device(p.device):
+        L.check(_lib.brute_b200_popcount_total(p.data_ptr() if p.numel() else None,
+                                               p.numel() * p.element_size(), out.data_ptr(), _stream(p)),
+                "packed_popcount")
+    return out
+
+
+def bit1_hamming_total(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    _check(A.shape == B.shape, "bit1_hamming_total: shape mismatch")
+    _check(A.dtype == B.dtype, "bit1_hamming_total: dtype mismatch")
+    Ac, Bc = A.contiguous(), B.contiguous()
+    out = torch.empty((), dtype=torch.int64, device=Ac.device)
+    with torch.cuda.device(Ac.device):
+        L.check(_lib.brute_b200_hamming_total(Ac.data_ptr() if Ac.numel() else None,
+                                              Bc.data_ptr() if Bc.numel() else None,
+                                              Ac.numel() * Ac.element_size(), out.data_ptr(), _stream(Ac)),
+                "bit1_hamming_total")
+    return out
+
+
+def hamming_distance(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    if A.shape == B.shape and A.dtype == torch.int64 and B.dtype == torch.int64:
+        Ac, Bc = A.contiguous(), B.contiguous()
+        out = torch.empty(Ac.shape, dtype=torch.int32, device=Ac.device)
+        if Ac.numel():
+            with torch.cuda.device(Ac.device):
+                L.check(_lib.brute_b200_hamming_words(Ac.data_ptr(), Bc.data_ptr(), out.data_ptr(),
+                                                      Ac.numel(), _stream(Ac)), "hamming_distance")
+        return out
+    return popcount(torch.bitwise_xor(A, B))       # broadcasting / other dtypes
+
+
+# ---------------------------------------------------------------------------
+# bitwise
+# ---------------------------------------------------------------------------
+def bit1_not_packed(A: torch.Tensor, last_dim_bits: int) -> torch.Tensor:
+    _check(A.dtype == torch.int64, "bit1_not_packed: input must be int64")
+    Ac = A.contiguous()
+    out = torch.empty_like(Ac)
+    if Ac.numel() == 0:
+        return out
+    wpr = Ac.size(-1) if Ac.dim() else 1
+    # the reference leaves the tail alone when last_dim_bits == 0 or a multiple of 64
+    with torch.cuda.device(Ac.device):
+        L.check(_lib.brute_b200_not_masked(Ac.data_ptr(), out.data_ptr(), Ac.numel() // wpr, wpr,
+                                           int(last_dim_bits), _stream(Ac)), "bit1_not_packed")
+    return out
+
+
+def bitwise_packed(A: torch.Tensor, B: torch.Tensor, op: int, last_dim_bits: int) -> torch.Tensor:
+    _check(A.shape == B.shape, "bitwise_packed: shape mismatch")
+    _check(A.dtype == torch.int64 and B.dtype == torch.int64, "bitwise_packed: inputs must be int64")
+    Ac, Bc = A.contiguous(), B.contiguous()
+    out = torch.empty_like(Ac)
+    if Ac.numel() == 0:
+        return out
+    wpr = Ac.size(-1) if Ac.dim() else 1
+    with torch.cuda.device(Ac.device):
+        L.check(_lib.brute_b200_bitwise(int(op), Ac.data_ptr(), Bc.data_ptr(), out.data_ptr(),
+                                        Ac.numel() // wpr, wpr, int(last_dim_bits), _stream(Ac)),
+                "bitwise_packed")
+    return out
+
+
+def select_packed(cond: torch.Tensor, A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    _check(cond.shape == A.shape == B.shape, "select_packed: shape mismatch")
+    c, a, b = cond.contiguous(), A.contiguous(), B.contiguous()
+    out = torch.empty_like(a)
+    if a.numel():
+        with torch.cuda.device(a.device):
+            L.check(_lib.brute_b200_select(c.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                           a.numel(), _stream(a)), "select_packed")
+    return out
+
+
+def row_any(A: torch.Tensor) -> torch.Tensor:
+    _check(A.dim() >= 1 and A.dtype == torch.int64, "row_any: input must be int64 with >= 1 dim")
+    Ac = A.contiguous()
+    out = torch.empty(Ac.shape[:-1], dtype=torch.bool, device=Ac.device)
+    if out.numel():
+        with torch.cuda.device(Ac.device):
+            L.check(_lib.brute_b200_row_any(Ac.data_ptr() if Ac.numel() else None, out.data_ptr(),
+                                            out.numel(), Ac.size(-1), _stream(Ac)), "row_any")
+    return out
+
+
+def row_all(A: torch.Tensor, last_dim_bits: int) -> torch.Tensor:
+    _check(A.dim() >= 1 and A.dtype == torch.int64, "row_all: input must be int64 with >= 1 dim")
+    Ac = A.contiguous()
+    out = torch.empty(Ac.shape[:-1], dtype=torch.bool, device=Ac.device)
+    if out.numel():
+        with torch.cuda.device(Ac.device):
+            L.check(_lib.brute_b200_row_all(Ac.data_ptr() if Ac.numel() else None, out.data_ptr(),
+                                            out.numel(), Ac.size(-1), int(last_dim_bits), _stream(Ac)),
+                    "row_all")
+    return out
+
+
+def randomize_bits(out: torch.Tensor) -> torch.Tensor:
+    out.random_()          # cbrute/cuda/ops_cuda.cu:340, a plain ATen call
+    return out
+
+
+# ---------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------
+def binary_attention(Qp: torch.Tensor, Kp: torch.Tensor, V: torch.Tensor, causal: bool, scale: float) -> torch.Tensor:
+    _check(V.dim() == 4 and Qp.dim() == 4 and Kp.dim() == 4, "binary_attention: Qp, Kp, V must be 4-D [B,H,S,*]")
+    B, H, S, D = V.shape
+    _check(V.dtype == torch.bfloat16, "binary_attention: V must be bfloat16")
+    _check(Qp.dtype == torch.int64 and Kp.dtype == torch.int64, "binary_attention: Qp, Kp must be int64 packed")
+    _check(D in (64, 128), "binary_attention: head dim must be 64 or 128")
+    _check(tuple(Qp.shape) == (B, H, S, D // 64) and tuple(Kp.shape) == (B, H, S, D // 64),
+           "binary_attention: packed Q/K shape must be [B,H,S,D/64]")
+    q, k, v = Qp.contiguous(), Kp.contiguous(), V.contiguous()
+    out = torch.empty_like(v)
+    if out.numel():
+        with torch.cuda.device(v.device):
+            L.check(_lib.brute_b200_binary_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                                         B, H, S, D, int(bool(causal)), float(scale), _stream(v)),
+                    "binary_attention")
+    return out
+
+
+_CUDA_IMPLS = {
+    "pack_bool": pack_bool, "unpack_bits": unpack_bits, "unpack_bool": unpack_bool,
+    "xnor_popcount_matmul": xnor_popcount_matmul, "signed_bundle": signed_bundle,
+    "popcount": popcount, "packed_popcount": packed_popcount, "hamming_distance": hamming_distance,
+    "bit1_hamming_total": bit1_hamming_total, "bit1_not_packed": bit1_not_packed,
+    "randomize_bits": randomize_bits,
+    "pack_sign": pack_sign, "bitwise_packed": bitwise_packed, "select_packed": select_packed,
+    "row_any": row_any, "row_all": row_all, "xnor_popcount_matmul_impl": xnor_popcount_matmul_impl,
+    "xnor_matmul_scale_sign_pack": xnor_matmul_scale_sign_pack, "binary_attention": binary_attention,
+}
+_IMPL = torch.library.Library("brute", "IMPL", "CUDA")
+for _name, _fn in _CUDA_IMPLS.items():
+    _IMPL.impl(_name, _fn)
+
+
+# Shape-only kernels so that FakeTensor / torch.compile tracing sees the ops
+# (the reference registers none and graph-breaks).
+def _register_fakes() -> None:
+    reg = torch.library.register_fake
+
+    def packed_like(x):
+        s = list(x.shape)
+        s[-1] = _words(s[-1])
+        return x.new_empty(s, dtype=torch.int64)
+
+    reg("brute::pack_bool")(lambda input: packed_like(input))
+    reg("brute::pack_sign")(lambda input, mode: packed_like(input))
+    reg("brute::unpack_bool")(lambda packed, logical_shape: packed.new_empty(list(logical_shape), dtype=torch.bool))
+    reg("brute::unpack_bits")(lambda packed, logical_shape: packed.new_empty(list(logical_shape), dtype=torch.float32))
+    reg("brute::xnor_popcount_matmul")(lambda A, B, K: A.new_empty((A.shape[0], B.shape[0]), dtype=torch.int32))
+    reg("brute::xnor_popcount_matmul_impl")(lambda A, B, K, impl: A.new_empty((A.shape[0], B.shape[0]), dtype=torch.int32))
+    reg("brute::xnor_matmul_scale_sign_pack")(
+        lambda A, B, scale, K, mode: A.new_empty((A.shape[0], _words(B.shape[0])), dtype=torch.int64))
+    reg("brute::popcount")(lambda x: x.new_empty(x.shape, dtype=torch.int32))
+    reg("brute::packed_popcount")(lambda x: x.new_empty((), dtype=torch.int64))
+    reg("brute::bit1_hamming_total")(lambda A, B: A.new_empty((), dtype=torch.int64))
+    reg("brute::hamming_distance")(lambda A, B: torch.empty_like(torch.bitwise_xor(A, B), dtype=torch.int32))
+    reg("brute::bit1_not_packed")(lambda A, last_dim_bits: torch.empty_like(A))
+    reg("brute::bitwise_packed")(lambda A, B, op, last_dim_bits: torch.empty_like(A))
+    reg("brute::select_packed")(lambda cond, A, B: torch.empty_like(A))
+    reg("brute::row_any")(lambda A: A.new_empty(A.shape[:-1], dtype=torch.bool))
+    reg("brute::row_all")(lambda A, last_dim_bits: A.new_empty(A.shape[:-1], dtype=torch.bool))
+    reg("brute::binary_attention")(lambda Qp, Kp, V, causal, scale: torch.empty_like(V))
+
+
+try:
+    _register_fakes()
+except Exception:       # older torch without register_fake: tracing support is optional
+    pass

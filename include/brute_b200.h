@@ -1,0 +1,197 @@
+/*
+ * brute_b200 — C ABI of the B200 (sm_100a) kernels behind the `brute.bit1` ops.
+ *
+ * Every entry point is a stateless launcher: it validates its arguments,
+ * enqueues work on `stream` of the CURRENT device and returns immediately.
+ * It never throws, never synchronises, never allocates device memory (scratch
+ * is passed in by the caller) and never traps the GPU. The return value is
+ * BRUTE_OK (0) or a negative BRUTE_ERR_* code; brute_b200_strerror() names it.
+ *
+ * Conventions shared by all entry points
+ *   - bit1 data is packed 64 logical bits per uint64 word along the LAST
+ *     dimension, LSB first, little endian; a row of `ld` bits occupies
+ *     ceil(ld/64) words and its pad bits are always 0.
+ *   - bit value 1 means +1, bit value 0 means -1.
+ *   - all pointers are DEVICE pointers unless stated otherwise; `stream` is a
+ *     cudaStream_t passed as void* so that this header stays plain C.
+ *
+ * Each declaration cites the reference (TheoCoombes/Brute) interface it
+ * replaces as file:line within that project.
+ */
+#ifndef BRUTE_B200_H_
+#define BRUTE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define BRUTE_OK                 0
+#define BRUTE_ERR_INVALID_ARG   -1   /* null pointer, negative size, bad enum     */
+#define BRUTE_ERR_MISALIGNED    -2   /* pointer / pitch alignment rule violated   */
+#define BRUTE_ERR_UNSUPPORTED   -3   /* shape or dtype outside what is built      */
+#define BRUTE_ERR_LAUNCH        -4   /* cudaGetLastError() after launch != 0      */
+#define BRUTE_ERR_WORKSPACE     -5   /* scratch buffer missing or too small       */
+#define BRUTE_ERR_DEVICE_WAIT   -6   /* a bounded in-kernel wait gave up          */
+#define BRUTE_ERR_DRIVER        -7   /* a CUDA driver entry point was unavailable */
+
+/* ---- enums ------------------------------------------------------------- */
+/* float -> bit threshold convention. The reference front end uses x > 0 for
+ * `.to(bit1)` (brute/tensor.py:163-169) and x >= 0 for `randn(dtype=bit1)`
+ * (brute/functional.py:131-133). NaN maps to 0 under both. */
+#define BRUTE_SIGN_GT0  0
+#define BRUTE_SIGN_GE0  1
+
+/* source dtype of brute_b200_pack_sign */
+#define BRUTE_DT_F32   0
+#define BRUTE_DT_BF16  1
+#define BRUTE_DT_F16   2
+
+/* word-wise binary ops of brute_b200_bitwise */
+#define BRUTE_OP_AND     0
+#define BRUTE_OP_OR      1
+#define BRUTE_OP_XOR     2
+#define BRUTE_OP_XNOR    3   /* pad bits of each row's last word forced to 0 */
+#define BRUTE_OP_ANDNOT  4   /* a & ~b                                       */
+
+/* GEMM instruction path; AUTO picks the fastest one that accepts the shape */
+#define BRUTE_GEMM_AUTO     0
+#define BRUTE_GEMM_POPC     1   /* CUDA-core __popcll, register blocked, any shape */
+#define BRUTE_GEMM_MMA_B1   2   /* legacy mma.sync m16n8k256 .b1 and.popc          */
+#define BRUTE_GEMM_TCGEN05  3   /* tcgen05.mma kind::i8 on in-kernel expanded bits  */
+
+/* ---- library ----------------------------------------------------------- */
+const char* brute_b200_strerror(int code);
+/* Bit mask of BRUTE_CAP_*; host only, no GPU needed. */
+#define BRUTE_CAP_SM100A        1u
+#define BRUTE_CAP_GEMM_POPC     2u
+#define BRUTE_CAP_GEMM_MMA_B1   4u
+#define BRUTE_CAP_GEMM_TCGEN05  8u
+#define BRUTE_CAP_ATTENTION    16u
+uint32_t brute_b200_query_caps(void);
+/* Reads (device -> host, synchronising the device) and clears the device-side
+ * status word that bounded in-kernel waits write when they give up. Returns
+ * BRUTE_OK or BRUTE_ERR_DEVICE_WAIT. Meant for tests and diagnostics, not for
+ * the per-call path. */
+int brute_b200_device_status(void);
+
+/* ---- pack / unpack ----------------------------------------------------- */
+/* bool bytes [rows, ld] -> packed words [rows, ceil(ld/64)]; any nonzero byte
+ * is 1; every output word is written in full (pad bits 0), so the output needs
+ * no prior memset.
+ * Replaces cbrute::cuda::pack_bool, cbrute/cuda/ops_cuda.cu:54-90 and
+ * k_pack_bool_warp/_persistent, cbrute/cuda/kernels/packing.cuh:26-72. */
+int brute_b200_pack_bool(const uint8_t* in, uint64_t* out,
+                         int64_t rows, int64_t ld, void* stream);
+
+/* float [rows, ld] -> packed words, bit = (x > 0) or (x >= 0) per `mode`,
+ * in one pass (no 1-byte-per-element temporary).
+ * Replaces the two-kernel path `_to_bool` + pack_bool, brute/tensor.py:163-177
+ * and brute/functional.py:131-133. */
+int brute_b200_pack_sign(const void* in, int dtype, uint64_t* out,
+                         int64_t rows, int64_t ld, int mode, void* stream);
+
+/* packed words [rows, ceil(ll/64)] -> bool bytes [rows, ll] (0/1).
+ * Replaces cbrute::cuda::unpack_bool, cbrute/cuda/ops_cuda.cu:112-137 and
+ * k_unpack_bool_warp/_persistent, cbrute/cuda/kernels/packing.cuh:76-94,116-143. */
+int brute_b200_unpack_bool(const uint64_t* in, uint8_t* out,
+                           int64_t rows, int64_t ll, void* stream);
+
+/* packed words -> float32 (+1.0f for bit 1, -1.0f for bit 0); no limit on rows.
+ * Replaces cbrute::cuda::unpack_bits, cbrute/cuda/ops_cuda.cu:93-109 and
+ * k_unpack_pm1_warp, cbrute/cuda/kernels/packing.cuh:96-114. */
+int brute_b200_unpack_pm1_f32(const uint64_t* in, float* out,
+                              int64_t rows, int64_t ll, void* stream);
+
+/* ---- popcount / hamming ------------------------------------------------ */
+/* per-element popcount of n elements of elem_bytes in {1,2,4,8} -> int32.
+ * Replaces cbrute::cuda::popcount, cbrute/cuda/ops_cuda.cu:244-280 and
+ * k_popcnt_u8/u16/u32/u64, cbrute/cuda/kernels/popcount.cuh:22-41. */
+int brute_b200_popcount_elems(const void* in, int32_t* out,
+                              int64_t n, int elem_bytes, void* stream);
+
+/* total popcount of n_bytes bytes -> *out (uint64, zeroed by the call itself).
+ * Replaces cbrute::cuda::packed_popcount, cbrute/cuda/ops_cuda.cu:283-304 and
+ * k_packed_popcount_total/k_popcount_tail_byte, cbrute/cuda/kernels/popcount.cuh:75-98,129-136. */
+int brute_b200_popcount_total(const void* in, int64_t n_bytes,
+                              uint64_t* out, void* stream);
+
+/* total popcount(a ^ b) over n_bytes bytes -> *out, no XOR temporary.
+ * Replaces cbrute::cuda::bit1_hamming_total, cbrute/cuda/ops_cuda.cu:312-338 and
+ * k_hamming_total/k_hamming_tail_byte, cbrute/cuda/kernels/popcount.cuh:101-124,138-149. */
+int brute_b200_hamming_total(const void* a, const void* b, int64_t n_bytes,
+                             uint64_t* out, void* stream);
+
+/* per-word popcount(a ^ b) for equal-shape word buffers -> int32, fused
+ * (the reference materialises the XOR first).
+ * Replaces cbrute::cuda::hamming_distance, cbrute/cuda/ops_cuda.cu:307-309. */
+int brute_b200_hamming_words(const uint64_t* a, const uint64_t* b, int32_t* out,
+                             int64_t n_words, void* stream);
+
+/* ---- bitwise ----------------------------------------------------------- */
+/* out = a OP b over [rows, words_per_row]; `last_dim_bits` is only read by
+ * XNOR, which clears each row's pad bits. out may alias a or b.
+ * Replaces the ATen int64 bitwise launches of brute/tensor.py:564-598,1494-1537
+ * and brute/fast.py:37-83 (eq = xor + bit1_not_packed fused into one XNOR). */
+int brute_b200_bitwise(int op, const uint64_t* a, const uint64_t* b, uint64_t* out,
+                       int64_t rows, int64_t words_per_row, int64_t last_dim_bits,
+                       void* stream);
+
+/* out = ~a with the pad bits of each row's last word kept 0.
+ * Replaces bit1_not_packed_composite, cbrute/ext.cpp:27-39 (3 ATen launches). */
+int brute_b200_not_masked(const uint64_t* a, uint64_t* out,
+                          int64_t rows, int64_t words_per_row, int64_t last_dim_bits,
+                          void* stream);
+
+/* out = (cond & a) | (~cond & b), word-wise select.
+ * Replaces the 4-launch packed `where` of brute/tensor.py:1863-1883. */
+int brute_b200_select(const uint64_t* cond, const uint64_t* a, const uint64_t* b,
+                      uint64_t* out, int64_t n_words, void* stream);
+
+/* out[r] = 1 if any bit of row r is set / if all `last_dim_bits` bits are set.
+ * Replaces the ATen compositions of brute/tensor.py:1415-1431. */
+int brute_b200_row_any(const uint64_t* a, uint8_t* out, int64_t rows,
+                       int64_t words_per_row, void* stream);
+int brute_b200_row_all(const uint64_t* a, uint8_t* out, int64_t rows,
+                       int64_t words_per_row, int64_t last_dim_bits, void* stream);
+
+/* ---- xnor-popcount GEMM ------------------------------------------------ */
+/* A [M, Kp] words, B [N, Kp] words (rows of B are output features), K logical
+ * bits (K <= 64*Kp, pad bits 0) -> C [M, N] int32 with row pitch ldc elements,
+ * C[m,n] = K - 2 * sum_k popcount(A[m,k] ^ B[n,k])  (the +-1 dot product).
+ * `impl` is a BRUTE_GEMM_* value. M, N or Kp equal to 0 are legal.
+ * Replaces cbrute::cuda::xnor_popcount_matmul, cbrute/cuda/ops_cuda.cu:144-221,
+ * CutlassB1XorGemm + KMinusTwoH, cbrute/cuda/kernels/matmul_cutlass.cuh:36-105 and
+ * k_xnor_popcount_matmul, cbrute/cuda/kernels/matmul_fallback.cuh:20-59. */
+int brute_b200_xnor_gemm(const uint64_t* A, const uint64_t* B, int32_t* C,
+                         int64_t M, int64_t N, int64_t Kp, int64_t K, int64_t ldc,
+                         int impl, void* stream);
+
+/* Same contraction with the binarised-MLP epilogue fused: the int32 count is
+ * scaled by scale[n] (fp32), thresholded per `mode` and re-packed, so
+ * out [M, ceil(N/64)] words holds bit(m,n) = sign(scale[n] * C[m,n]).
+ * Replaces the composition xnor_popcount_matmul -> float scale -> `_to_bool` ->
+ * pack_bool (cbrute/cuda/ops_cuda.cu:144-221, brute/tensor.py:163-177). */
+int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B,
+                                         const float* scale, uint64_t* out,
+                                         int64_t M, int64_t N, int64_t Kp, int64_t K,
+                                         int mode, int impl, void* stream);
+
+/* ---- binary attention -------------------------------------------------- */
+/* Qp, Kp_ [B, H, S, D/64] words (sign-binarised Q and K), V and O bf16
+ * [B, H, S, D]; score(i,j) = (D - 2*popcount(q_i ^ k_j)) * scale, optional
+ * causal mask (j <= i), softmax in fp32, O = P @ V in bf16. D must be 64 or 128.
+ * The reference has no such kernel (one docstring mention, brute/fast.py:122-124);
+ * it replaces the composition of xnor_popcount_matmul
+ * (cbrute/cuda/ops_cuda.cu:144-221) per (b,h) with torch softmax and matmul. */
+int brute_b200_binary_attention_fwd(const uint64_t* Qp, const uint64_t* Kp_,
+                                    const void* V, void* O,
+                                    int64_t B, int64_t H, int64_t S, int64_t D,
+                                    int causal, float scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRUTE_B200_H_ */

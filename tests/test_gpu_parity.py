@@ -1,0 +1,380 @@
+"""GPU parity: every kernel, called through torch.ops.brute.* -> ctypes -> the C ABI,
+against the CPU oracle on the same seeded inputs (bit-exact for integer work),
+against the committed golden fixtures, and through size-independent properties
+at the full BASELINE sizes."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops(lib_built):
+    import brute_b200  # noqa: F401
+    return torch.ops.brute
+
+
+@pytest.fixture(scope="module")
+def co():
+    from oracle import c_oracle
+    return c_oracle
+
+
+def u64(t: torch.Tensor) -> np.ndarray:
+    return t.cpu().numpy().view(np.uint64)
+
+
+def gen(seed):
+    return torch.Generator(device="cpu").manual_seed(seed)
+
+
+# ---------------------------------------------------------------------------
+# pack / unpack
+# ---------------------------------------------------------------------------
+TAIL_SHAPES = [(n,) for n in list(range(1, 131)) + [191, 192, 193, 255, 256, 257, 1003, 4096, 4097]]
+ND_SHAPES = [(3, 13), (13,), (4, 64), (7, 130), (2, 3, 65), (33, 1003), (5, 4097), (256, 4097),
+             (1, 1), (1, 65536), (65537,), (17, 16), (1000, 7), (9, 48), (6, 80)]
+
+
+@pytest.mark.parametrize("shape", TAIL_SHAPES[::3] + ND_SHAPES)
+def test_pack_unpack_bool(ops, co, shape):
+    x = torch.rand(shape, generator=gen(sum(shape))) < 0.3
+    p = ops.pack_bool(x.to(DEV))
+    assert p.dtype == torch.int64 and tuple(p.shape) == shape[:-1] + ((shape[-1] + 63) // 64,)
+    assert np.array_equal(u64(p), co.pack_bool(x.numpy()))
+    assert torch.equal(ops.unpack_bool(p, list(shape)).cpu(), x)
+    assert np.array_equal(ops.unpack_bits(p, list(shape)).cpu().numpy(), co.unpack_pm1(u64(p), shape))
+    assert int(ops.packed_popcount(p)) == int(x.sum())
+
+
+def test_pack_bool_any_nonzero_byte_is_one(ops, co):
+    raw = torch.randint(0, 256, (37, 201), generator=gen(1), dtype=torch.uint8)
+    raw[raw < 128] = 0
+    x = raw.view(torch.bool)
+    assert np.array_equal(u64(ops.pack_bool(x.to(DEV))), co.pack_bool(raw.numpy()))
+
+
+def test_pack_bool_unaligned_base(ops, co):
+    # a view that starts 1..15 bytes into an allocation: rows and base both unaligned
+    big = torch.rand((70000,), generator=gen(2)) < 0.5
+    d = big.to(DEV)
+    for off in (1, 3, 8, 15):
+        for n in (64 * 100, 4097, 999):
+            v = d[off:off + n]
+            assert v.data_ptr() % 16 != 0 or off % 16 == 0
+            got = ops.pack_bool(v)      # .contiguous() is a no-op on a 1-D slice: the offset survives
+            assert np.array_equal(u64(got), co.pack_bool(big[off:off + n].numpy()))
+            assert torch.equal(ops.unpack_bool(got, [n]).cpu(), big[off:off + n])
+
+
+def test_pack_empty_and_ragged(ops):
+    assert tuple(ops.pack_bool(torch.zeros((3, 0), dtype=torch.bool, device=DEV)).shape) == (3, 0)
+    assert tuple(ops.pack_bool(torch.zeros((0, 7), dtype=torch.bool, device=DEV)).shape) == (0, 1)
+    assert tuple(ops.unpack_bool(torch.zeros((0, 1), dtype=torch.int64, device=DEV), [0, 7]).shape) == (0, 7)
+    with pytest.raises(RuntimeError, match="must be torch.bool"):
+        ops.pack_bool(torch.zeros(4, device=DEV))
+    with pytest.raises(RuntimeError, match=">= 1 dim"):
+        ops.pack_bool(torch.zeros((), dtype=torch.bool, device=DEV))
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("shape", [(1,), (63,), (64,), (65,), (9, 131), (3, 256), (5, 4097), (1 << 16,), (31, 1003)])
+def test_pack_sign_f32(ops, co, mode, shape):
+    x = torch.randn(shape, generator=gen(mode + sum(shape)))
+    flat = x.view(-1)
+    flat[: min(5, flat.numel())] = torch.tensor([0.0, -0.0, float("nan"), float("inf"), -float("inf")])[: min(5, flat.numel())]
+    assert np.array_equal(u64(ops.pack_sign(x.to(DEV), mode)), co.pack_sign_f32(x.numpy(), mode))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1,), (65,), (9, 131), (9, 130), (4, 512), (1 << 15,), (3, 1003)])
+def test_pack_sign_16bit(ops, co, dtype, shape):
+    x = torch.randn(shape, generator=gen(sum(shape))).to(dtype)
+    x.view(-1)[0] = 0.0
+    for mode in (0, 1):
+        assert np.array_equal(u64(ops.pack_sign(x.to(DEV), mode)), co.pack_sign_f32(x.float().numpy(), mode))
+
+
+def test_known_answers(ops, golden):
+    x = torch.from_numpy(golden["ka_float_in"]).to(DEV)
+    got = ops.unpack_bool(ops.pack_sign(x, 0), [4]).cpu().numpy()
+    assert np.array_equal(got, golden["ka_float_bits_gt0"])
+    bits = torch.from_numpy(golden["ka_pm1_bits"]).to(DEV)
+    assert np.array_equal(ops.unpack_bits(ops.pack_bool(bits), [5]).cpu().numpy(), golden["ka_pm1_out"])
+
+
+# ---------------------------------------------------------------------------
+# popcount / bitwise
+# ---------------------------------------------------------------------------
+def test_popcount_golden(ops, golden):
+    for idx in range(int(golden["pop_count"])):
+        packed = torch.from_numpy(golden[f"pop{idx}_packed"]).to(DEV)
+        assert np.array_equal(ops.popcount(packed).cpu().numpy(), golden[f"pop{idx}_words"])
+        assert int(ops.packed_popcount(packed)) == int(golden[f"pop{idx}_total"])
+    assert np.array_equal(ops.popcount(torch.from_numpy(golden["pop_u8_in"]).to(DEV)).cpu().numpy(), golden["pop_u8_out"])
+    assert np.array_equal(ops.popcount(torch.from_numpy(golden["pop_i32_in"]).to(DEV)).cpu().numpy(), golden["pop_i32_out"])
+
+
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.int8, torch.int16, torch.int32, torch.int64, torch.bool])
+@pytest.mark.parametrize("n", [1, 15, 16, 17, 1000, 65537])
+def test_popcount_elems_dtypes(ops, co, dtype, n):
+    if dtype == torch.bool:
+        x = torch.rand(n, generator=gen(n)) < 0.5
+    else:
+        info = torch.iinfo(dtype)
+        x = torch.randint(info.min, info.max, (n,), generator=gen(n), dtype=torch.int64).to(dtype)
+    got = ops.popcount(x.to(DEV))
+    assert got.dtype == torch.int32
+    assert np.array_equal(got.cpu().numpy(), co.popcount_elems(x.numpy()))
+    # a view that is not 16-byte aligned takes the element-wise path
+    if n > 3:
+        assert np.array_equal(ops.popcount(x.to(DEV)[1:]).cpu().numpy(), co.popcount_elems(x[1:].numpy()))
+    with pytest.raises(RuntimeError, match="unsupported dtype"):
+        ops.popcount(torch.zeros(4, device=DEV))
+
+
+@pytest.mark.parametrize("n_words", [0, 1, 2, 3, 255, 256, 257, 100003, 1 << 20])
+def test_totals(ops, co, n_words):
+    a = torch.randint(-2 ** 63, 2 ** 63 - 1, (n_words,), generator=gen(n_words), dtype=torch.int64)
+    b = torch.randint(-2 ** 63, 2 ** 63 - 1, (n_words,), generator=gen(n_words + 1), dtype=torch.int64)
+    da, db = a.to(DEV), b.to(DEV)
+    assert int(ops.packed_popcount(da)) == co.popcount_total(a.numpy())
+    assert int(ops.bit1_hamming_total(da, db)) == co.hamming_total(a.numpy(), b.numpy())
+    assert np.array_equal(ops.hamming_distance(da, db).cpu().numpy(), co.hamming_words(a.numpy(), b.numpy()))
+    if n_words > 4:   # misaligned views, equal and different misalignment
+        assert int(ops.packed_popcount(da[1:])) == co.popcount_total(a[1:].numpy())
+        assert int(ops.bit1_hamming_total(da[1:], db[1:])) == co.hamming_total(a[1:].numpy(), b[1:].numpy())
+        assert int(ops.bit1_hamming_total(da[1:-1], db[2:])) == co.hamming_total(a[1:-1].numpy(), b[2:].numpy())
+    # byte-typed buffers with a tail that is not a whole word
+    if n_words > 2:
+        u = a.view(torch.uint8)[: n_words * 8 - 3].contiguous()
+        assert int(ops.packed_popcount(u.to(DEV))) == co.popcount_total(u.numpy())
+    with pytest.raises(RuntimeError, match="shape mismatch"):
+        ops.bit1_hamming_total(da, torch.zeros(n_words + 1, dtype=torch.int64, device=DEV))
+
+
+@pytest.mark.parametrize("shape", [(1,), (7,), (64,), (65,), (3, 13), (4, 64), (7, 130), (33, 1003), (4096, 4097 // 8),
+                                   (1000, 7), (2, 3, 65)])
+def test_bitwise_family(ops, co, shape):
+    n = shape[-1]
+    x = torch.rand(shape, generator=gen(n)) < 0.3
+    y = torch.rand(shape, generator=gen(n + 1)) < 0.5
+    c = torch.rand(shape, generator=gen(n + 2)) < 0.5
+    px, py, pc = ops.pack_bool(x.to(DEV)), ops.pack_bool(y.to(DEV)), ops.pack_bool(c.to(DEV))
+    for code, name in enumerate(["and", "or", "xor", "xnor", "andnot"]):
+        got = ops.bitwise_packed(px, py, code, n)
+        assert np.array_equal(u64(got), co.bitwise(name, u64(px), u64(py), n)), name
+    inv = ops.bit1_not_packed(px, n)
+    assert np.array_equal(u64(inv), co.bitwise("not", u64(px), None, n))
+    assert int(ops.packed_popcount(inv)) == x.numel() - int(x.sum())
+    assert np.array_equal(u64(ops.select_packed(pc, px, py)), co.select(u64(pc), u64(px), u64(py)))
+    assert np.array_equal(ops.row_any(px).cpu().numpy(), x.any(dim=-1).numpy())
+    assert np.array_equal(ops.row_all(px, n).cpu().numpy(), x.all(dim=-1).numpy())
+    ones = ops.bitwise_packed(px, inv, 1, n)
+    assert bool(ops.row_all(ones, n).all())
+
+
+def test_not_pad_safe_sizes(ops, golden):
+    for n in golden["ka_not_sizes"]:
+        n = int(n)
+        src = torch.rand(n, generator=gen(n)) < 0.5
+        p = ops.pack_bool(src.to(DEV))
+        inv = ops.bit1_not_packed(p, n)
+        assert int(ops.packed_popcount(inv)) == n - int(src.sum())
+        assert torch.equal(ops.unpack_bool(inv, [n]).cpu(), ~src)
+
+
+# ---------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------
+def impls():
+    from brute_b200 import _lib as L
+    return {"auto": L.GEMM_AUTO, "popc": L.GEMM_POPC, "mma_b1": L.GEMM_MMA_B1, "tcgen05": L.GEMM_TCGEN05}
+
+
+def status_ok():
+    from brute_b200 import _lib as L
+    return L.load().brute_b200_device_status() == 0
+
+
+def test_gemm_golden(ops, golden):
+    for idx, (M, K, N) in enumerate(golden["gemm_cases"]):
+        ap = torch.from_numpy(golden[f"gemm{idx}_ap"]).to(DEV)
+        bp = torch.from_numpy(golden[f"gemm{idx}_bp"]).to(DEV)
+        for name, impl in impls().items():
+            Kp = ap.shape[1]
+            if name in ("mma_b1", "tcgen05") and Kp % 2:
+                with pytest.raises(RuntimeError):
+                    ops.xnor_popcount_matmul_impl(ap, bp, int(K), impl)
+                continue
+            got = ops.xnor_popcount_matmul_impl(ap, bp, int(K), impl)
+            assert got.dtype == torch.int32
+            assert np.array_equal(got.cpu().numpy(), golden[f"gemm{idx}_c"]), (name, M, K, N)
+    assert status_ok()
+
+
+GEMM_SHAPES = [(1, 128, 1), (5, 128, 7), (128, 128, 256), (130, 256, 258), (127, 1024, 255), (256, 2048, 512),
+               (300, 640, 700), (64, 8192, 64), (1, 4096, 1000), (513, 384, 129)]
+
+
+@pytest.mark.parametrize("impl_name", ["popc", "mma_b1", "tcgen05", "auto"])
+@pytest.mark.parametrize("M,K,N", GEMM_SHAPES)
+def test_gemm_vs_oracle(ops, co, impl_name, M, K, N):
+    a = torch.randint(0, 2, (M, K), generator=gen(M + K)).bool()
+    b = torch.randint(0, 2, (N, K), generator=gen(N + K + 1)).bool()
+    ap, bp = ops.pack_bool(a.to(DEV)), ops.pack_bool(b.to(DEV))
+    want = co.xnor_gemm(u64(ap), u64(bp), K)
+    got = ops.xnor_popcount_matmul_impl(ap, bp, K, impls()[impl_name]).cpu().numpy()
+    assert np.array_equal(got, want)
+    assert status_ok()
+
+
+@pytest.mark.parametrize("M,K,N", [(3, 13, 5), (9, 100, 12), (33, 257, 66), (8, 65, 8), (32, 1, 32), (40, 777, 50)])
+def test_gemm_k_not_multiple_of_64(ops, co, M, K, N):
+    # K tails, as the reference fuzzes them (tests/fuzz/test_fuzz_matmul.py:15-34); odd word
+    # counts are only accepted by the CUDA-core path, which AUTO then picks
+    a = torch.randint(0, 2, (M, K), generator=gen(K)).bool()
+    b = torch.randint(0, 2, (N, K), generator=gen(K + 1)).bool()
+    ap, bp = ops.pack_bool(a.to(DEV)), ops.pack_bool(b.to(DEV))
+    got = ops.xnor_popcount_matmul(ap, bp, K).cpu().numpy()
+    ref = (a.float() * 2 - 1) @ (b.float() * 2 - 1).t()
+    assert np.array_equal(got, ref.numpy().astype(np.int32))
+    assert np.array_equal(got, co.xnor_gemm(u64(ap), u64(bp), K))
+
+
+def test_gemm_errors_and_empty(ops):
+    a = torch.zeros((4, 2), dtype=torch.int64, device=DEV)
+    with pytest.raises(RuntimeError, match="must be 2-D"):
+        ops.xnor_popcount_matmul(a[0], a, 128)
+    with pytest.raises(RuntimeError, match="packed K mismatch"):
+        ops.xnor_popcount_matmul(a, torch.zeros((4, 3), dtype=torch.int64, device=DEV), 128)
+    assert tuple(ops.xnor_popcount_matmul(a[:0], a, 128).shape) == (0, 4)
+    assert tuple(ops.xnor_popcount_matmul(a, a[:0], 128).shape) == (4, 0)
+    z = ops.xnor_popcount_matmul(torch.zeros((3, 0), dtype=torch.int64, device=DEV),
+                                 torch.zeros((5, 0), dtype=torch.int64, device=DEV), 0)
+    assert tuple(z.shape) == (3, 5) and int(z.abs().sum()) == 0
+
+
+def test_gemm_config1_all_paths(ops, co):
+    # BASELINE config 1: 1024 x 1024 x 4096, Bernoulli(0.5) bits
+    a = torch.randint(-2 ** 63, 2 ** 63 - 1, (1024, 64), generator=gen(1234), dtype=torch.int64)
+    b = torch.randint(-2 ** 63, 2 ** 63 - 1, (1024, 64), generator=gen(1235), dtype=torch.int64)
+    want = co.xnor_gemm(a.numpy(), b.numpy(), 4096)
+    for name, impl in impls().items():
+        got = ops.xnor_popcount_matmul_impl(a.to(DEV), b.to(DEV), 4096, impl).cpu().numpy()
+        assert np.array_equal(got, want), name
+    assert status_ok()
+
+
+def test_gemm_large_properties(ops):
+    # BASELINE config 3 scale (16384^3 is checked by structure, not against the CPU):
+    #  * the tensor-core path equals the CUDA-core path bit for bit on a 4096-row slab,
+    #  * a row of A against itself gives K on the diagonal, and -K against its complement.
+    K = 16384
+    Kp = K // 64
+    g = gen(3)
+    a = torch.randint(-2 ** 63, 2 ** 63 - 1, (16384, Kp), generator=g, dtype=torch.int64).to(DEV)
+    b = torch.randint(-2 ** 63, 2 ** 63 - 1, (16384, Kp), generator=g, dtype=torch.int64).to(DEV)
+    c = ops.xnor_popcount_matmul(a, b, K)
+    assert tuple(c.shape) == (16384, 16384)
+    slab = ops.xnor_popcount_matmul_impl(a[:512], b[:4096], K, impls()["popc"])
+    assert torch.equal(c[:512, :4096], slab)
+    # linearity in the hamming domain: C(a, b) + C(a, ~b) == 0
+    c2 = ops.xnor_popcount_matmul(a[:1024], torch.bitwise_not(b[:2048]), K)
+    assert int((c[:1024, :2048] + c2).abs().max()) == 0
+    d = ops.xnor_popcount_matmul(a[:2048], a[:2048], K)
+    assert bool((d.diagonal() == K).all()) and bool((d == d.t()).all())
+    assert int(c.abs().max()) <= K and int((c & 1).sum()) == 0
+    assert status_ok()
+
+
+@pytest.mark.parametrize("impl_name", ["popc", "mma_b1", "tcgen05"])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_mlp_layer(ops, co, impl_name, mode):
+    from brute_b200 import _lib as L
+    M, K, N = 200, 512, 330
+    a = torch.randint(0, 2, (M, K), generator=gen(1)).bool()
+    w = torch.randint(0, 2, (N, K), generator=gen(2)).bool()
+    scale = torch.rand(N, generator=gen(3)) + 0.5
+    ap, wp = ops.pack_bool(a.to(DEV)), ops.pack_bool(w.to(DEV))
+    want = co.xnor_gemm_scale_sign_pack(u64(ap), u64(wp), scale.numpy(), K, mode)
+    out = torch.empty((M, (N + 63) // 64), dtype=torch.int64, device=DEV)
+    rc = L.load().brute_b200_xnor_gemm_scale_sign_pack(
+        ap.data_ptr(), wp.data_ptr(), scale.to(DEV).data_ptr(), out.data_ptr(), M, N, K // 64, K, mode,
+        impls()[impl_name], torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert np.array_equal(u64(out), want)
+    assert np.array_equal(u64(ops.xnor_matmul_scale_sign_pack(ap, wp, scale.to(DEV), K, mode)), want)
+
+
+def test_mlp_config4_chain(ops, co):
+    # BASELINE config 4 at reduced batch against the oracle: 4096 -> 16384 -> 4096
+    import brute_b200 as brute
+    g = gen(4)
+    x = torch.randn((256, 4096), generator=g)
+    w1 = torch.randn((16384, 4096), generator=g)
+    w2 = torch.randn((4096, 16384), generator=g)
+    s1 = torch.rand(16384, generator=g) + 0.5
+    s2 = torch.rand(4096, generator=g) + 0.5
+    xb, w1b, w2b = (brute.pack_sign(t.to(DEV), ge0=True) for t in (x, w1, w2))
+    h = brute.binary_linear(xb, w1b, s1.to(DEV))
+    y = brute.binary_linear(h, w2b, s2.to(DEV))
+    xp, w1p, w2p = (co.pack_sign_f32(t.numpy(), 1) for t in (x, w1, w2))
+    hp = co.xnor_gemm_scale_sign_pack(xp, w1p, s1.numpy(), 4096, 1)
+    yp = co.xnor_gemm_scale_sign_pack(hp, w2p, s2.numpy(), 16384, 1)
+    assert np.array_equal(u64(h._packed_buf), hp)
+    assert np.array_equal(u64(y._packed_buf), yp)
+
+
+# ---------------------------------------------------------------------------
+# attention (parity unpinned: no reference kernel; oracle = composition)
+# ---------------------------------------------------------------------------
+ATT_TOL = 2e-2      # relative to the largest |output|, the tolerance the task states for bf16
+
+
+@pytest.mark.parametrize("B,H,S,D,causal", [(1, 2, 256, 128, True), (1, 1, 200, 128, True), (2, 2, 128, 64, True),
+                                            (1, 2, 333, 128, False), (1, 1, 64, 64, False), (1, 1, 1, 128, True),
+                                            (1, 3, 1000, 128, True)])
+def test_attention_vs_oracle(ops, co, B, H, S, D, causal):
+    import brute_b200 as brute
+    g = gen(S + D)
+    q = torch.randn((B, H, S, D), generator=g)
+    k = torch.randn((B, H, S, D), generator=g)
+    v = torch.randn((B, H, S, D), generator=g).to(torch.bfloat16)
+    qb, kb = brute.pack_sign(q.to(DEV), ge0=True), brute.pack_sign(k.to(DEV), ge0=True)
+    out = brute.binary_attention(qb, kb, v.to(DEV), causal=causal)
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (B, H, S, D)
+    want = co.binary_attention(co.pack_sign_f32(q.numpy(), 1), co.pack_sign_f32(k.numpy(), 1),
+                               v.float().numpy(), causal, D ** -0.5)
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= ATT_TOL * max(np.abs(want).max(), 1e-6)
+
+
+def test_attention_first_row_is_v0(ops):
+    # causal: query 0 sees only key 0, so the output row is exactly V[0]
+    import brute_b200 as brute
+    g = gen(5)
+    q = torch.randn((2, 4, 512, 128), generator=g)
+    k = torch.randn((2, 4, 512, 128), generator=g)
+    v = torch.randn((2, 4, 512, 128), generator=g).to(torch.bfloat16).to(DEV)
+    out = brute.binary_attention(brute.pack_sign(q.to(DEV)), brute.pack_sign(k.to(DEV)), v, causal=True)
+    assert torch.equal(out[:, :, 0], v[:, :, 0])
+
+
+def test_attention_config5_properties(ops):
+    # BASELINE config 5 shape on one (b) slice of the full head count: constant V rows
+    # must come back unchanged (softmax weights sum to 1), whatever the scores are.
+    import brute_b200 as brute
+    g = gen(6)
+    B, H, S, D = 1, 32, 4096, 128
+    q = torch.randn((B, H, S, D), generator=g)
+    k = torch.randn((B, H, S, D), generator=g)
+    row = torch.randn((B, H, 1, D), generator=g).to(torch.bfloat16)
+    v = row.expand(B, H, S, D).contiguous().to(DEV)
+    out = brute.binary_attention(brute.pack_sign(q.to(DEV), ge0=True), brute.pack_sign(k.to(DEV), ge0=True), v, causal=True)
+    err = (out.float() - v.float()).abs().max() / v.float().abs().max()
+    assert float(err) < ATT_TOL
