@@ -47,6 +47,11 @@ def parse_args():
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--size", type=int, default=16384, help="M=N=K (profiling runs use smaller sizes)")
+    ap.add_argument("--op", default="gemm",
+                    help="time ONE op alone (for profiler captures): gemm | pack_sign | pack_bool | unpack_bool | "
+                         "unpack_pm1 | popcount_total | hamming_total | word_popcount | xor | not | attention | mlp")
+    ap.add_argument("--log2-bits", type=int, default=28, help="size of the bandwidth ops under --op")
+    ap.add_argument("--att", default="2,8,4096,128", help="B,H,S,D of --op attention")
     return ap.parse_args()
 
 
@@ -300,7 +305,7 @@ def run_ours(args):
     if world > 1:
         # optional all-gather of the C blocks (NCCL), timed apart from the GEMM
         c_loc = holder["C"]
-        gathered = torch.empty((world, m, n_loc), dtype=torch.int32, device=dev)
+        gathered = torch.empty((world * m, n_loc), dtype=torch.int32, device=dev)
         g_times = time_steps(lambda: dist.all_gather_into_tensor(gathered, c_loc), 3, 1, lambda: None, sync)
         tg = torch.tensor([sum(g_times) / 3], dtype=torch.float64, device=dev)
         dist.all_reduce(tg, op=dist.ReduceOp.MAX)
@@ -415,10 +420,66 @@ def secondary_workloads(dev, peaks, flush, sync):
     return out
 
 
+def run_single_op(args):
+    """One op alone, a few launches, one JSON line: the command that profiler captures use."""
+    import torch
+    import brute_b200 as brute
+    ops = torch.ops.brute
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    n = 1 << args.log2_bits
+    g = torch.Generator(device=dev).manual_seed(1235)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    alg = None
+    if args.op in ("pack_sign",):
+        x = torch.randn(n, generator=g, device=dev)
+        fn, alg = (lambda: ops.pack_sign(x, 1)), 4 * n + n // 8
+    elif args.op == "attention":
+        Bq, H, S, D = (int(v) for v in args.att.split(","))
+        qb = brute.pack_sign(torch.randn((Bq, H, S, D), generator=g, device=dev), ge0=True)
+        kb = brute.pack_sign(torch.randn((Bq, H, S, D), generator=g, device=dev), ge0=True)
+        v = torch.randn((Bq, H, S, D), generator=g, device=dev).to(torch.bfloat16)
+        fn, alg = (lambda: brute.binary_attention(qb, kb, v, causal=True)), 2 * Bq * H * S * (D // 4) + 2 * Bq * H * S * D * 2
+    elif args.op == "mlp":
+        xs = brute.pack_sign(torch.randn((8192, 4096), generator=g, device=dev), ge0=True)
+        w1 = brute.pack_sign(torch.randn((16384, 4096), generator=g, device=dev), ge0=True)
+        w2 = brute.pack_sign(torch.randn((4096, 16384), generator=g, device=dev), ge0=True)
+        s1 = torch.rand(16384, generator=g, device=dev) + 0.5
+        s2 = torch.rand(4096, generator=g, device=dev) + 0.5
+        fn = lambda: brute.binary_linear(brute.binary_linear(xs, w1, s1), w2, s2)
+    else:
+        p = torch.randint(-2 ** 63, 2 ** 63 - 1, (n // 64,), generator=g, dtype=torch.int64, device=dev)
+        q = torch.randint(-2 ** 63, 2 ** 63 - 1, (n // 64,), generator=g, dtype=torch.int64, device=dev)
+        table = {
+            "unpack_bool": (lambda: ops.unpack_bool(p, [n]), n // 8 + n),
+            "unpack_pm1": (lambda: ops.unpack_bits(p, [n]), n // 8 + 4 * n),
+            "popcount_total": (lambda: ops.packed_popcount(p), n // 8),
+            "hamming_total": (lambda: ops.bit1_hamming_total(p, q), 2 * n // 8),
+            "word_popcount": (lambda: ops.popcount(p), n // 8 + n // 16),
+            "xor": (lambda: ops.bitwise_packed(p, q, 2, n), 3 * n // 8),
+            "not": (lambda: ops.bit1_not_packed(p, n), 2 * n // 8),
+        }
+        if args.op == "pack_bool":
+            xb = ops.unpack_bool(p, [n])
+            fn, alg = (lambda: ops.pack_bool(xb)), n + n // 8
+        else:
+            fn, alg = table[args.op]
+    ts = time_steps(fn, args.steps, args.warmup, flush_buf.zero_, torch.cuda.synchronize)
+    ms = statistics.median(ts)
+    line = {"op": args.op, "ms": ms, "steps": args.steps, "log2_bits": args.log2_bits}
+    if alg is not None:
+        line.update({"algorithmic_bytes": alg, "GB/s": alg / (ms * 1e-3) / 1e9,
+                     "frac_of_hbm": alg / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.op != "gemm":
+        run_single_op(args)
     else:
         run_ours(args)
 

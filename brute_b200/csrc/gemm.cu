@@ -79,7 +79,13 @@ static int env_impl() {
 }
 
 static int dispatch(const GemmArgs& g, int impl, cudaStream_t st) {
-    if (impl == BRUTE_GEMM_AUTO) impl = env_impl();
+    if (impl == BRUTE_GEMM_AUTO) {
+        // the environment override applies only where that path accepts the shape
+        const int e = env_impl();
+        if (e == BRUTE_GEMM_POPC) impl = e;
+        else if (e == BRUTE_GEMM_MMA_B1 && mma_b1_accepts(g)) impl = e;
+        else if (e == BRUTE_GEMM_TCGEN05 && tc5_accepts(g.A, g.B, g.M, g.N, g.Kp)) impl = e;
+    }
     if (impl == BRUTE_GEMM_AUTO) {
         // Small problems do not fill the tensor-core tiles; the CUDA-core path
         // has no shape rules at all.

@@ -71,9 +71,10 @@ def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group
         return c_local
     M = a_packed.shape[0]
     if N % world == 0:
-        stacked = torch.empty((world, M, N // world), dtype=c_local.dtype, device=c_local.device)
+        # rank blocks arrive stacked along dim 0: [world * M, N / world]
+        stacked = torch.empty((world * M, N // world), dtype=c_local.dtype, device=c_local.device)
         dist.all_gather_into_tensor(stacked, c_local.contiguous(), group=group)
-        return stacked.permute(1, 0, 2).reshape(M, N)
+        return stacked.view(world, M, N // world).permute(1, 0, 2).reshape(M, N)
     parts = [torch.empty((M, shard_bounds(N, world, r)[1] - shard_bounds(N, world, r)[0]),
                          dtype=c_local.dtype, device=c_local.device) for r in range(world)]
     dist.all_gather(parts, c_local.contiguous(), group=group)

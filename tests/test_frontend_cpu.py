@@ -1,0 +1,275 @@
+"""Host-side logic of the front end on CPU tensors.
+
+The product has CUDA kernels only; here the CPU dispatch key of torch.ops.brute.*
+is bound to the oracle (tests/conftest.py) so that the subclass state machine --
+lazy bool storage, version-tracked re-pack, packed-domain fast paths, the t()
+source for matmul -- can be exercised without a GPU. The checker is torch.bool
+itself, as in the reference's op catalog (tests/ops_catalog.py): run the same
+function on a bool tensor and on the bit1 tensor and compare.
+"""
+import copy
+import io
+import pickle
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.usefixtures("cpu_ops")
+
+
+@pytest.fixture(scope="module")
+def brute(cpu_ops):
+    import brute_b200
+    return brute_b200
+
+
+def b1(brute, t):
+    return brute.Tensor(t, dtype=brute.bit1)
+
+
+def as_bool(x):
+    if hasattr(x, "_ensure_bool_valid"):
+        x._ensure_bool_valid()
+        return x.as_subclass(torch.Tensor)
+    return x
+
+
+def rnd(shape, seed=0, p=0.5):
+    return torch.rand(shape, generator=torch.Generator().manual_seed(seed)) < p
+
+
+SHAPES = [(16,), (4, 8), (3, 13), (13,), (2, 3, 65), (5, 64), (2, 128)]
+
+
+def test_dtype_sentinel(brute):
+    assert repr(brute.bit1) == "brute.bit1" and str(brute.bit1) == "bit1"
+    assert brute.bit1 == type(brute.bit1)() and hash(brute.bit1) == hash(type(brute.bit1)())
+    x = b1(brute, rnd((4, 8)))
+    assert x.dtype == brute.bit1 and x.type() == "brute.Bit1Tensor"
+    with pytest.raises(TypeError):
+        x.element_size()
+    with pytest.raises(TypeError):
+        x.itemsize
+    assert x.nbytes == 4 * 8          # 4 rows x 1 word
+
+
+def test_float_threshold_known_answer(brute):
+    # reference tests/unit/test_dtype.py:79-83: [-1, 0, 0.5, 1] -> [F, F, T, T]
+    x = brute.tensor([-1.0, 0.0, 0.5, 1.0], dtype=torch.float32).to(brute.bit1)
+    assert torch.equal(as_bool(x), torch.tensor([False, False, True, True]))
+    y = brute.tensor([0, 1, 0, 1, 1], dtype=torch.int32).to(brute.bit1)
+    assert torch.equal(as_bool(y), torch.tensor([False, True, False, True, True]))
+
+
+def test_unpack_pm1_known_answer(brute):
+    a = brute.tensor([True, False, True, True, False], dtype=brute.bit1)
+    assert torch.equal(a.unpack_pm1(), torch.tensor([1.0, -1.0, 1.0, 1.0, -1.0]))
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_roundtrip_and_reductions(brute, shape):
+    src = rnd(shape, 1)
+    x = b1(brute, src)
+    assert torch.equal(as_bool(x.bool()), src)
+    assert int(x.popcount()) == int(src.sum()) == int(x.sum()) == int(torch.count_nonzero(x))
+    assert int(x.word_popcount().as_subclass(torch.Tensor).long().sum()) == int(src.sum())
+    assert bool(torch.any(x)) == bool(src.any()) and bool(torch.all(x)) == bool(src.all())
+    assert torch.equal(as_bool(torch.any(x, dim=-1)), src.any(dim=-1))
+    assert torch.equal(as_bool(torch.all(x, -1)), src.all(dim=-1))
+    if len(shape) >= 2:
+        assert torch.equal(as_bool(x.any(dim=0)), src.any(dim=0))
+        assert torch.equal(as_bool(x.all(dim=0, keepdim=True)), src.all(dim=0, keepdim=True))
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_bitwise_parity_with_bool(brute, shape):
+    sa, sb, sc = rnd(shape, 2), rnd(shape, 3), rnd(shape, 4)
+    a, b, c = b1(brute, sa), b1(brute, sb), b1(brute, sc)
+    cases = {
+        "and": (a & b, sa & sb), "or": (a | b, sa | sb), "xor": (a ^ b, sa ^ sb), "not": (~a, ~sa),
+        "f_and": (torch.bitwise_and(a, b), sa & sb), "l_or": (torch.logical_or(a, b), sa | sb),
+        "l_xor": (a.logical_xor(b), sa ^ sb), "l_not": (torch.logical_not(a), ~sa),
+        "eq": (a == b, sa == sb), "ne": (torch.ne(a, b), sa != sb),
+        "where": (torch.where(c, a, b), torch.where(sc, sa, sb)),
+        "fast_eq": (brute.eq(a, b), sa == sb), "fast_xor": (brute.bitwise_xor(a, b), sa ^ sb),
+        "fast_not": (brute.bitwise_not(a), ~sa),
+    }
+    for name, (got, want) in cases.items():
+        assert got.dtype == brute.bit1, name
+        assert got.__dict__.get("_bool_dirty") is True, f"{name}: packed-domain result should be lazy"
+        assert torch.equal(as_bool(got), want), name
+        assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
+    assert int(a.hamming(b)) == int((sa ^ sb).sum()) == int(brute.hamming(a, b))
+    assert torch.equal(a, a.clone()) and (not torch.equal(a, ~a) or a.numel() == 0)
+
+
+def test_invert_pad_safe_sizes(brute):
+    for n in [1, 7, 8, 9, 31, 32, 33, 63, 64, 65, 1003, 4096]:
+        src = rnd((n,), n)
+        inv = ~b1(brute, src)
+        assert int(inv.popcount()) == n - int(src.sum())
+        assert torch.equal(as_bool(inv), ~src)
+
+
+def test_inplace_ops_touch_only_packed(brute):
+    sa, sb = rnd((3, 70), 5), rnd((3, 70), 6)
+    a, b = b1(brute, sa), b1(brute, sb)
+    a &= b
+    assert a.__dict__["_bool_dirty"] is True
+    assert torch.equal(as_bool(a), sa & sb)
+    a |= b
+    a ^= b
+    assert torch.equal(as_bool(a), ((sa & sb) | sb) ^ sb)
+
+
+def test_version_counter_repacks_after_bool_write(brute):
+    src = rnd((4, 70), 7)
+    x = b1(brute, src.clone())
+    before = x._packed_buf.clone()
+    x.as_subclass(torch.Tensor)[1, 3] = not bool(src[1, 3])        # write through the bool storage
+    after = x._packed_buf
+    assert not torch.equal(before, after)
+    src2 = src.clone()
+    src2[1, 3] = not bool(src[1, 3])
+    assert int(x.popcount()) == int(src2.sum())
+    x.fill_(True)
+    assert int(x.popcount()) == x.numel() and bool(as_bool(x).all())
+    x.zero_()
+    assert int(x.popcount()) == 0
+
+
+def test_lazy_bool_materialises_once(brute):
+    a, b = b1(brute, rnd((5, 65), 8)), b1(brute, rnd((5, 65), 9))
+    c = a ^ b
+    assert c.__dict__["_bool_dirty"] is True
+    _ = c.shape, c.dim(), c.device                       # metadata never unpacks
+    assert c.__dict__["_bool_dirty"] is True
+    _ = c + 0                                             # a generic op does
+    assert c.__dict__["_bool_dirty"] is False
+    assert torch.equal(as_bool(c), as_bool(a) ^ as_bool(b))
+
+
+@pytest.mark.parametrize("shape", [(4, 64), (3, 13), (2, 3, 128), (2, 5, 7)])
+def test_view_ops_parity(brute, shape):
+    src = rnd(shape, 10)
+    x = b1(brute, src)
+    fns = [
+        lambda t: t.reshape(-1), lambda t: t.flatten(), lambda t: t.ravel(), lambda t: t.clone(),
+        lambda t: t.unsqueeze(0), lambda t: t.unsqueeze(-1), lambda t: t.unsqueeze(0).squeeze(0),
+        lambda t: t.transpose(0, -1), lambda t: t.transpose(0, 0), lambda t: t.detach(),
+        lambda t: t.permute(*reversed(range(t.dim()))), lambda t: t.contiguous(),
+        lambda t: t.movedim(0, -1), lambda t: torch.flip(t, [0]), lambda t: t[0], lambda t: t[1:],
+        lambda t: t.view(t.shape), lambda t: t.repeat(*([2] + [1] * (t.dim() - 1))),
+        lambda t: torch.index_select(t, 0, torch.tensor([1, 0, 1])),
+        lambda t: t.repeat_interleave(2, dim=0),
+    ]
+    if len(shape) >= 3:
+        fns += [lambda t: t.transpose(0, 1), lambda t: t.permute(1, 0, 2), lambda t: torch.swapaxes(t, 0, 1),
+                lambda t: torch.movedim(t, 0, 1), lambda t: torch.fliplr(t), lambda t: torch.flipud(t)]
+    for i, fn in enumerate(fns):
+        got, want = fn(x), fn(src)
+        assert got.dtype == brute.bit1, i
+        assert tuple(got.shape) == tuple(want.shape), i
+        assert torch.equal(as_bool(got), want), i
+        assert int(got.popcount()) == int(want.sum()), i
+
+
+def test_setitem_fast_paths(brute):
+    src = rnd((6, 70), 11)
+    x = b1(brute, src.clone())
+    ref = src.clone()
+    x[2] = True; ref[2] = True
+    x[4:6] = False; ref[4:6] = False
+    x[:, 69] = True; ref[:, 69] = True
+    x[..., 3] = False; ref[..., 3] = False
+    x[0, 5] = True; ref[0, 5] = True                      # generic path
+    assert torch.equal(as_bool(x), ref) and int(x.popcount()) == int(ref.sum())
+    with pytest.raises(IndexError):
+        x[:, 70] = True
+
+
+def test_matmul_paths(brute):
+    M, K, N = 5, 130, 7
+    sa, sb = rnd((M, K), 12), rnd((N, K), 13)
+    a, b = b1(brute, sa), b1(brute, sb)
+    want = ((sa.float() * 2 - 1) @ (sb.float() * 2 - 1).t()).to(torch.int32)
+    assert torch.equal(a @ b, want)                        # B stored (N, K)
+    assert torch.equal(a @ b.t(), want)                    # via _t_source
+    assert torch.equal(torch.matmul(a, b.t()), want)
+    assert torch.equal(torch.mm(a, b.transpose(0, 1)), want)
+    assert torch.equal(brute.matmul(a, b), want)
+    assert torch.equal(brute.matmul_packed(a._packed_buf, b._packed_buf, K), want)
+    assert (a @ b).dtype == torch.int32 and not isinstance(a @ b, brute.Tensor)
+
+
+def test_factories(brute):
+    for size in [(5,), (3, 70), (2, 64)]:
+        z, o = brute.zeros(*size, dtype=brute.bit1), brute.ones(size, dtype=brute.bit1)
+        assert int(z.popcount()) == 0 and int(o.popcount()) == int(np.prod(size))
+        assert bool(as_bool(o).all()) and not bool(as_bool(z).any())
+        e = brute.empty(*size, dtype=brute.bit1)
+        assert int(e.popcount()) <= int(np.prod(size))
+        f = brute.full(size, 1, dtype=brute.bit1)
+        assert int(f.popcount()) == int(np.prod(size))
+    g = torch.Generator().manual_seed(3)
+    r = brute.randn(4, 100, dtype=brute.bit1, generator=g)
+    ref = torch.randn(4, 100, generator=torch.Generator().manual_seed(3)) >= 0
+    assert torch.equal(as_bool(r), ref)
+    ri = brute.randint(0, 2, (128,), dtype=brute.bit1)
+    assert ri.dtype == brute.bit1 and 0 <= int(ri.popcount()) <= 128
+    assert brute.zeros_like(r).dtype == brute.bit1 and brute.ones_like(r, dtype=torch.float32).dtype == torch.float32
+    assert isinstance(brute.arange(5), brute.Tensor) and brute.nn is None and brute.optim is None
+
+
+def test_randomize_keeps_pad_bits_zero(brute):
+    a = brute.zeros(3, 1003, dtype=brute.bit1)
+    a.randomize_()
+    assert 0 < int(a.popcount()) < 3 * 1003
+    assert int(a.popcount()) == int(as_bool(a.bool()).sum())
+
+
+def test_type_errors(brute):
+    a = brute.zeros(8, dtype=brute.bit1)
+    plain = torch.zeros(8, dtype=torch.bool).as_subclass(brute.Tensor)
+    with pytest.raises(TypeError):
+        a.hamming(torch.zeros(8, dtype=torch.bool))
+    with pytest.raises(ValueError):
+        a.hamming(brute.zeros(16, dtype=brute.bit1))
+    for fn in (lambda: plain.word_popcount(), lambda: plain.randomize_(), lambda: plain.unpack_pm1()):
+        with pytest.raises(TypeError):
+            fn()
+    assert int(brute.Tensor(torch.ones(4, dtype=torch.bool)).popcount()) == 4
+
+
+def test_mixed_bool_does_not_promote(brute):
+    sa, sb = rnd((4, 9), 14), rnd((4, 9), 15)
+    out = torch.logical_and(b1(brute, sa), sb)
+    assert out.dtype == torch.bool and torch.equal(out.as_subclass(torch.Tensor), sa & sb)
+    picked = b1(brute, sa)[sb]                           # mask indexing keeps bit1
+    assert picked.dtype == brute.bit1
+    assert int(torch.argmax(b1(brute, sa).flatten())) == int(torch.argmax(sa.flatten().to(torch.uint8)))
+
+
+def test_pickle_deepcopy_numpy_repr(brute):
+    src = rnd((3, 70), 16)
+    x = b1(brute, src) ^ b1(brute, torch.zeros_like(src))          # a lazy one
+    y = pickle.loads(pickle.dumps(x))
+    assert y.dtype == brute.bit1 and torch.equal(as_bool(y), src)
+    buf = io.BytesIO()
+    torch.save(x, buf)
+    buf.seek(0)
+    z = torch.load(buf, weights_only=False)
+    assert torch.equal(as_bool(z), src)
+    d = copy.deepcopy(x)
+    assert d.dtype == brute.bit1 and torch.equal(as_bool(d), src) and int(d.popcount()) == int(src.sum())
+    assert np.array_equal(np.asarray(x), src.numpy())
+    assert "brute.Tensor(" in repr(x) and "dtype=brute.bit1" in repr(x)
+
+
+def test_empty_and_zero_dim(brute):
+    for shape in [(0,), (3, 0), (0, 5)]:
+        x = b1(brute, torch.zeros(shape, dtype=torch.bool))
+        assert tuple(x.shape) == shape and int(x.popcount()) == 0
+    s = brute.Tensor(torch.tensor(True), dtype=brute.bit1)
+    assert s.dim() == 0 and int(s.popcount()) == 1 and bool(as_bool(~s)) is False

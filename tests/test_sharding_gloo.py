@@ -1,0 +1,60 @@
+"""The multi-rank layout of the column-sharded GEMM on two CPU ranks (gloo).
+
+Checks the partition of B's rows, the local GEMM per rank and the layout of the
+optional all-gather against the unsharded result. The CPU ranks use the oracle
+for the local contraction (see tests/conftest.py); the collective and the layout
+logic are the product's (brute_b200/kernels.py)."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _worker(rank, world, port, n_rows, result_dir):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import conftest
+    conftest.install_oracle_cpu_ops()
+    from brute_b200.kernels import shard_bounds, sharded_matmul
+    g = torch.Generator().manual_seed(1234)                 # same operands on every rank
+    K = 200
+    a = torch.randint(0, 2, (9, K), generator=g).bool()
+    b = torch.randint(0, 2, (n_rows, K), generator=g).bool()
+    ap, bp = torch.ops.brute.pack_bool(a), torch.ops.brute.pack_bool(b)
+    full = torch.ops.brute.xnor_popcount_matmul(ap, bp, K)
+    lo, hi = shard_bounds(n_rows, world, rank)
+    local = sharded_matmul(ap, bp, K, gather=False)
+    assert torch.equal(local, full[:, lo:hi])
+    gathered = sharded_matmul(ap, bp, K, gather=True)
+    assert torch.equal(gathered, full)
+    np.save(os.path.join(result_dir, f"ok{rank}.npy"), np.array([lo, hi]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n_rows", [16, 13])
+def test_two_rank_sharded_gemm(tmp_path, lib_built, n_rows):
+    port = 29500 + (os.getpid() % 1000) + n_rows
+    mp.spawn(_worker, args=(2, port, n_rows, str(tmp_path)), nprocs=2, join=True)
+    spans = [np.load(tmp_path / f"ok{r}.npy") for r in range(2)]
+    assert spans[0][0] == 0 and spans[0][1] == spans[1][0] and spans[1][1] == n_rows
+
+
+def test_shard_bounds_cover_everything():
+    from brute_b200.kernels import shard_bounds
+    for n in (0, 1, 7, 16, 16384):
+        for w in (1, 2, 4, 8):
+            spans = [shard_bounds(n, w, r) for r in range(w)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(w - 1))
+            assert max(h - l for l, h in spans) - min(h - l for l, h in spans) <= 1
