@@ -41,6 +41,18 @@ inline int stream_grid(int64_t work_items, int items_per_block, int blocks_per_s
 // ---- device helpers ------------------------------------------------------
 #ifdef __CUDACC__
 
+// Grid of a persistent grid-stride kernel: exactly the blocks that are resident
+// at once (SMs x occupancy), so there is no second, partial wave.
+template <class Kernel>
+inline int resident_grid(Kernel kernel, int block_threads, int64_t blocks_needed) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block_threads, 0) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+    const int64_t cap = (int64_t)kNumSMs * per_sm;
+    if (blocks_needed < 1) blocks_needed = 1;
+    return (int)(blocks_needed < cap ? blocks_needed : cap);
+}
+
 // 128-bit streaming load that does not allocate in L1.
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;

@@ -1,11 +1,13 @@
 // xnor-popcount GEMM on the 5th-generation tensor cores (tcgen05.mma kind::i8).
 //
 // sm_100a has no binary tcgen05 kind, so the bits are expanded to int8 ON CHIP:
-// bit 1 -> -1 (0xFF), bit 0 -> +1 (0x01) for both operands, which leaves every
-// product unchanged ((-a)(-b) = ab), so the int32 accumulator holds the +-1 dot
-// product over the padded K and C = acc - (64*Kp - K). Only PACKED operands
-// ever cross HBM/L2 (8x less operand traffic than an int8 GEMM), the expansion
-// is paid per CTA in shared memory.
+// bit 1 -> -64 (0xC0), bit 0 -> +64 (0x40) for both operands. The two codes
+// differ in bit 7 only, so a byte costs one shift (shared by four bytes) and
+// one three-input logic op; the sign flip is the same on both sides and leaves
+// every product's sign unchanged, so the int32 accumulator holds 4096 times the
+// +-1 dot product over the padded K and C = (acc >> 12) - (64*Kp - K), exact
+// for 64*Kp < 2^19. Only PACKED operands ever cross HBM/L2 (8x less operand
+// traffic than an int8 GEMM); the expansion is paid per CTA in shared memory.
 //
 // Per CTA (one 128 x 256 tile of C, accumulator = 256 TMEM columns):
 //   warp 8      TMA producer: packed A [128 rows x 64 B] and B [256 rows x 64 B]
@@ -127,27 +129,82 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
 constexpr uint32_t TC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
                               ((uint32_t)(TC_BM >> 4) << 24);
 
-// 4 bits of h (bits j, 8+j, 16+j, 24+j) -> 4 bytes, 0xFF for a set bit, 0x01 otherwise
+// 4 bits of h (bits j, 8+j, 16+j, 24+j) -> 4 bytes: 0xC0 (-64) for a set bit, 0x40 (+64) otherwise
 __device__ __forceinline__ uint32_t tc_expand4(uint32_t h, int j) {
-    uint32_t m;
-    asm("prmt.b32 %0, %1, 0, 0xBA98;" : "=r"(m) : "r"(h << (7 - j)));   // msb of each byte replicated
-    return m | 0x01010101u;
+    return ((h << (7 - j)) & 0x80808080u) | 0x40404040u;
 }
 
-// 64 bits (one half of a 128-bit k-block of one row) -> 64 int8 into 4 chunks of
-// the 128-byte operand row. `half` selects chunks 4*half .. 4*half+3.
-__device__ __forceinline__ void tc_expand_half(uint2 bits, uint32_t row_saddr, int row, int half) {
+template <int IMM>
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0+%5], {%1,%2,%3,%4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "n"(IMM) : "memory");
+}
+template <int IMM>
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(IMM) : "memory");
+    return v;
+}
+
+// 64 bits (one half of a 128-bit k-block of one row) -> 64 int8 into the 4
+// chunks (16 bytes each) of the 128-byte operand row that this half owns.
+// dst[c] is the shared address of chunk c (swizzle applied), IMM a constant
+// offset (ring slot, operand, +128 rows).
+template <int IMM>
+__device__ __forceinline__ void tc_expand_half(uint2 bits, const uint32_t (&dst)[4]) {
     const uint32_t h[2] = {bits.x, bits.y};
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            const uint32_t w0 = tc_expand4(h[q], 4 * c + 0), w1 = tc_expand4(h[q], 4 * c + 1);
-            const uint32_t w2 = tc_expand4(h[q], 4 * c + 2), w3 = tc_expand4(h[q], 4 * c + 3);
-            const int chunk = 4 * half + 2 * q + c;
-            const uint32_t dst = row_saddr + (uint32_t)(((chunk ^ (row & 7)) << 4));
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" :: "r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-        }
+        for (int c = 0; c < 2; ++c)
+            sts128<IMM>(dst[2 * q + c], tc_expand4(h[q], 4 * c + 0), tc_expand4(h[q], 4 * c + 1),
+                        tc_expand4(h[q], 4 * c + 2), tc_expand4(h[q], 4 * c + 3));
+    }
+}
+
+// One k-block of the expander loop with every ring index a compile-time
+// constant: U = k-block index modulo 12 (3 operand slots x 4 k-blocks per
+// packed stage), so the only run-time state is the parity bit of the packed ring.
+struct ExpanderCtx {
+    uint32_t bars, p_ring, lds_off[4], sts_addr[4];
+    volatile int* abort_flag;
+    int lane;
+};
+
+template <int U>
+__device__ __forceinline__ bool tc_expander_step(const ExpanderCtx& cx, uint32_t p_parity, bool last_kb) {
+    constexpr int S = U / TC_KB_PER_STAGE, KB = U % TC_KB_PER_STAGE, R = U % TC_ESTAGES;
+    constexpr uint32_t E_PARITY = ((U / TC_ESTAGES) & 1) ^ 1;
+    const uint32_t p_full = cx.bars + 8u * S, p_empty = cx.bars + 8u * (TC_PSTAGES + S);
+    const uint32_t e_full = cx.bars + 8u * (2 * TC_PSTAGES + R), e_empty = cx.bars + 8u * (2 * TC_PSTAGES + TC_ESTAGES + R);
+    if (KB == 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait(p_full, p_parity, cx.abort_flag, 3))) return false;
+    }
+    const uint32_t src = cx.p_ring + cx.lds_off[KB];
+    const uint2 a  = lds64<S * TC_P_STAGE>(src);
+    const uint2 b0 = lds64<S * TC_P_STAGE + TC_P_A>(src);
+    const uint2 b1 = lds64<S * TC_P_STAGE + TC_P_A + 128 * TC_PK>(src);
+    if (KB == TC_KB_PER_STAGE - 1 || last_kb) {
+        __syncwarp();
+        if (cx.lane == 0) mbar_arrive(p_empty);
+    }
+    if (!__all_sync(0xffffffffu, mbar_wait(e_empty, E_PARITY, cx.abort_flag, 4))) return false;
+    tc_expand_half<R * TC_E_STAGE>(a, cx.sts_addr);
+    tc_expand_half<R * TC_E_STAGE + TC_E_A>(b0, cx.sts_addr);
+    tc_expand_half<R * TC_E_STAGE + TC_E_A + 128 * 128>(b1, cx.sts_addr);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (cx.lane == 0) mbar_arrive(e_full);
+    return true;
+}
+
+template <int U>
+__device__ __forceinline__ bool tc_expander_steps(const ExpanderCtx& cx, int32_t i0, int32_t nkb, uint32_t p_parity) {
+    if constexpr (U < 12) {
+        if (i0 + U >= nkb) return true;
+        if (!tc_expander_step<U>(cx, p_parity, i0 + U == nkb - 1)) return false;
+        return tc_expander_steps<U + 1>(cx, i0, nkb, p_parity);
+    } else {
+        return true;
     }
 }
 
@@ -253,37 +310,17 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else {
         // ================= expanders, then epilogue =================
         const int erow = tid >> 1, half = tid & 1;       // rows erow (A), erow and erow+128 (B)
+        ExpanderCtx cx;
+        cx.bars = bars; cx.p_ring = p_ring; cx.abort_flag = abort_flag; cx.lane = lane;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)       // packed 8 bytes of (row, k-block, half) under SWIZZLE_64B
+            cx.lds_off[kb] = (uint32_t)(erow * TC_PK + (((kb ^ (erow >> 1)) & 3) << 4) + half * 8);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)          // chunk 4*half + c of the 128-byte operand row under SWIZZLE_128B
+            cx.sts_addr[c] = e_ring + (uint32_t)(erow * 128 + (((4 * half + c) ^ (erow & 7)) << 4));
         bool ok = true;
-        for (int32_t i = 0; i < nkb && ok; ++i) {
-            const int32_t st = i / TC_KB_PER_STAGE, kb = i % TC_KB_PER_STAGE;
-            const int s = st % TC_PSTAGES;
-            if (kb == 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(p_full(s), (st / TC_PSTAGES) & 1, abort_flag, 3));
-                if (!ok) break;
-            }
-            // packed 8 bytes of (row, k-block, half) under SWIZZLE_64B
-            const uint8_t* ps = gp_ring + s * TC_P_STAGE;
-            auto packed = [&](const uint8_t* tile, int row) {
-                return *reinterpret_cast<const uint2*>(tile + row * TC_PK + (((kb ^ (row >> 1)) & 3) << 4) + half * 8);
-            };
-            const uint2 a  = packed(ps, erow);
-            const uint2 b0 = packed(ps + TC_P_A, erow);
-            const uint2 b1 = packed(ps + TC_P_A, erow + 128);
-            if (kb == TC_KB_PER_STAGE - 1 || i == nkb - 1) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_empty(s));
-            }
-            const int r = i % TC_ESTAGES;
-            ok = __all_sync(0xffffffffu, mbar_wait(e_empty(r), ((i / TC_ESTAGES) & 1) ^ 1, abort_flag, 4));
-            if (!ok) break;
-            const uint32_t ea = e_ring + r * TC_E_STAGE, eb = ea + TC_E_A;
-            tc_expand_half(a,  ea + erow * 128, erow, half);
-            tc_expand_half(b0, eb + erow * 128, erow, half);
-            tc_expand_half(b1, eb + (erow + 128) * 128, erow + 128, half);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(e_full(r));
-        }
+        for (int32_t i0 = 0; i0 < nkb && ok; i0 += 12)
+            ok = tc_expander_steps<0>(cx, i0, nkb, (uint32_t)((i0 / 12) & 1));
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, 5));
         if (ok) {
             tc_fence_after();
@@ -302,11 +339,11 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<int4*>(dst + j) = make_int4((int32_t)v[j] - kcorr, (int32_t)v[j + 1] - kcorr,
-                                                                             (int32_t)v[j + 2] - kcorr, (int32_t)v[j + 3] - kcorr);
+                                *reinterpret_cast<int4*>(dst + j) = make_int4(((int32_t)v[j] >> 12) - kcorr, ((int32_t)v[j + 1] >> 12) - kcorr,
+                                                                             ((int32_t)v[j + 2] >> 12) - kcorr, ((int32_t)v[j + 3] >> 12) - kcorr);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) if (n + j < N) dst[j] = (int32_t)v[j] - kcorr;
+                            for (int j = 0; j < 32; ++j) if (n + j < N) dst[j] = ((int32_t)v[j] >> 12) - kcorr;
                         }
                     }
                 } else {
@@ -314,7 +351,7 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         if (n + j < N) {
-                            const float y = __ldg(scale + n + j) * (float)((int32_t)v[j] - kcorr);
+                            const float y = __ldg(scale + n + j) * (float)(((int32_t)v[j] >> 12) - kcorr);
                             const bool b = mode == BRUTE_SIGN_GE0 ? (y >= 0.0f) : (y > 0.0f);
                             bits |= (b ? 1u : 0u) << j;
                         }
@@ -369,7 +406,7 @@ static bool tc5_make_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t
 // stride rule), 16-byte aligned bases, tile counts within the grid limits.
 static bool tc5_accepts(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp) {
     return Kp > 0 && (Kp % 2) == 0 && aligned16(A) && aligned16(B) && M > 0 && N > 0 &&
-           (M + TC_BM - 1) / TC_BM <= 65535 && Kp * 8 < (1ll << 31);
+           (M + TC_BM - 1) / TC_BM <= 65535 && Kp * 64 < (1ll << 19);   // 4096 * K must fit int32
 }
 
 static int tc5_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp, int64_t K,

@@ -29,39 +29,83 @@ __device__ __forceinline__ uint4 load16_guarded(uintptr_t p, uintptr_t lo, uintp
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// task -> (row, chunk of the row). FLAT: a single row, no division at all.
+// Otherwise a 32-bit division when the task count allows it (the usual case).
+struct TaskMap {
+    int64_t cpr;        // chunks (warp tasks) per row
+    uint32_t cpr32;
+    int small;          // tasks < 2^32
+};
+
+template <bool FLAT>
+__device__ __forceinline__ void split_task(int64_t task, const TaskMap& tm, int64_t& r, int64_t& c) {
+    if (FLAT) { r = 0; c = task; }
+    else if (tm.small) {
+        const uint32_t t = (uint32_t)task, q = t / tm.cpr32;
+        r = q; c = t - q * tm.cpr32;
+    } else { r = task / tm.cpr; c = task - r * tm.cpr; }
+}
+
+// 16 bool bytes -> 16 bits. Bytes that are already 0/1 (what torch writes) skip
+// the normalisation; any other nonzero byte still counts as 1.
+__device__ __forceinline__ uint32_t bools16_to_bits(uint4 v) {
+    if ((v.x | v.y | v.z | v.w) & 0xFEFEFEFEu) {
+        v.x = ((((v.x & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | v.x) >> 7) & 0x01010101u;
+        v.y = ((((v.y & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | v.y) >> 7) & 0x01010101u;
+        v.z = ((((v.z & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | v.z) >> 7) & 0x01010101u;
+        v.w = ((((v.w & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | v.w) >> 7) & 0x01010101u;
+    }
+    // bits 0,8,16,24 -> 28..31 with one multiply (no two partial products share a bit)
+    constexpr uint32_t G = 0x10204080u;
+    return ((v.x * G) >> 28) | (((v.y * G) >> 24) & 0xF0u) | (((v.z * G) >> 20) & 0xF00u) |
+           (((v.w * G) >> 16) & 0xF000u);
+}
+
 struct PackLoad {
     uint4 lo, hi;      // aligned group of this lane; lane 31 also holds the next one
     int64_t r, g;      // row, 16-byte group index within the row
     uint32_t m;        // misalignment of the row start (bytes, 0..15)
 };
 
-__device__ __forceinline__ PackLoad pack_bool_load(const uint8_t* in, int64_t ld, int64_t cpr,
+// ALIGNED: every row starts on a 16-byte boundary, so a lane's group is one
+// aligned vector and no bits move between lanes.
+template <bool FLAT, bool ALIGNED>
+__device__ __forceinline__ PackLoad pack_bool_load(const uint8_t* in, int64_t ld, const TaskMap& tm,
                                                    int64_t task, uintptr_t buf_lo, uintptr_t buf_hi,
                                                    int lane) {
     PackLoad t;
-    t.r = task / cpr;
-    const int64_t c = task - t.r * cpr;
+    int64_t c;
+    split_task<FLAT>(task, tm, t.r, c);
     t.g = c * 32 + lane;
     const uintptr_t rowp = reinterpret_cast<uintptr_t>(in) + (uintptr_t)(t.r * ld);
     const uintptr_t row_end = rowp + (uintptr_t)ld;
-    t.m = (uint32_t)(rowp & 15u);
-    const uintptr_t ab = rowp + (uintptr_t)(t.g * 16) - t.m;
     t.lo = make_uint4(0u, 0u, 0u, 0u);
     t.hi = make_uint4(0u, 0u, 0u, 0u);
-    if (ab < row_end) t.lo = load16_guarded(ab, buf_lo, buf_hi);
-    if (t.m != 0 && lane == 31 && ab + 16 < row_end) t.hi = load16_guarded(ab + 16, buf_lo, buf_hi);
+    if (ALIGNED) {
+        t.m = 0;
+        const uintptr_t a = rowp + (uintptr_t)(t.g * 16);
+        if (a + 16 <= row_end) t.lo = ldg_stream(reinterpret_cast<const void*>(a));
+        else if (a < row_end) t.lo = load16_guarded(a, buf_lo, buf_hi);
+    } else {
+        t.m = (uint32_t)(rowp & 15u);
+        const uintptr_t ab = rowp + (uintptr_t)(t.g * 16) - t.m;
+        if (ab < row_end) t.lo = load16_guarded(ab, buf_lo, buf_hi);
+        if (t.m != 0 && lane == 31 && ab + 16 < row_end) t.hi = load16_guarded(ab + 16, buf_lo, buf_hi);
+    }
     return t;
 }
 
+template <bool ALIGNED>
 __device__ __forceinline__ void pack_bool_finish(const PackLoad& t, uint64_t* out, int64_t ld,
                                                  int64_t wpr, int lane) {
-    const uint32_t lob = nonzero_bytes_to_bits16(t.lo);
-    uint32_t hib = __shfl_down_sync(0xffffffffu, lob, 1);
-    if (lane == 31) hib = nonzero_bytes_to_bits16(t.hi);
-    uint32_t bits = ((lob | (hib << 16)) >> t.m) & 0xFFFFu;
+    uint32_t bits = bools16_to_bits(t.lo);
+    if (!ALIGNED) {
+        uint32_t hib = __shfl_down_sync(0xffffffffu, bits, 1);
+        if (lane == 31) hib = bools16_to_bits(t.hi);
+        bits = ((bits | (hib << 16)) >> t.m) & 0xFFFFu;
+    }
     const int64_t valid = ld - t.g * 16;
-    if (valid <= 0) bits = 0;
-    else if (valid < 16) bits &= (1u << (int)valid) - 1u;
+    if (valid < 16) bits = valid <= 0 ? 0u : (bits & ((1u << (int)valid) - 1u));
     // 4 neighbouring lanes hold the four 16-bit quarters of one word
     uint32_t half = bits << (16 * (lane & 1));
     half |= __shfl_xor_sync(0xffffffffu, half, 1);
@@ -72,25 +116,28 @@ __device__ __forceinline__ void pack_bool_finish(const PackLoad& t, uint64_t* ou
     }
 }
 
+template <bool FLAT, bool ALIGNED>
 __global__ void __launch_bounds__(256)
 k_pack_bool(const uint8_t* __restrict__ in, uint64_t* __restrict__ out,
-            int64_t rows, int64_t ld, int64_t wpr, int64_t cpr, int64_t tasks) {
+            int64_t rows, int64_t ld, int64_t wpr, TaskMap tm, int64_t tasks) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const uintptr_t buf_lo = reinterpret_cast<uintptr_t>(in);
     const uintptr_t buf_hi = buf_lo + (uintptr_t)(rows * ld);
     int64_t task = warp;
-    // two tasks per trip: both loads are in flight before either is consumed
-    for (; task + nwarps < tasks; task += 2 * nwarps) {
-        PackLoad a = pack_bool_load(in, ld, cpr, task, buf_lo, buf_hi, lane);
-        PackLoad b = pack_bool_load(in, ld, cpr, task + nwarps, buf_lo, buf_hi, lane);
-        pack_bool_finish(a, out, ld, wpr, lane);
-        pack_bool_finish(b, out, ld, wpr, lane);
+    // four tasks per trip: all loads are in flight before any is consumed
+    for (; task + 3 * nwarps < tasks; task += 4 * nwarps) {
+        PackLoad t[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            t[k] = pack_bool_load<FLAT, ALIGNED>(in, ld, tm, task + k * nwarps, buf_lo, buf_hi, lane);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) pack_bool_finish<ALIGNED>(t[k], out, ld, wpr, lane);
     }
-    if (task < tasks) {
-        PackLoad a = pack_bool_load(in, ld, cpr, task, buf_lo, buf_hi, lane);
-        pack_bool_finish(a, out, ld, wpr, lane);
+    for (; task < tasks; task += nwarps) {
+        PackLoad a = pack_bool_load<FLAT, ALIGNED>(in, ld, tm, task, buf_lo, buf_hi, lane);
+        pack_bool_finish<ALIGNED>(a, out, ld, wpr, lane);
     }
 }
 
@@ -103,33 +150,36 @@ template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; 
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
 template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
 
-__device__ __forceinline__ bool sign_bit(float x, int mode) {
-    return mode == BRUTE_SIGN_GE0 ? (x >= 0.0f) : (x > 0.0f);   // NaN -> false
+template <int MODE> __device__ __forceinline__ bool sign_bit(float x) {
+    return MODE == BRUTE_SIGN_GE0 ? (x >= 0.0f) : (x > 0.0f);   // NaN -> false
 }
 
 // One element per lane and load: fully coalesced scalar loads, one ballot per
 // 32 elements. Warp task = 256 elements of one row = 4 output words.
-template <typename T>
+template <typename T, bool FLAT, int MODE>
 __global__ void __launch_bounds__(256)
 k_pack_sign_ballot(const T* __restrict__ in, uint64_t* __restrict__ out,
-                   int64_t ld, int64_t wpr, int64_t cpr, int64_t tasks, int mode) {
+                   int64_t ld, int64_t wpr, TaskMap tm, int64_t tasks) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t task = warp; task < tasks; task += nwarps) {
-        const int64_t r = task / cpr;
-        const int64_t c = task - r * cpr;
-        const T* rowp = in + r * ld;
-        const int64_t base = c * 256 + lane;
+        int64_t r, c;
+        split_task<FLAT>(task, tm, r, c);
+        const int64_t e0 = c * 256;
+        const T* p = in + r * ld + e0 + lane;
         float x[8];
+        if (e0 + 256 <= ld) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int64_t i = base + 32 * j;
-            x[j] = (i < ld) ? to_f32<T>(__ldcs(rowp + i)) : -1.0f;
+            for (int j = 0; j < 8; ++j) x[j] = to_f32<T>(__ldcs(p + 32 * j));
+        } else {
+            const int left = (int)(ld - e0) - lane;      // elements from this lane's first one to the row end
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = (32 * j < left) ? to_f32<T>(__ldcs(p + 32 * j)) : -1.0f;
         }
         uint32_t b[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) b[j] = __ballot_sync(0xffffffffu, sign_bit(x[j], mode));
+        for (int j = 0; j < 8; ++j) b[j] = __ballot_sync(0xffffffffu, sign_bit<MODE>(x[j]));
         if (lane < 4) {
             const uint32_t lo = lane == 0 ? b[0] : lane == 1 ? b[2] : lane == 2 ? b[4] : b[6];
             const uint32_t hi = lane == 0 ? b[1] : lane == 1 ? b[3] : lane == 2 ? b[5] : b[7];
@@ -142,17 +192,17 @@ k_pack_sign_ballot(const T* __restrict__ in, uint64_t* __restrict__ out,
 // 16-bit source types, two elements per 32-bit load (row starts 4-byte
 // aligned): each lane yields 2 bits, a warp-wide OR-reduction builds the word.
 // Warp task = 512 elements = 8 output words.
-template <typename T>
+template <typename T, bool FLAT, int MODE>
 __global__ void __launch_bounds__(256)
 k_pack_sign_pair16(const T* __restrict__ in, uint64_t* __restrict__ out,
-                   int64_t ld, int64_t wpr, int64_t cpr, int64_t tasks, int mode) {
+                   int64_t ld, int64_t wpr, TaskMap tm, int64_t tasks) {
     static_assert(sizeof(T) == 2, "pair kernel is for 16-bit element types");
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t task = warp; task < tasks; task += nwarps) {
-        const int64_t r = task / cpr;
-        const int64_t c = task - r * cpr;
+        int64_t r, c;
+        split_task<FLAT>(task, tm, r, c);
         const T* rowp = in + r * ld;
         const int64_t base = c * 512 + 2 * lane;
         uint32_t raw[8];
@@ -171,8 +221,8 @@ k_pack_sign_pair16(const T* __restrict__ in, uint64_t* __restrict__ out,
             const uint16_t u0 = (uint16_t)(raw[j] & 0xFFFFu), u1 = (uint16_t)(raw[j] >> 16);
             e0 = *reinterpret_cast<const T*>(&u0);
             e1 = *reinterpret_cast<const T*>(&u1);
-            const uint32_t two = (sign_bit(to_f32<T>(e0), mode) ? 1u : 0u) |
-                                 (sign_bit(to_f32<T>(e1), mode) ? 2u : 0u);
+            const uint32_t two = (sign_bit<MODE>(to_f32<T>(e0)) ? 1u : 0u) |
+                                 (sign_bit<MODE>(to_f32<T>(e1)) ? 2u : 0u);
             const uint32_t v = two << (2 * (lane & 15));
             const uint32_t lo = __reduce_or_sync(0xffffffffu, lane < 16 ? v : 0u);
             const uint32_t hi = __reduce_or_sync(0xffffffffu, lane >= 16 ? v : 0u);
@@ -199,19 +249,28 @@ __device__ __forceinline__ uint32_t row_bits16(const uint64_t* rowp, int64_t col
     return (uint32_t)x & 0xFFFFu;
 }
 
+// 4 consecutive bits starting at bit `col` (inside the row's words)
+__device__ __forceinline__ uint32_t row_bits16_short(const uint64_t* rowp, int64_t col, int64_t wpr) {
+    const int64_t w = col >> 6;
+    const int sh = (int)(col & 63);
+    uint64_t x = __ldg(rowp + w) >> sh;
+    if (sh > 60 && w + 1 < wpr) x |= __ldg(rowp + w + 1) << (64 - sh);
+    return (uint32_t)x & 0xFu;
+}
+
 // ELEM = bytes per output element (1: bool byte, 4: float +-1). A lane owns one
 // 16-byte ALIGNED group of the output, i.e. EPG = 16/ELEM elements.
-template <int ELEM>
+template <int ELEM, bool FLAT>
 __global__ void __launch_bounds__(256)
 k_unpack(const uint64_t* __restrict__ in, uint8_t* __restrict__ out,
-         int64_t ll, int64_t wpr, int64_t cpr, int64_t tasks) {
+         int64_t ll, int64_t wpr, TaskMap tm, int64_t tasks) {
     constexpr int EPG = 16 / ELEM;
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t task = warp; task < tasks; task += nwarps) {
-        const int64_t r = task / cpr;
-        const int64_t c = task - r * cpr;
+        int64_t r, c;
+        split_task<FLAT>(task, tm, r, c);
         const int64_t g = c * 32 + lane;
         const uint64_t* rowp = in + r * wpr;
         uint8_t* orow = out + r * ll * ELEM;
@@ -219,7 +278,12 @@ k_unpack(const uint64_t* __restrict__ in, uint8_t* __restrict__ out,
         const int64_t col0 = g * EPG - m;            // first element of this lane's group
         if (col0 >= ll || col0 + EPG <= 0) continue;
         if (col0 >= 0 && col0 + EPG <= ll) {
-            const uint32_t bits = row_bits16(rowp, col0, wpr);
+            uint32_t bits;
+            if (ELEM == 1) {
+                bits = row_bits16(rowp, col0, wpr);
+            } else {
+                bits = row_bits16_short(rowp, col0, wpr);
+            }
             uint4 v;
             if (ELEM == 1) {
                 v.x = bits4_to_bytes01(bits);       v.y = bits4_to_bytes01(bits >> 4);
@@ -254,6 +318,14 @@ static inline void flatten_rows(int64_t& rows, int64_t& len) {
 
 using namespace bb;
 
+static inline TaskMap make_task_map(int64_t cpr, int64_t tasks) {
+    TaskMap tm;
+    tm.cpr = cpr;
+    tm.cpr32 = (uint32_t)(cpr < 0xFFFFFFFFll ? cpr : 0xFFFFFFFFll);
+    tm.small = (tasks < 0xFFFFFFFFll && cpr < 0xFFFFFFFFll) ? 1 : 0;
+    return tm;
+}
+
 extern "C" int brute_b200_pack_bool(const uint8_t* in, uint64_t* out,
                                     int64_t rows, int64_t ld, void* stream) {
     BB_REQUIRE(rows >= 0 && ld >= 0, BRUTE_ERR_INVALID_ARG);
@@ -264,24 +336,45 @@ extern "C" int brute_b200_pack_bool(const uint8_t* in, uint64_t* out,
     const int64_t wpr = (ld + 63) / 64;
     const int64_t cpr = (wpr + 7) / 8;      // 32 groups of 16 bytes = 8 words per warp task
     const int64_t tasks = rows * cpr;
+    const TaskMap tm = make_task_map(cpr, tasks);
     const int grid = stream_grid(tasks, 8, 8);
-    k_pack_bool<<<grid, 256, 0, as_stream(stream)>>>(in, out, rows, ld, wpr, cpr, tasks);
+    const bool flat = rows == 1;
+    const bool aligned = aligned16(in) && (flat || (ld & 15) == 0);
+    cudaStream_t st = as_stream(stream);
+    if (flat && aligned)  k_pack_bool<true, true><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
+    else if (flat)        k_pack_bool<true, false><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
+    else if (aligned)     k_pack_bool<false, true><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
+    else                  k_pack_bool<false, false><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
     return launch_status();
 }
 
-template <typename T>
-static int launch_pack_sign(const T* in, uint64_t* out, int64_t rows, int64_t ld, int mode,
-                            cudaStream_t st) {
+template <typename T, bool FLAT, int MODE>
+static void launch_pack_sign_one(const T* in, uint64_t* out, int64_t rows, int64_t ld, cudaStream_t st) {
     const int64_t wpr = (ld + 63) / 64;
     const bool pair_ok = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0 &&
                          (rows == 1 || (ld & 1) == 0);
     if (pair_ok) {
         const int64_t cpr = (wpr + 7) / 8, tasks = rows * cpr;
         if constexpr (sizeof(T) == 2)
-            k_pack_sign_pair16<T><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(in, out, ld, wpr, cpr, tasks, mode);
+            k_pack_sign_pair16<T, FLAT, MODE><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(
+                in, out, ld, wpr, make_task_map(cpr, tasks), tasks);
     } else {
         const int64_t cpr = (wpr + 3) / 4, tasks = rows * cpr;
-        k_pack_sign_ballot<T><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(in, out, ld, wpr, cpr, tasks, mode);
+        k_pack_sign_ballot<T, FLAT, MODE><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(
+            in, out, ld, wpr, make_task_map(cpr, tasks), tasks);
+    }
+}
+
+template <typename T>
+static int launch_pack_sign(const T* in, uint64_t* out, int64_t rows, int64_t ld, int mode,
+                            cudaStream_t st) {
+    const bool flat = rows == 1;
+    if (mode == BRUTE_SIGN_GE0) {
+        if (flat) launch_pack_sign_one<T, true, BRUTE_SIGN_GE0>(in, out, rows, ld, st);
+        else      launch_pack_sign_one<T, false, BRUTE_SIGN_GE0>(in, out, rows, ld, st);
+    } else {
+        if (flat) launch_pack_sign_one<T, true, BRUTE_SIGN_GT0>(in, out, rows, ld, st);
+        else      launch_pack_sign_one<T, false, BRUTE_SIGN_GT0>(in, out, rows, ld, st);
     }
     return launch_status();
 }
@@ -317,8 +410,10 @@ static int launch_unpack(const uint64_t* in, void* out, int64_t rows, int64_t ll
     const int64_t gpr = (fll + 2 * EPG - 2) / EPG;
     const int64_t cpr = (gpr + 31) / 32;
     const int64_t tasks = frows * cpr;
-    k_unpack<ELEM><<<stream_grid(tasks, 8, 8), 256, 0, st>>>(
-        in, static_cast<uint8_t*>(out), fll, fwpr, cpr, tasks);
+    const TaskMap tm = make_task_map(cpr, tasks);
+    const int grid = stream_grid(tasks, 8, 8);
+    if (frows == 1) k_unpack<ELEM, true><<<grid, 256, 0, st>>>(in, static_cast<uint8_t*>(out), fll, fwpr, tm, tasks);
+    else            k_unpack<ELEM, false><<<grid, 256, 0, st>>>(in, static_cast<uint8_t*>(out), fll, fwpr, tm, tasks);
     return launch_status();
 }
 

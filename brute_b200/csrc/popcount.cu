@@ -2,6 +2,7 @@
 // All are HBM-bound: 128-bit loads, grid sized in whole waves over the SMs,
 // one 64-bit atomic per block for the totals.
 #include "common.cuh"
+#include <algorithm>
 
 namespace bb {
 
@@ -76,7 +77,7 @@ k_hamming_words(const uint64_t* __restrict__ a, const uint64_t* __restrict__ b,
 // outside the vector range are added by thread 0 of block 0.
 // ---------------------------------------------------------------------------
 template <bool TWO>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(256)
 k_popcount_total(const uint8_t* __restrict__ a, const uint8_t* __restrict__ b,
                  int64_t head, int64_t nvec, int64_t tail, unsigned long long* __restrict__ out) {
     __shared__ uint64_t red[32];
@@ -200,8 +201,9 @@ extern "C" int brute_b200_popcount_total(const void* in, int64_t n_bytes, uint64
     BB_REQUIRE(in != nullptr, BRUTE_ERR_INVALID_ARG);
     int64_t head, nvec, tail;
     split_aligned(in, n_bytes, head, nvec, tail);
-    const int grid = stream_grid(nvec, 512 * 4, 4);
-    k_popcount_total<false><<<grid, 512, 0, st>>>(static_cast<const uint8_t*>(in), nullptr, head, nvec, tail,
+    static const int per_launch = resident_grid(k_popcount_total<false>, 256, 1 << 30);
+    const int grid = (int)std::min<int64_t>(per_launch, std::max<int64_t>(1, (nvec + 256 * 4 - 1) / (256 * 4)));
+    k_popcount_total<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(in), nullptr, head, nvec, tail,
                                                   reinterpret_cast<unsigned long long*>(out));
     return launch_status();
 }
@@ -222,8 +224,9 @@ extern "C" int brute_b200_hamming_total(const void* a, const void* b, int64_t n_
     }
     int64_t head, nvec, tail;
     split_aligned(a, n_bytes, head, nvec, tail);
-    const int grid = stream_grid(nvec, 512 * 4, 4);
-    k_popcount_total<true><<<grid, 512, 0, st>>>(static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b),
+    static const int per_launch = resident_grid(k_popcount_total<true>, 256, 1 << 30);
+    const int grid = (int)std::min<int64_t>(per_launch, std::max<int64_t>(1, (nvec + 256 * 4 - 1) / (256 * 4)));
+    k_popcount_total<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b),
                                                  head, nvec, tail, o);
     return launch_status();
 }

@@ -75,7 +75,12 @@ def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group
         stacked = torch.empty((world * M, N // world), dtype=c_local.dtype, device=c_local.device)
         dist.all_gather_into_tensor(stacked, c_local.contiguous(), group=group)
         return stacked.view(world, M, N // world).permute(1, 0, 2).reshape(M, N)
-    parts = [torch.empty((M, shard_bounds(N, world, r)[1] - shard_bounds(N, world, r)[0]),
-                         dtype=c_local.dtype, device=c_local.device) for r in range(world)]
-    dist.all_gather(parts, c_local.contiguous(), group=group)
-    return torch.cat(parts, dim=1)
+    # uneven blocks: pad every block to the widest one, gather, drop the padding
+    widths = [shard_bounds(N, world, r)[1] - shard_bounds(N, world, r)[0] for r in range(world)]
+    wmax = max(widths)
+    padded = torch.zeros((M, wmax), dtype=c_local.dtype, device=c_local.device)
+    padded[:, :hi - lo] = c_local
+    stacked = torch.empty((world * M, wmax), dtype=c_local.dtype, device=c_local.device)
+    dist.all_gather_into_tensor(stacked, padded, group=group)
+    blocks = stacked.view(world, M, wmax)
+    return torch.cat([blocks[r, :, :widths[r]] for r in range(world)], dim=1)
