@@ -1,8 +1,16 @@
 // Fused binary attention forward.
 //
 //   score(i,j) = (D - 2*popcount(q_i ^ k_j)) * scale      (integer popcount scores)
-//   P = softmax_j(score) in fp32 (online, blockwise), optional causal mask
+//   P = softmax_j(score) in fp32, optional causal mask
 //   O = P @ V, V and O in bf16, fp32 accumulation on the tensor cores
+//
+// A score takes only D+1 values, one per Hamming distance h, so
+// exp(score - rowmax) = rowfactor * T[h] with T[h] = exp(-2*scale*h) and the row
+// factor cancels between numerator and denominator of the softmax. The TABLE
+// kernel therefore keeps T in shared memory (fp32, T <= 1, every term positive)
+// and needs no running maximum, no exp and no rescaling of O: blockwise softmax
+// without the "online" bookkeeping. It is used while exp(-2*|scale|*D) stays a
+// normal fp32 number; steeper scales take the ONLINE kernel (running max, exp2).
 //
 // One CTA owns 128 query rows of one (batch, head); 8 warps of 16 rows. K (packed
 // words) and V (bf16) stream through shared memory in 64-key tiles with a
@@ -227,6 +235,175 @@ k_binary_attention_fwd(const uint64_t* __restrict__ Qp, const uint64_t* __restri
     }
 }
 
+
+// Hamming distance of two D-bit vectors; for D = 128 a carry-save step turns four
+// 32-bit popcounts into three (the POPC pipe is the narrow one).
+template <int W> __device__ __forceinline__ int hamming_bits(const uint32_t* q, const uint32_t* k);
+template <> __device__ __forceinline__ int hamming_bits<1>(const uint32_t* q, const uint32_t* k) {
+    return __popc(q[0] ^ k[0]) + __popc(q[1] ^ k[1]);
+}
+template <> __device__ __forceinline__ int hamming_bits<2>(const uint32_t* q, const uint32_t* k) {
+    const uint32_t x0 = q[0] ^ k[0], x1 = q[1] ^ k[1], x2 = q[2] ^ k[2], x3 = q[3] ^ k[3];
+    const uint32_t s = x0 ^ x1 ^ x2;
+    const uint32_t c = (x0 & x1) | (x0 & x2) | (x1 & x2);
+    return __popc(s) + __popc(x3) + 2 * __popc(c);
+}
+
+template <int W>
+__global__ void __launch_bounds__(AT_THREADS, 2)
+k_binary_attention_fwd_table(const uint64_t* __restrict__ Qp, const uint64_t* __restrict__ Kp,
+                             const __nv_bfloat16* __restrict__ V, __nv_bfloat16* __restrict__ O,
+                             int64_t S, int causal, float neg2c_log2 /* -2*scale*log2(e) */, float bias_log2,
+                             int64_t q_tiles) {
+    constexpr int D = 64 * W;
+    constexpr int VROW = D * 2;
+    constexpr int VCH = D / 8;
+    constexpr int NT = D / 8;
+    __shared__ __align__(16) uint64_t Ks[2][AT_BN * W];
+    __shared__ __align__(128) uint8_t Vs[2][AT_BN * VROW];
+    __shared__ float T[D + 1];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t qt = q_tiles - 1 - (int64_t)blockIdx.x;
+    const int64_t bh = blockIdx.y;
+    const int64_t q0 = qt * AT_BM;
+    const uint64_t* Qb = Qp + bh * S * W;
+    const uint64_t* Kb = Kp + bh * S * W;
+    const __nv_bfloat16* Vb = V + bh * S * D;
+    __nv_bfloat16* Ob = O + bh * S * D;
+
+    if (tid <= D) T[tid] = exp2f(neg2c_log2 * (float)tid - bias_log2);
+
+    const int64_t row_lo = q0 + warp * 16 + g, row_hi = row_lo + 8;
+    uint32_t q[2][2 * W];
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+        const uint64_t a = row_lo < S ? __ldg(Qb + row_lo * W + w) : 0ull;
+        const uint64_t b = row_hi < S ? __ldg(Qb + row_hi * W + w) : 0ull;
+        q[0][2 * w] = (uint32_t)a; q[0][2 * w + 1] = (uint32_t)(a >> 32);
+        q[1][2 * w] = (uint32_t)b; q[1][2 * w + 1] = (uint32_t)(b >> 32);
+    }
+
+    const int64_t kend = causal ? (q0 + AT_BM < S ? q0 + AT_BM : S) : S;
+    const int64_t ntiles = (kend + AT_BN - 1) / AT_BN;
+    const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(&Ks[0][0]);
+    const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(&Vs[0][0]);
+
+    auto load_tile = [&](int buf, int64_t tile) {
+        const int64_t k0 = tile * AT_BN;
+        if (tid < AT_BN * W) {
+            const int key = tid / W, w = tid % W;
+            const bool ok = k0 + key < S;
+            at_cp_async8(ks_base + (buf * AT_BN * W + tid) * 8, Kb + (ok ? (k0 + key) * W + w : 0), ok ? 8 : 0);
+        }
+#pragma unroll
+        for (int it = 0; it < (AT_BN * VCH) / AT_THREADS; ++it) {
+            const int idx = tid + it * AT_THREADS;
+            const int row = idx / VCH, ch = idx % VCH;
+            const bool ok = k0 + row < S;
+            const int sch = (ch & ~7) | ((ch ^ row) & 7);
+            at_cp_async16(vs_base + buf * AT_BN * VROW + row * VROW + sch * 16,
+                          Vb + (ok ? (k0 + row) * D + ch * 8 : 0), ok ? 16 : 0);
+        }
+    };
+
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float lrow[2] = {0.f, 0.f};
+
+    if (ntiles > 0) load_tile(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    for (int64_t tile = 0; tile < ntiles; ++tile) {
+        const int buf = (int)(tile & 1);
+        if (tile + 1 < ntiles) load_tile(buf ^ 1, tile + 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+
+        const int64_t k0 = tile * AT_BN;
+        const bool active = !(causal && k0 > q0 + warp * 16 + 15);
+        if (active) {
+            const bool need_mask = (causal && k0 + AT_BN - 1 > q0 + warp * 16) || (k0 + AT_BN > S);
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+                float p[2][4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int key = kb * 16 + 2 * t + (c & 1) + ((c >> 1) << 3);
+                    uint32_t kw[2 * W];
+                    if (W == 2) {
+                        const uint4 kv = *reinterpret_cast<const uint4*>(&Ks[buf][key * 2]);
+                        kw[0] = kv.x; kw[1] = kv.y; kw[2 * W - 2] = kv.z; kw[2 * W - 1] = kv.w;
+                    } else {
+                        const uint2 kv = *reinterpret_cast<const uint2*>(&Ks[buf][key]);
+                        kw[0] = kv.x; kw[1] = kv.y;
+                    }
+                    float p0 = T[hamming_bits<W>(q[0], kw)];
+                    float p1 = T[hamming_bits<W>(q[1], kw)];
+                    if (need_mask) {
+                        const int64_t kidx = k0 + key;
+                        if (kidx >= S || (causal && kidx > row_lo)) p0 = 0.f;
+                        if (kidx >= S || (causal && kidx > row_hi)) p1 = 0.f;
+                    }
+                    p[0][c] = p0; p[1][c] = p1;
+                }
+                const uint32_t a0 = pack_bf16x2(p[0][0], p[0][1]);
+                const uint32_t a1 = pack_bf16x2(p[1][0], p[1][1]);
+                const uint32_t a2 = pack_bf16x2(p[0][2], p[0][3]);
+                const uint32_t a3 = pack_bf16x2(p[1][2], p[1][3]);
+                // the denominator sums the SAME bf16-rounded weights that enter the MMA,
+                // so the normalised weights of a row add up to exactly one
+                lrow[0] += (__uint_as_float(a0 << 16) + __uint_as_float(a0 & 0xFFFF0000u)) +
+                           (__uint_as_float(a2 << 16) + __uint_as_float(a2 & 0xFFFF0000u));
+                lrow[1] += (__uint_as_float(a1 << 16) + __uint_as_float(a1 & 0xFFFF0000u)) +
+                           (__uint_as_float(a3 << 16) + __uint_as_float(a3 & 0xFFFF0000u));
+                const int vrow = kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                for (int j = 0; j < NT; j += 2) {
+                    const int ch = j + (lane >> 4);
+                    const int sch = (ch & ~7) | ((ch ^ vrow) & 7);
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(vs_base + buf * AT_BN * VROW + vrow * VROW + sch * 16, b0, b1, b2, b3);
+                    mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+                    mma_bf16_16816(o[j + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float l = lrow[h];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int r = warp * 16 + g + 8 * h;
+        uint8_t* srow = &Vs[0][0] + r * VROW;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const int sch = (j & ~7) | ((j ^ r) & 7);
+            *reinterpret_cast<uint32_t*>(srow + sch * 16 + t * 4) =
+                pack_bf16x2(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < (AT_BM * VCH) / AT_THREADS; ++it) {
+        const int idx = tid + it * AT_THREADS;
+        const int r = idx / VCH, ch = idx % VCH;
+        const int sch = (ch & ~7) | ((ch ^ r) & 7);
+        if (q0 + r < S) {
+            const uint4 v = *reinterpret_cast<const uint4*>(&Vs[0][0] + r * VROW + sch * 16);
+            *reinterpret_cast<uint4*>(Ob + (q0 + r) * D + ch * 8) = v;
+        }
+    }
+}
+
 }  // namespace bb
 
 using namespace bb;
@@ -248,6 +425,15 @@ extern "C" int brute_b200_binary_attention_fwd(const uint64_t* Qp, const uint64_
     cudaStream_t st = as_stream(stream);
     auto* v = static_cast<const __nv_bfloat16*>(V);
     auto* o = static_cast<__nv_bfloat16*>(O);
+    // table kernel while T[D] = exp2(-2*|scale|*log2(e)*D) is a normal fp32 number
+    const float span_log2 = 2.0f * fabsf(scale_log2) * (float)D;
+    if (span_log2 <= 100.0f) {
+        const float neg2c = -2.0f * scale_log2;
+        const float bias = scale_log2 < 0.f ? neg2c * (float)D : 0.f;      // keeps max(T) == 1
+        if (D == 128) k_binary_attention_fwd_table<2><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
+        else          k_binary_attention_fwd_table<1><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
+        return launch_status();
+    }
     if (D == 128) k_binary_attention_fwd<2><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, scale_log2, q_tiles);
     else          k_binary_attention_fwd<1><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, scale_log2, q_tiles);
     return launch_status();

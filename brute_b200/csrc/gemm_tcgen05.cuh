@@ -1,13 +1,17 @@
 // xnor-popcount GEMM on the 5th-generation tensor cores (tcgen05.mma kind::i8).
 //
-// sm_100a has no binary tcgen05 kind, so the bits are expanded to int8 ON CHIP:
-// bit 1 -> -64 (0xC0), bit 0 -> +64 (0x40) for both operands. The two codes
-// differ in bit 7 only, so a byte costs one shift (shared by four bytes) and
-// one three-input logic op; the sign flip is the same on both sides and leaves
-// every product's sign unchanged, so the int32 accumulator holds 4096 times the
-// +-1 dot product over the padded K and C = (acc >> 12) - (64*Kp - K), exact
-// for 64*Kp < 2^19. Only PACKED operands ever cross HBM/L2 (8x less operand
-// traffic than an int8 GEMM); the expansion is paid per CTA in shared memory.
+// sm_100a has no binary tcgen05 kind, so the bits are expanded to unsigned int8 ON CHIP, with
+// weights chosen so that the expansion is ONE logic op per 4 bytes and no shift at all:
+//   A byte (b, j) = bit << j        : word_j = h & (0x01010101 << j), bits stay where they are;
+//   B byte (b, j) = bit << (7 - j)  : the packed word is first bit-reversed inside each byte
+//                                     (brev + prmt, once per 32 bits), then word_j = g' & (0x01010101 << (7-j)).
+// Every product of two set bits is 2^j * 2^(7-j) = 128, so the int32 accumulator holds
+// 128 * popcount(a & b) and, with the row popcounts pa[m], pb[n] that the expanders count on the
+// way (pad bits are 0 and count nothing),
+//   popcount(a ^ b) = pa + pb - 2*popcount(a & b),   C = K - 2*pa[m] - 2*pb[n] + 4*(acc >> 7),
+// exact in int32 for K < 2^24. Only PACKED operands ever cross HBM/L2 (8x less operand traffic
+// than an int8 GEMM); the expansion is paid per CTA on chip. The ALU pipe (16 lanes/clk per SM
+// quarter) is the scarce unit of the expansion, which is why the op count per byte matters.
 //
 // Per CTA (one 128 x 256 tile of C, accumulator = 256 TMEM columns):
 //   warp 8      TMA producer: packed A [128 rows x 64 B] and B [256 rows x 64 B]
@@ -41,10 +45,19 @@ constexpr int TC_P_A = TC_BM * TC_PK, TC_P_B = TC_BN * TC_PK;
 constexpr int TC_P_STAGE = TC_P_A + TC_P_B;             // 24 KB
 constexpr int TC_E_A = TC_BM * 128, TC_E_B = TC_BN * 128;
 constexpr int TC_E_STAGE = TC_E_A + TC_E_B;             // 48 KB
-constexpr int TC_EXP_WARPS = 8;
-constexpr int TC_THREADS = (TC_EXP_WARPS + 2) * 32;     // 320
-constexpr int TC_TMEM_COLS = 256;
-constexpr int TC_SMEM = TC_ESTAGES * TC_E_STAGE + TC_PSTAGES * TC_P_STAGE + 256 + 1024;
+constexpr int TC_GROUP_WARPS = 8;                       // warps that expand one k-block together
+constexpr int TC_GROUPS = 2;                            // groups alternate k-blocks, so their latency chains overlap
+constexpr int TC_EXP_WARPS = TC_GROUP_WARPS * TC_GROUPS;
+constexpr int TC_THREADS = (TC_EXP_WARPS + 2) * 32;     // 576
+// The A operand (M = 128 rows) goes to TENSOR MEMORY, not shared memory: the expanders write their
+// int8 words straight from registers with tcgen05.st and the MMA reads A from TMEM, so only B's
+// 256 rows pay shared-memory store (and MMA read) bandwidth. 32 columns per k-block and ring slot.
+constexpr bool TC_A_IN_TMEM = true;
+constexpr int TC_A_COLS = 32;                           // 128 int8 of K per row = 32 columns of 32 bits
+constexpr int TC_ACC_COLS = 256;
+constexpr int TC_TMEM_COLS = TC_A_IN_TMEM ? 512 : 256;  // power of two >= 256 + 3 * 32
+constexpr int TC_ROWPOP_BYTES = (TC_BM + TC_BN) * 4;      // pa[128], pb[256] of the tile
+constexpr int TC_SMEM = TC_ESTAGES * TC_E_STAGE + TC_PSTAGES * TC_P_STAGE + 256 + TC_ROWPOP_BYTES + 1024;
 constexpr uint64_t TC_WAIT_NS = 1000000000ull;          // bound of every in-kernel wait
 
 __device__ int g_tc_status = 0;                         // 0 ok; else which wait gave up
@@ -94,7 +107,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
         :: "r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
+#ifndef BB_EXP_NO_FENCE   // timing experiment only: results are wrong
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -106,6 +121,20 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint6
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's own TMEM lane (lane = 32 * (warp % 4) + laneid)
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -125,17 +154,27 @@ __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
 }
-// kind::i8, D = s32, A = B = signed int8, both K-major, M = 128, N = 256
-constexpr uint32_t TC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
+// kind::i8, D = s32, A = B = unsigned int8 (format 0), both K-major, M = 128, N = 256
+constexpr uint32_t TC_IDESC = (2u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
                               ((uint32_t)(TC_BM >> 4) << 24);
 
-// 4 bits of h (bits j, 8+j, 16+j, 24+j) -> 4 bytes: 0xC0 (-64) for a set bit, 0x40 (+64) otherwise
+// 4 bits of h (bits j, 8+j, 16+j, 24+j) -> 4 bytes. A side: the bit stays at position j of its
+// byte. B side (h already bit-reversed inside each byte): original bit j sits at position 7-j.
+template <bool IS_B>
 __device__ __forceinline__ uint32_t tc_expand4(uint32_t h, int j) {
-    return ((h << (7 - j)) & 0x80808080u) | 0x40404040u;
+#ifdef BB_EXP_NO_ALU      // timing experiment only: results are wrong
+    return h + j;
+#endif
+    return h & (0x01010101u << (IS_B ? 7 - j : j));
 }
+// reverse the bit order inside each byte of a packed word (B operand, once per 32 bits)
+__device__ __forceinline__ uint32_t tc_brev_bytes(uint32_t g) { return __byte_perm(__brev(g), 0u, 0x0123u); }
 
 template <int IMM>
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+#ifdef BB_EXP_NO_STS      // timing experiment only: results are wrong
+    if (a == 0x12345678u && b == c && d == 7u)
+#endif
     asm volatile("st.shared.v4.b32 [%0+%5], {%1,%2,%3,%4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "n"(IMM) : "memory");
 }
 template <int IMM>
@@ -149,15 +188,15 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 // chunks (16 bytes each) of the 128-byte operand row that this half owns.
 // dst[c] is the shared address of chunk c (swizzle applied), IMM a constant
 // offset (ring slot, operand, +128 rows).
-template <int IMM>
+template <int IMM, bool IS_B>
 __device__ __forceinline__ void tc_expand_half(uint2 bits, const uint32_t (&dst)[4]) {
-    const uint32_t h[2] = {bits.x, bits.y};
+    const uint32_t h[2] = {IS_B ? tc_brev_bytes(bits.x) : bits.x, IS_B ? tc_brev_bytes(bits.y) : bits.y};
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
-            sts128<IMM>(dst[2 * q + c], tc_expand4(h[q], 4 * c + 0), tc_expand4(h[q], 4 * c + 1),
-                        tc_expand4(h[q], 4 * c + 2), tc_expand4(h[q], 4 * c + 3));
+            sts128<IMM>(dst[2 * q + c], tc_expand4<IS_B>(h[q], 4 * c + 0), tc_expand4<IS_B>(h[q], 4 * c + 1),
+                        tc_expand4<IS_B>(h[q], 4 * c + 2), tc_expand4<IS_B>(h[q], 4 * c + 3));
     }
 }
 
@@ -166,43 +205,65 @@ __device__ __forceinline__ void tc_expand_half(uint2 bits, const uint32_t (&dst)
 // packed stage), so the only run-time state is the parity bit of the packed ring.
 struct ExpanderCtx {
     uint32_t bars, p_ring, lds_off[4], sts_addr[4];
+    uint32_t a_lds_off[4], a_taddr;      // A through TMEM: packed-bit offsets and TMEM address of this thread's half row
+    int pc_a, pc_b0, pc_b1;              // set bits seen so far in this thread's half rows (for pa[m], pb[n])
     volatile int* abort_flag;
     int lane;
 };
 
-template <int U>
-__device__ __forceinline__ bool tc_expander_step(const ExpanderCtx& cx, uint32_t p_parity, bool last_kb) {
+// Group G (0 or 1) owns the k-blocks with U % 2 == G; inside a packed stage (4 k-blocks) it reads
+// k-blocks G and G + 2, so it waits for the stage before the first and releases it after the second.
+template <int G, int U>
+__device__ __forceinline__ bool tc_expander_step(ExpanderCtx& cx, uint32_t p_parity) {
     constexpr int S = U / TC_KB_PER_STAGE, KB = U % TC_KB_PER_STAGE, R = U % TC_ESTAGES;
     constexpr uint32_t E_PARITY = ((U / TC_ESTAGES) & 1) ^ 1;
     const uint32_t p_full = cx.bars + 8u * S, p_empty = cx.bars + 8u * (TC_PSTAGES + S);
     const uint32_t e_full = cx.bars + 8u * (2 * TC_PSTAGES + R), e_empty = cx.bars + 8u * (2 * TC_PSTAGES + TC_ESTAGES + R);
-    if (KB == 0) {
+    if (KB == G) {
         if (!__all_sync(0xffffffffu, mbar_wait(p_full, p_parity, cx.abort_flag, 3))) return false;
     }
     const uint32_t src = cx.p_ring + cx.lds_off[KB];
-    const uint2 a  = lds64<S * TC_P_STAGE>(src);
+    const uint2 a  = TC_A_IN_TMEM ? lds64<S * TC_P_STAGE>(cx.p_ring + cx.a_lds_off[KB]) : lds64<S * TC_P_STAGE>(src);
     const uint2 b0 = lds64<S * TC_P_STAGE + TC_P_A>(src);
     const uint2 b1 = lds64<S * TC_P_STAGE + TC_P_A + 128 * TC_PK>(src);
-    if (KB == TC_KB_PER_STAGE - 1 || last_kb) {
+    if (KB == G + 2) {
+        // The packed slot is only ever refilled for a LATER stage, and a stage that short of
+        // 4 k-blocks is the last one, so an arrival that a tail skips is never waited for.
         __syncwarp();
         if (cx.lane == 0) mbar_arrive(p_empty);
     }
+    cx.pc_a  += __popc(a.x) + __popc(a.y);
+    cx.pc_b0 += __popc(b0.x) + __popc(b0.y);
+    cx.pc_b1 += __popc(b1.x) + __popc(b1.y);
     if (!__all_sync(0xffffffffu, mbar_wait(e_empty, E_PARITY, cx.abort_flag, 4))) return false;
-    tc_expand_half<R * TC_E_STAGE>(a, cx.sts_addr);
-    tc_expand_half<R * TC_E_STAGE + TC_E_A>(b0, cx.sts_addr);
-    tc_expand_half<R * TC_E_STAGE + TC_E_A + 128 * 128>(b1, cx.sts_addr);
+    if (TC_A_IN_TMEM) {
+        tc_fence_after();
+        uint32_t w[16];
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[8 * q + j] = tc_expand4<false>(q == 0 ? a.x : a.y, j);
+        tc_st16(cx.a_taddr + (uint32_t)(R * TC_A_COLS), w);
+    } else {
+        tc_expand_half<R * TC_E_STAGE, false>(a, cx.sts_addr);
+    }
+    tc_expand_half<R * TC_E_STAGE + TC_E_A, true>(b0, cx.sts_addr);
+    tc_expand_half<R * TC_E_STAGE + TC_E_A + 128 * 128, true>(b1, cx.sts_addr);
+    if (TC_A_IN_TMEM) { tc_wait_st(); tc_fence_before(); }
     fence_proxy_async_smem();
     __syncwarp();
     if (cx.lane == 0) mbar_arrive(e_full);
     return true;
 }
 
-template <int U>
-__device__ __forceinline__ bool tc_expander_steps(const ExpanderCtx& cx, int32_t i0, int32_t nkb, uint32_t p_parity) {
+template <int G, int U>
+__device__ __forceinline__ bool tc_expander_steps(ExpanderCtx& cx, int32_t i0, int32_t nkb, uint32_t p_parity) {
     if constexpr (U < 12) {
         if (i0 + U >= nkb) return true;
-        if (!tc_expander_step<U>(cx, p_parity, i0 + U == nkb - 1)) return false;
-        return tc_expander_steps<U + 1>(cx, i0, nkb, p_parity);
+        if constexpr ((U & 1) == G) {
+            if (!tc_expander_step<G, U>(cx, p_parity)) return false;
+        }
+        return tc_expander_steps<G, U + 1>(cx, i0, nkb, p_parity);
     } else {
         return true;
     }
@@ -211,7 +272,7 @@ __device__ __forceinline__ bool tc_expander_steps(const ExpanderCtx& cx, int32_t
 template <bool PACK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    int64_t M, int64_t N, int32_t nkb /* 128-bit k-blocks */, int32_t kcorr /* 64*Kp - K */,
+                    int64_t M, int64_t N, int32_t nkb /* 128-bit k-blocks */, int32_t klogical /* K */,
                     int32_t* __restrict__ C, int64_t ldc,
                     const float* __restrict__ scale, uint32_t* __restrict__ out32, int64_t halves_per_row, int mode) {
     extern __shared__ uint8_t tc_smem_raw[];
@@ -238,13 +299,17 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (2 * TC_PSTAGES + 2 * TC_ESTAGES + 2));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (2 * TC_PSTAGES + 2 * TC_ESTAGES + 2) + 4);
 
+    int* pa_s = reinterpret_cast<int*>(gbars + 256);      // set bits per A row of the tile
+    int* pb_s = pa_s + TC_BM;                             // set bits per B row of the tile
+
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t m0 = (int64_t)blockIdx.y * TC_BM, n0 = (int64_t)blockIdx.x * TC_BN;
     const int32_t nstages = (nkb + TC_KB_PER_STAGE - 1) / TC_KB_PER_STAGE;
 
+    if (tid < TC_BM + TC_BN) pa_s[tid] = 0;
     if (tid == 0) {
         for (int s = 0; s < TC_PSTAGES; ++s) { mbar_init(p_full(s), 1); mbar_init(p_empty(s), TC_EXP_WARPS); }
-        for (int s = 0; s < TC_ESTAGES; ++s) { mbar_init(e_full(s), TC_EXP_WARPS); mbar_init(e_empty(s), 1); }
+        for (int s = 0; s < TC_ESTAGES; ++s) { mbar_init(e_full(s), TC_GROUP_WARPS); mbar_init(e_empty(s), 1); }
         mbar_init(acc_full, 1);
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -298,7 +363,16 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const uint64_t bdesc = tc_smem_desc(e_ring + r * TC_E_STAGE + TC_E_A);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)      // 32 bytes of K per instruction: +2 in the encoded address
-                    tc_mma_i8(tmem, adesc + 2u * k, bdesc + 2u * k, TC_IDESC, (i > 0 || k > 0) ? 1u : 0u);
+#ifdef BB_EXP_NO_MMA      // timing experiment only: results are wrong
+                    if (i == 0 && k == 0)
+#endif
+                {
+                    if (TC_A_IN_TMEM)
+                        tc_mma_i8_ts(tmem, tmem + (uint32_t)(TC_ACC_COLS + r * TC_A_COLS + 8 * k), bdesc + 2u * k, TC_IDESC,
+                                     (i > 0 || k > 0) ? 1u : 0u);
+                    else
+                        tc_mma_i8(tmem, adesc + 2u * k, bdesc + 2u * k, TC_IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                }
                 tc_commit(e_empty(r));
             }
             if (ok) tc_commit(acc_full);
@@ -309,29 +383,52 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     } else {
         // ================= expanders, then epilogue =================
-        const int erow = tid >> 1, half = tid & 1;       // rows erow (A), erow and erow+128 (B)
+        const int group = warp / TC_GROUP_WARPS, gwarp = warp % TC_GROUP_WARPS, gtid = tid % (TC_GROUP_WARPS * 32);
+        const int erow = gtid >> 1, half = gtid & 1;     // B rows erow and erow + 128 of this group's k-blocks
         ExpanderCtx cx;
         cx.bars = bars; cx.p_ring = p_ring; cx.abort_flag = abort_flag; cx.lane = lane;
+        cx.pc_a = cx.pc_b0 = cx.pc_b1 = 0;
 #pragma unroll
         for (int kb = 0; kb < 4; ++kb)       // packed 8 bytes of (row, k-block, half) under SWIZZLE_64B
             cx.lds_off[kb] = (uint32_t)(erow * TC_PK + (((kb ^ (erow >> 1)) & 3) << 4) + half * 8);
 #pragma unroll
         for (int c = 0; c < 4; ++c)          // chunk 4*half + c of the 128-byte operand row under SWIZZLE_128B
             cx.sts_addr[c] = e_ring + (uint32_t)(erow * 128 + (((4 * half + c) ^ (erow & 7)) << 4));
+        int arow = erow;
+        if (TC_A_IN_TMEM)
+        {   // A through TMEM: a thread can only write its own TMEM lane, 32 * (warp % 4) + lane
+            arow = (gwarp & 3) * 32 + lane;
+            const int ahalf = gwarp >> 2;
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb)
+                cx.a_lds_off[kb] = (uint32_t)(arow * TC_PK + (((kb ^ (arow >> 1)) & 3) << 4) + ahalf * 8);
+            cx.a_taddr = tmem + ((uint32_t)((gwarp & 3) * 32) << 16) + (uint32_t)(TC_ACC_COLS + ahalf * 16);
+        }
         bool ok = true;
         for (int32_t i0 = 0; i0 < nkb && ok; i0 += 12)
-            ok = tc_expander_steps<0>(cx, i0, nkb, (uint32_t)((i0 / 12) & 1));
+            ok = group == 0 ? tc_expander_steps<0, 0>(cx, i0, nkb, (uint32_t)((i0 / 12) & 1))
+                            : tc_expander_steps<1, 0>(cx, i0, nkb, (uint32_t)((i0 / 12) & 1));
+        // row popcounts of the tile: every thread adds what it saw (half rows, alternate k-blocks)
+        atomicAdd(pa_s + arow, cx.pc_a);
+        atomicAdd(pb_s + erow, cx.pc_b0);
+        atomicAdd(pb_s + erow + 128, cx.pc_b1);
+        asm volatile("bar.sync 1, %0;" :: "n"(TC_EXP_WARPS * 32) : "memory");     // all expander warps, whatever `ok` is
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, 5));
         if (ok) {
             tc_fence_after();
-            const int quarter = warp & 3, chalf = warp >> 2;
+            const int quarter = warp & 3, cblock = warp >> 2;     // 16 warps: 4 lane quarters x 4 blocks of 64 columns
             const int64_t m = m0 + quarter * 32 + lane;
+            // C = K - 2*(pa + pb) + 4*popcount(a & b), popcount(a & b) = acc >> 7
+            const int32_t row_term = klogical - 2 * pa_s[quarter * 32 + lane];
 #pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                const int col = chalf * 128 + cc * 32;
+            for (int cc = 0; cc < 2; ++cc) {
+                const int col = cblock * 64 + cc * 32;
                 uint32_t v[32];
                 tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col, v);
                 tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    v[j] = (uint32_t)(row_term - 2 * pb_s[col + j] + 4 * (int32_t)(v[j] >> 7));
                 const int64_t n = n0 + col;
                 if (!PACK) {
                     if (m < M) {
@@ -339,11 +436,10 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<int4*>(dst + j) = make_int4(((int32_t)v[j] >> 12) - kcorr, ((int32_t)v[j + 1] >> 12) - kcorr,
-                                                                             ((int32_t)v[j + 2] >> 12) - kcorr, ((int32_t)v[j + 3] >> 12) - kcorr);
+                                *reinterpret_cast<int4*>(dst + j) = make_int4((int32_t)v[j], (int32_t)v[j + 1], (int32_t)v[j + 2], (int32_t)v[j + 3]);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) if (n + j < N) dst[j] = ((int32_t)v[j] >> 12) - kcorr;
+                            for (int j = 0; j < 32; ++j) if (n + j < N) dst[j] = (int32_t)v[j];
                         }
                     }
                 } else {
@@ -351,7 +447,7 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         if (n + j < N) {
-                            const float y = __ldg(scale + n + j) * (float)(((int32_t)v[j] >> 12) - kcorr);
+                            const float y = __ldg(scale + n + j) * (float)(int32_t)v[j];
                             const bool b = mode == BRUTE_SIGN_GE0 ? (y >= 0.0f) : (y > 0.0f);
                             bits |= (b ? 1u : 0u) << j;
                         }
@@ -406,7 +502,7 @@ static bool tc5_make_map(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t
 // stride rule), 16-byte aligned bases, tile counts within the grid limits.
 static bool tc5_accepts(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp) {
     return Kp > 0 && (Kp % 2) == 0 && aligned16(A) && aligned16(B) && M > 0 && N > 0 &&
-           (M + TC_BM - 1) / TC_BM <= 65535 && Kp * 64 < (1ll << 19);   // 4096 * K must fit int32
+           (M + TC_BM - 1) / TC_BM <= 65535 && Kp * 64 < (1ll << 24);   // 128 * K must fit int32
 }
 
 static int tc5_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp, int64_t K,
@@ -418,21 +514,21 @@ static int tc5_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, i
     static bool attr_set[2] = {false, false};
     const dim3 grid((unsigned)((N + TC_BN - 1) / TC_BN), (unsigned)((M + TC_BM - 1) / TC_BM));
     const int32_t nkb = (int32_t)(Kp / 2);
-    const int32_t kcorr = (int32_t)(64 * Kp - K);
+    const int32_t klogical = (int32_t)K;
     if (!pack) {
         if (!attr_set[0]) {
             if (cudaFuncSetAttribute(k_xnor_gemm_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess)
                 return BRUTE_ERR_LAUNCH;
             attr_set[0] = true;
         }
-        k_xnor_gemm_tcgen05<false><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, kcorr, C, ldc, nullptr, nullptr, 0, 0);
+        k_xnor_gemm_tcgen05<false><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, klogical, C, ldc, nullptr, nullptr, 0, 0);
     } else {
         if (!attr_set[1]) {
             if (cudaFuncSetAttribute(k_xnor_gemm_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess)
                 return BRUTE_ERR_LAUNCH;
             attr_set[1] = true;
         }
-        k_xnor_gemm_tcgen05<true><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, kcorr, nullptr, 0, scale,
+        k_xnor_gemm_tcgen05<true><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, klogical, nullptr, 0, scale,
                                                                     reinterpret_cast<uint32_t*>(out), 2 * ((N + 63) / 64), mode);
     }
     return launch_status();
