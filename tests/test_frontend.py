@@ -1,11 +1,13 @@
-"""Host-side logic of the front end on CPU tensors.
+"""The front end (brute.Tensor, factories, fast helpers) against torch.bool.
 
-The product has CUDA kernels only; here the CPU dispatch key of torch.ops.brute.*
-is bound to the oracle (tests/conftest.py) so that the subclass state machine --
-lazy bool storage, version-tracked re-pack, packed-domain fast paths, the t()
-source for matmul -- can be exercised without a GPU. The checker is torch.bool
-itself, as in the reference's op catalog (tests/ops_catalog.py): run the same
-function on a bool tensor and on the bit1 tensor and compare.
+Every test runs twice: on CUDA tensors (marked gpu; the product's kernels) and on
+CPU tensors. The product has CUDA kernels only; for the CPU run the CPU dispatch
+key of torch.ops.brute.* is bound to the oracle (tests/conftest.py) so that the
+subclass state machine -- lazy bool storage, version-tracked re-pack,
+packed-domain fast paths, the t() source for matmul -- is exercised without a GPU.
+The checker is torch.bool itself, as in the reference's op catalog
+(tests/ops_catalog.py): run the same function on a bool tensor and on the bit1
+tensor and compare.
 """
 import copy
 import io
@@ -15,11 +17,22 @@ import numpy as np
 import pytest
 import torch
 
-pytestmark = pytest.mark.usefixtures("cpu_ops")
+DEV = "cpu"
+
+
+@pytest.fixture(scope="module", params=["cpu", pytest.param("cuda", marks=pytest.mark.gpu)], autouse=True)
+def device(request, lib_built):
+    global DEV
+    if request.param == "cpu":
+        import conftest
+        conftest.install_oracle_cpu_ops()
+    DEV = request.param
+    yield request.param
+    DEV = "cpu"
 
 
 @pytest.fixture(scope="module")
-def brute(cpu_ops):
+def brute(device):
     import brute_b200
     return brute_b200
 
@@ -29,14 +42,25 @@ def b1(brute, t):
 
 
 def as_bool(x):
+    """Plain CPU bool view of a brute tensor (materialises a lazy one)."""
     if hasattr(x, "_ensure_bool_valid"):
         x._ensure_bool_valid()
-        return x.as_subclass(torch.Tensor)
-    return x
+        x = x.as_subclass(torch.Tensor)
+    return x.cpu() if isinstance(x, torch.Tensor) else x
 
 
 def rnd(shape, seed=0, p=0.5):
-    return torch.rand(shape, generator=torch.Generator().manual_seed(seed)) < p
+    """Seeded bool tensor on the device under test (generated on the CPU so both runs see the same bits)."""
+    return (torch.rand(shape, generator=torch.Generator().manual_seed(seed)) < p).to(DEV)
+
+
+def cpu(t):
+    return t.as_subclass(torch.Tensor).cpu() if isinstance(t, torch.Tensor) else t
+
+
+def same(a, b):
+    """torch.equal on CPU copies, so that a materialised view and its torch.bool twin can sit on any device."""
+    return torch.equal(cpu(a), cpu(b))
 
 
 SHAPES = [(16,), (4, 8), (3, 13), (13,), (2, 3, 65), (5, 64), (2, 128)]
@@ -56,30 +80,30 @@ def test_dtype_sentinel(brute):
 
 def test_float_threshold_known_answer(brute):
     # reference tests/unit/test_dtype.py:79-83: [-1, 0, 0.5, 1] -> [F, F, T, T]
-    x = brute.tensor([-1.0, 0.0, 0.5, 1.0], dtype=torch.float32).to(brute.bit1)
-    assert torch.equal(as_bool(x), torch.tensor([False, False, True, True]))
-    y = brute.tensor([0, 1, 0, 1, 1], dtype=torch.int32).to(brute.bit1)
-    assert torch.equal(as_bool(y), torch.tensor([False, True, False, True, True]))
+    x = brute.tensor([-1.0, 0.0, 0.5, 1.0], dtype=torch.float32, device=DEV).to(brute.bit1)
+    assert same(as_bool(x), torch.tensor([False, False, True, True]))
+    y = brute.tensor([0, 1, 0, 1, 1], dtype=torch.int32, device=DEV).to(brute.bit1)
+    assert same(as_bool(y), torch.tensor([False, True, False, True, True]))
 
 
 def test_unpack_pm1_known_answer(brute):
-    a = brute.tensor([True, False, True, True, False], dtype=brute.bit1)
-    assert torch.equal(a.unpack_pm1(), torch.tensor([1.0, -1.0, 1.0, 1.0, -1.0]))
+    a = brute.tensor([True, False, True, True, False], dtype=brute.bit1, device=DEV)
+    assert same(a.unpack_pm1(), torch.tensor([1.0, -1.0, 1.0, 1.0, -1.0]))
 
 
 @pytest.mark.parametrize("shape", SHAPES)
 def test_roundtrip_and_reductions(brute, shape):
     src = rnd(shape, 1)
     x = b1(brute, src)
-    assert torch.equal(as_bool(x.bool()), src)
+    assert same(as_bool(x.bool()), src)
     assert int(x.popcount()) == int(src.sum()) == int(x.sum()) == int(torch.count_nonzero(x))
     assert int(x.word_popcount().as_subclass(torch.Tensor).long().sum()) == int(src.sum())
     assert bool(torch.any(x)) == bool(src.any()) and bool(torch.all(x)) == bool(src.all())
-    assert torch.equal(as_bool(torch.any(x, dim=-1)), src.any(dim=-1))
-    assert torch.equal(as_bool(torch.all(x, -1)), src.all(dim=-1))
+    assert same(as_bool(torch.any(x, dim=-1)), src.any(dim=-1))
+    assert same(as_bool(torch.all(x, -1)), src.all(dim=-1))
     if len(shape) >= 2:
-        assert torch.equal(as_bool(x.any(dim=0)), src.any(dim=0))
-        assert torch.equal(as_bool(x.all(dim=0, keepdim=True)), src.all(dim=0, keepdim=True))
+        assert same(as_bool(x.any(dim=0)), src.any(dim=0))
+        assert same(as_bool(x.all(dim=0, keepdim=True)), src.all(dim=0, keepdim=True))
 
 
 @pytest.mark.parametrize("shape", SHAPES)
@@ -98,7 +122,7 @@ def test_bitwise_parity_with_bool(brute, shape):
     for name, (got, want) in cases.items():
         assert got.dtype == brute.bit1, name
         assert got.__dict__.get("_bool_dirty") is True, f"{name}: packed-domain result should be lazy"
-        assert torch.equal(as_bool(got), want), name
+        assert same(as_bool(got), want), name
         assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
     assert int(a.hamming(b)) == int((sa ^ sb).sum()) == int(brute.hamming(a, b))
     assert torch.equal(a, a.clone()) and (not torch.equal(a, ~a) or a.numel() == 0)
@@ -109,7 +133,7 @@ def test_invert_pad_safe_sizes(brute):
         src = rnd((n,), n)
         inv = ~b1(brute, src)
         assert int(inv.popcount()) == n - int(src.sum())
-        assert torch.equal(as_bool(inv), ~src)
+        assert same(as_bool(inv), ~src)
 
 
 def test_inplace_ops_touch_only_packed(brute):
@@ -117,10 +141,10 @@ def test_inplace_ops_touch_only_packed(brute):
     a, b = b1(brute, sa), b1(brute, sb)
     a &= b
     assert a.__dict__["_bool_dirty"] is True
-    assert torch.equal(as_bool(a), sa & sb)
+    assert same(as_bool(a), sa & sb)
     a |= b
     a ^= b
-    assert torch.equal(as_bool(a), ((sa & sb) | sb) ^ sb)
+    assert same(as_bool(a), ((sa & sb) | sb) ^ sb)
 
 
 def test_version_counter_repacks_after_bool_write(brute):
@@ -147,7 +171,7 @@ def test_lazy_bool_materialises_once(brute):
     assert c.__dict__["_bool_dirty"] is True
     _ = c + 0                                             # a generic op does
     assert c.__dict__["_bool_dirty"] is False
-    assert torch.equal(as_bool(c), as_bool(a) ^ as_bool(b))
+    assert same(as_bool(c), as_bool(a) ^ as_bool(b))
 
 
 @pytest.mark.parametrize("shape", [(4, 64), (3, 13), (2, 3, 128), (2, 5, 7)])
@@ -161,7 +185,7 @@ def test_view_ops_parity(brute, shape):
         lambda t: t.permute(*reversed(range(t.dim()))), lambda t: t.contiguous(),
         lambda t: t.movedim(0, -1), lambda t: torch.flip(t, [0]), lambda t: t[0], lambda t: t[1:],
         lambda t: t.view(t.shape), lambda t: t.repeat(*([2] + [1] * (t.dim() - 1))),
-        lambda t: torch.index_select(t, 0, torch.tensor([1, 0, 1])),
+        lambda t: torch.index_select(t, 0, torch.tensor([1, 0, 1], device=DEV)),
         lambda t: t.repeat_interleave(2, dim=0),
     ]
     if len(shape) >= 3:
@@ -171,7 +195,7 @@ def test_view_ops_parity(brute, shape):
         got, want = fn(x), fn(src)
         assert got.dtype == brute.bit1, i
         assert tuple(got.shape) == tuple(want.shape), i
-        assert torch.equal(as_bool(got), want), i
+        assert same(as_bool(got), want), i
         assert int(got.popcount()) == int(want.sum()), i
 
 
@@ -184,7 +208,7 @@ def test_setitem_fast_paths(brute):
     x[:, 69] = True; ref[:, 69] = True
     x[..., 3] = False; ref[..., 3] = False
     x[0, 5] = True; ref[0, 5] = True                      # generic path
-    assert torch.equal(as_bool(x), ref) and int(x.popcount()) == int(ref.sum())
+    assert same(as_bool(x), ref) and int(x.popcount()) == int(ref.sum())
     with pytest.raises(IndexError):
         x[:, 70] = True
 
@@ -194,58 +218,58 @@ def test_matmul_paths(brute):
     sa, sb = rnd((M, K), 12), rnd((N, K), 13)
     a, b = b1(brute, sa), b1(brute, sb)
     want = ((sa.float() * 2 - 1) @ (sb.float() * 2 - 1).t()).to(torch.int32)
-    assert torch.equal(a @ b, want)                        # B stored (N, K)
-    assert torch.equal(a @ b.t(), want)                    # via _t_source
-    assert torch.equal(torch.matmul(a, b.t()), want)
-    assert torch.equal(torch.mm(a, b.transpose(0, 1)), want)
-    assert torch.equal(brute.matmul(a, b), want)
-    assert torch.equal(brute.matmul_packed(a._packed_buf, b._packed_buf, K), want)
+    assert same(a @ b, want)                        # B stored (N, K)
+    assert same(a @ b.t(), want)                    # via _t_source
+    assert same(torch.matmul(a, b.t()), want)
+    assert same(torch.mm(a, b.transpose(0, 1)), want)
+    assert same(brute.matmul(a, b), want)
+    assert same(brute.matmul_packed(a._packed_buf, b._packed_buf, K), want)
     assert (a @ b).dtype == torch.int32 and not isinstance(a @ b, brute.Tensor)
 
 
 def test_factories(brute):
     for size in [(5,), (3, 70), (2, 64)]:
-        z, o = brute.zeros(*size, dtype=brute.bit1), brute.ones(size, dtype=brute.bit1)
+        z, o = brute.zeros(*size, dtype=brute.bit1, device=DEV), brute.ones(size, dtype=brute.bit1, device=DEV)
         assert int(z.popcount()) == 0 and int(o.popcount()) == int(np.prod(size))
         assert bool(as_bool(o).all()) and not bool(as_bool(z).any())
-        e = brute.empty(*size, dtype=brute.bit1)
+        e = brute.empty(*size, dtype=brute.bit1, device=DEV)
         assert int(e.popcount()) <= int(np.prod(size))
-        f = brute.full(size, 1, dtype=brute.bit1)
+        f = brute.full(size, 1, dtype=brute.bit1, device=DEV)
         assert int(f.popcount()) == int(np.prod(size))
-    g = torch.Generator().manual_seed(3)
-    r = brute.randn(4, 100, dtype=brute.bit1, generator=g)
-    ref = torch.randn(4, 100, generator=torch.Generator().manual_seed(3)) >= 0
-    assert torch.equal(as_bool(r), ref)
-    ri = brute.randint(0, 2, (128,), dtype=brute.bit1)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    r = brute.randn(4, 100, dtype=brute.bit1, generator=g, device=DEV)
+    ref = torch.randn(4, 100, generator=torch.Generator(device=DEV).manual_seed(3), device=DEV) >= 0
+    assert same(as_bool(r), ref)
+    ri = brute.randint(0, 2, (128,), dtype=brute.bit1, device=DEV)
     assert ri.dtype == brute.bit1 and 0 <= int(ri.popcount()) <= 128
     assert brute.zeros_like(r).dtype == brute.bit1 and brute.ones_like(r, dtype=torch.float32).dtype == torch.float32
     assert isinstance(brute.arange(5), brute.Tensor) and brute.nn is None and brute.optim is None
 
 
 def test_randomize_keeps_pad_bits_zero(brute):
-    a = brute.zeros(3, 1003, dtype=brute.bit1)
+    a = brute.zeros(3, 1003, dtype=brute.bit1, device=DEV)
     a.randomize_()
     assert 0 < int(a.popcount()) < 3 * 1003
     assert int(a.popcount()) == int(as_bool(a.bool()).sum())
 
 
 def test_type_errors(brute):
-    a = brute.zeros(8, dtype=brute.bit1)
-    plain = torch.zeros(8, dtype=torch.bool).as_subclass(brute.Tensor)
+    a = brute.zeros(8, dtype=brute.bit1, device=DEV)
+    plain = torch.zeros(8, dtype=torch.bool, device=DEV).as_subclass(brute.Tensor)
     with pytest.raises(TypeError):
-        a.hamming(torch.zeros(8, dtype=torch.bool))
+        a.hamming(torch.zeros(8, dtype=torch.bool, device=DEV))
     with pytest.raises(ValueError):
-        a.hamming(brute.zeros(16, dtype=brute.bit1))
+        a.hamming(brute.zeros(16, dtype=brute.bit1, device=DEV))
     for fn in (lambda: plain.word_popcount(), lambda: plain.randomize_(), lambda: plain.unpack_pm1()):
         with pytest.raises(TypeError):
             fn()
-    assert int(brute.Tensor(torch.ones(4, dtype=torch.bool)).popcount()) == 4
+    assert int(brute.Tensor(torch.ones(4, dtype=torch.bool, device=DEV)).popcount()) == 4
 
 
 def test_mixed_bool_does_not_promote(brute):
     sa, sb = rnd((4, 9), 14), rnd((4, 9), 15)
     out = torch.logical_and(b1(brute, sa), sb)
-    assert out.dtype == torch.bool and torch.equal(out.as_subclass(torch.Tensor), sa & sb)
+    assert out.dtype == torch.bool and same(out, sa & sb)
     picked = b1(brute, sa)[sb]                           # mask indexing keeps bit1
     assert picked.dtype == brute.bit1
     assert int(torch.argmax(b1(brute, sa).flatten())) == int(torch.argmax(sa.flatten().to(torch.uint8)))
@@ -255,21 +279,21 @@ def test_pickle_deepcopy_numpy_repr(brute):
     src = rnd((3, 70), 16)
     x = b1(brute, src) ^ b1(brute, torch.zeros_like(src))          # a lazy one
     y = pickle.loads(pickle.dumps(x))
-    assert y.dtype == brute.bit1 and torch.equal(as_bool(y), src)
+    assert y.dtype == brute.bit1 and same(as_bool(y), src)
     buf = io.BytesIO()
     torch.save(x, buf)
     buf.seek(0)
     z = torch.load(buf, weights_only=False)
-    assert torch.equal(as_bool(z), src)
+    assert same(as_bool(z), src)
     d = copy.deepcopy(x)
-    assert d.dtype == brute.bit1 and torch.equal(as_bool(d), src) and int(d.popcount()) == int(src.sum())
-    assert np.array_equal(np.asarray(x), src.numpy())
+    assert d.dtype == brute.bit1 and same(as_bool(d), src) and int(d.popcount()) == int(src.sum())
+    assert np.array_equal(np.asarray(x), src.cpu().numpy())
     assert "brute.Tensor(" in repr(x) and "dtype=brute.bit1" in repr(x)
 
 
 def test_empty_and_zero_dim(brute):
     for shape in [(0,), (3, 0), (0, 5)]:
-        x = b1(brute, torch.zeros(shape, dtype=torch.bool))
+        x = b1(brute, torch.zeros(shape, dtype=torch.bool, device=DEV))
         assert tuple(x.shape) == shape and int(x.popcount()) == 0
-    s = brute.Tensor(torch.tensor(True), dtype=brute.bit1)
+    s = brute.Tensor(torch.tensor(True, device=DEV), dtype=brute.bit1)
     assert s.dim() == 0 and int(s.popcount()) == 1 and bool(as_bool(~s)) is False
