@@ -49,7 +49,8 @@ def parse_args():
     ap.add_argument("--size", type=int, default=16384, help="M=N=K (profiling runs use smaller sizes)")
     ap.add_argument("--op", default="gemm",
                     help="time ONE op alone (for profiler captures): gemm | pack_sign | pack_bool | unpack_bool | "
-                         "unpack_pm1 | popcount_total | hamming_total | word_popcount | xor | not | attention | mlp")
+                         "unpack_pm1 | popcount_total | hamming_total | word_popcount | xor | not | attention | mlp | "
+                         "pack_bool_4097 | unpack_bool_4097 | memset")
     ap.add_argument("--log2-bits", type=int, default=28, help="size of the bandwidth ops under --op")
     ap.add_argument("--att", default="2,8,4096,128", help="B,H,S,D of --op attention")
     return ap.parse_args()
@@ -73,6 +74,8 @@ def cpu_gemm_sample(size: int, target_s: float = 10.0):
     import numpy as np
     from oracle import c_oracle as co
     co.build()
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm uses every core it may run on
+    co.set_num_threads(len(os.sched_getaffinity(0)))
     rng = np.random.default_rng(1234)
     kp = size // 64
     probe = min(1024, size)
@@ -314,7 +317,8 @@ def run_ours(args):
         del gathered
 
     if rank == 0 and not args.no_extra and size == 16384:
-        extra.update(secondary_workloads(dev, peaks, flush, sync))
+        # rank 0 alone runs these: synchronise the device only, no collective
+        extra.update(secondary_workloads(dev, peaks, flush, torch.cuda.synchronize))
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -463,6 +467,16 @@ def run_single_op(args):
         if args.op == "pack_bool":
             xb = ops.unpack_bool(p, [n])
             fn, alg = (lambda: ops.pack_bool(xb)), n + n // 8
+        elif args.op in ("pack_bool_4097", "unpack_bool_4097"):
+            # BASELINE config 2's ragged case: bool [4096, 4097], 65 words per row, 1 valid bit in the last
+            xr = torch.rand((4096, 4097), generator=g, device=dev) < 0.3
+            pr = ops.pack_bool(xr)
+            alg = 4096 * 4097 + 4096 * 65 * 8
+            fn = (lambda: ops.pack_bool(xr)) if args.op == "pack_bool_4097" else (lambda: ops.unpack_bool(pr, [4096, 4097]))
+        elif args.op == "memset":
+            # write-only reference: how fast this GPU stores, to read the unpack numbers against
+            buf = torch.empty(n, dtype=torch.uint8, device=dev)
+            fn, alg = buf.zero_, n
         else:
             fn, alg = table[args.op]
     ts = time_steps(fn, args.steps, args.warmup, flush_buf.zero_, torch.cuda.synchronize)

@@ -13,20 +13,23 @@
 // than an int8 GEMM); the expansion is paid per CTA on chip. The ALU pipe (16 lanes/clk per SM
 // quarter) is the scarce unit of the expansion, which is why the op count per byte matters.
 //
-// Per CTA (one 128 x 256 tile of C, accumulator = 256 TMEM columns):
-//   warp 8      TMA producer: packed A [128 rows x 64 B] and B [256 rows x 64 B]
-//               boxes (512 bits of K) into a 3-deep ring, SWIZZLE_64B.
-//   warps 0..7  expanders: per 128-bit k-block, each thread turns three 64-bit
-//               half rows into 3 x 64 int8 and stores them in the canonical
-//               K-major SWIZZLE_128B operand layout (3-deep ring), then
-//               fence.proxy.async + mbarrier arrive.
-//   warp 9      MMA issuer: 4 x tcgen05.mma (M128 N256 K32) per k-block,
-//               tcgen05.commit frees the operand slot; owns the TMEM allocation.
-//   warps 0..7  epilogue: tcgen05.ld 32x32b, K-correction, 128-bit stores (or the
-//               fused scale/sign/pack of the binarised MLP).
-// The order of the 128 k-positions inside a k-block is permuted by the
-// expansion (byte 4j+i of a 32-byte group holds bit 8i+j); A and B share the
-// permutation, which a dot product cannot see.
+// Per CTA (one 128 x 256 tile of C; accumulator = TMEM columns [0,256), A ring = columns [256,352)):
+//   warp 16      TMA producer: packed A [128 rows x 64 B] and B [256 rows x 64 B] boxes (512 bits
+//                of K) into a 3-deep ring, SWIZZLE_64B, cp.async.bulk.tensor + mbarrier complete_tx.
+//   warps 0..15  expanders, two groups of 8 warps that alternate k-blocks so that the latency
+//                chain of one group (ld.shared, logic ops, stores, fences, arrive) overlaps the
+//                other's. Per 128-bit k-block a thread expands one 64-bit half row of A and two of B.
+//                A never touches shared memory: the words go from registers into this thread's own
+//                TENSOR MEMORY lane (tcgen05.st) and the MMA reads A from TMEM, which takes a third
+//                of the stores and of the tensor core's operand reads off the shared-memory pipe.
+//                B goes into the canonical K-major SWIZZLE_128B layout (st.shared.v4, 3-deep ring),
+//                then fence.proxy.async + mbarrier arrive.
+//   warp 17      MMA issuer: 4 x tcgen05.mma (M128 N256 K32, A from TMEM, B from a shared-memory
+//                descriptor) per k-block; tcgen05.commit frees the slot; owns the TMEM allocation.
+//   warps 0..15  epilogue: tcgen05.ld 32x32b, popcount correction, 128-bit stores (or the fused
+//                scale/sign/pack of the binarised MLP).
+// The order of the 128 k-positions inside a k-block is permuted by the expansion (byte 4j+i of a
+// 32-byte group holds bit 8i+j); A and B share the permutation, which a dot product cannot see.
 //
 // Every mbarrier wait is bounded (about one second); a wait that gives up sets
 // the device status word and an abort flag, the CTA drains its copies, frees
@@ -43,19 +46,14 @@ constexpr int TC_PK = 64;                               // packed bytes of K per
 constexpr int TC_KB_PER_STAGE = 4;                      // 128-bit k-blocks per packed stage
 constexpr int TC_P_A = TC_BM * TC_PK, TC_P_B = TC_BN * TC_PK;
 constexpr int TC_P_STAGE = TC_P_A + TC_P_B;             // 24 KB
-constexpr int TC_E_A = TC_BM * 128, TC_E_B = TC_BN * 128;
-constexpr int TC_E_STAGE = TC_E_A + TC_E_B;             // 48 KB
+constexpr int TC_E_STAGE = TC_BN * 128;                 // expanded B of one k-block: 32 KB
 constexpr int TC_GROUP_WARPS = 8;                       // warps that expand one k-block together
 constexpr int TC_GROUPS = 2;                            // groups alternate k-blocks, so their latency chains overlap
 constexpr int TC_EXP_WARPS = TC_GROUP_WARPS * TC_GROUPS;
 constexpr int TC_THREADS = (TC_EXP_WARPS + 2) * 32;     // 576
-// The A operand (M = 128 rows) goes to TENSOR MEMORY, not shared memory: the expanders write their
-// int8 words straight from registers with tcgen05.st and the MMA reads A from TMEM, so only B's
-// 256 rows pay shared-memory store (and MMA read) bandwidth. 32 columns per k-block and ring slot.
-constexpr bool TC_A_IN_TMEM = true;
-constexpr int TC_A_COLS = 32;                           // 128 int8 of K per row = 32 columns of 32 bits
+constexpr int TC_A_COLS = 32;                           // A of one k-block: 128 int8 of K per row = 32 columns of 32 bits
 constexpr int TC_ACC_COLS = 256;
-constexpr int TC_TMEM_COLS = TC_A_IN_TMEM ? 512 : 256;  // power of two >= 256 + 3 * 32
+constexpr int TC_TMEM_COLS = 512;                       // power of two >= 256 + 3 * 32
 constexpr int TC_ROWPOP_BYTES = (TC_BM + TC_BN) * 4;      // pa[128], pb[256] of the tile
 constexpr int TC_SMEM = TC_ESTAGES * TC_E_STAGE + TC_PSTAGES * TC_P_STAGE + 256 + TC_ROWPOP_BYTES + 1024;
 constexpr uint64_t TC_WAIT_NS = 1000000000ull;          // bound of every in-kernel wait
@@ -107,20 +105,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
         :: "r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
-#ifndef BB_EXP_NO_FENCE   // timing experiment only: results are wrong
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
+// D[tmem] (+)= A[tmem] * B[shared-memory descriptor]
 __device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
@@ -162,9 +154,6 @@ constexpr uint32_t TC_IDESC = (2u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(T
 // byte. B side (h already bit-reversed inside each byte): original bit j sits at position 7-j.
 template <bool IS_B>
 __device__ __forceinline__ uint32_t tc_expand4(uint32_t h, int j) {
-#ifdef BB_EXP_NO_ALU      // timing experiment only: results are wrong
-    return h + j;
-#endif
     return h & (0x01010101u << (IS_B ? 7 - j : j));
 }
 // reverse the bit order inside each byte of a packed word (B operand, once per 32 bits)
@@ -172,9 +161,6 @@ __device__ __forceinline__ uint32_t tc_brev_bytes(uint32_t g) { return __byte_pe
 
 template <int IMM>
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-#ifdef BB_EXP_NO_STS      // timing experiment only: results are wrong
-    if (a == 0x12345678u && b == c && d == 7u)
-#endif
     asm volatile("st.shared.v4.b32 [%0+%5], {%1,%2,%3,%4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "n"(IMM) : "memory");
 }
 template <int IMM>
@@ -188,16 +174,26 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 // chunks (16 bytes each) of the 128-byte operand row that this half owns.
 // dst[c] is the shared address of chunk c (swizzle applied), IMM a constant
 // offset (ring slot, operand, +128 rows).
-template <int IMM, bool IS_B>
-__device__ __forceinline__ void tc_expand_half(uint2 bits, const uint32_t (&dst)[4]) {
-    const uint32_t h[2] = {IS_B ? tc_brev_bytes(bits.x) : bits.x, IS_B ? tc_brev_bytes(bits.y) : bits.y};
+// 64 bits of a B row (one half of a 128-bit k-block) -> 64 int8 into the 4 chunks (16 bytes each)
+// of the 128-byte operand row that this half owns. dst[c] is the shared address of chunk c
+// (swizzle applied), IMM a constant offset (ring slot, +128 rows).
+template <int IMM>
+__device__ __forceinline__ void tc_expand_b_half(uint2 bits, const uint32_t (&dst)[4]) {
+    const uint32_t h[2] = {tc_brev_bytes(bits.x), tc_brev_bytes(bits.y)};
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
-            sts128<IMM>(dst[2 * q + c], tc_expand4<IS_B>(h[q], 4 * c + 0), tc_expand4<IS_B>(h[q], 4 * c + 1),
-                        tc_expand4<IS_B>(h[q], 4 * c + 2), tc_expand4<IS_B>(h[q], 4 * c + 3));
+            sts128<IMM>(dst[2 * q + c], tc_expand4<true>(h[q], 4 * c + 0), tc_expand4<true>(h[q], 4 * c + 1),
+                        tc_expand4<true>(h[q], 4 * c + 2), tc_expand4<true>(h[q], 4 * c + 3));
     }
+}
+// 64 bits of an A row -> 16 columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_expand_a_half(uint2 bits, uint32_t taddr) {
+    uint32_t w[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { w[j] = tc_expand4<false>(bits.x, j); w[8 + j] = tc_expand4<false>(bits.y, j); }
+    tc_st16(taddr, w);
 }
 
 // One k-block of the expander loop with every ring index a compile-time
@@ -205,7 +201,7 @@ __device__ __forceinline__ void tc_expand_half(uint2 bits, const uint32_t (&dst)
 // packed stage), so the only run-time state is the parity bit of the packed ring.
 struct ExpanderCtx {
     uint32_t bars, p_ring, lds_off[4], sts_addr[4];
-    uint32_t a_lds_off[4], a_taddr;      // A through TMEM: packed-bit offsets and TMEM address of this thread's half row
+    uint32_t a_lds_off[4], a_taddr;      // A: packed-bit offsets and TMEM address of this thread's half row
     int pc_a, pc_b0, pc_b1;              // set bits seen so far in this thread's half rows (for pa[m], pb[n])
     volatile int* abort_flag;
     int lane;
@@ -223,7 +219,7 @@ __device__ __forceinline__ bool tc_expander_step(ExpanderCtx& cx, uint32_t p_par
         if (!__all_sync(0xffffffffu, mbar_wait(p_full, p_parity, cx.abort_flag, 3))) return false;
     }
     const uint32_t src = cx.p_ring + cx.lds_off[KB];
-    const uint2 a  = TC_A_IN_TMEM ? lds64<S * TC_P_STAGE>(cx.p_ring + cx.a_lds_off[KB]) : lds64<S * TC_P_STAGE>(src);
+    const uint2 a  = lds64<S * TC_P_STAGE>(cx.p_ring + cx.a_lds_off[KB]);
     const uint2 b0 = lds64<S * TC_P_STAGE + TC_P_A>(src);
     const uint2 b1 = lds64<S * TC_P_STAGE + TC_P_A + 128 * TC_PK>(src);
     if (KB == G + 2) {
@@ -236,20 +232,12 @@ __device__ __forceinline__ bool tc_expander_step(ExpanderCtx& cx, uint32_t p_par
     cx.pc_b0 += __popc(b0.x) + __popc(b0.y);
     cx.pc_b1 += __popc(b1.x) + __popc(b1.y);
     if (!__all_sync(0xffffffffu, mbar_wait(e_empty, E_PARITY, cx.abort_flag, 4))) return false;
-    if (TC_A_IN_TMEM) {
-        tc_fence_after();
-        uint32_t w[16];
-#pragma unroll
-        for (int q = 0; q < 2; ++q)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) w[8 * q + j] = tc_expand4<false>(q == 0 ? a.x : a.y, j);
-        tc_st16(cx.a_taddr + (uint32_t)(R * TC_A_COLS), w);
-    } else {
-        tc_expand_half<R * TC_E_STAGE, false>(a, cx.sts_addr);
-    }
-    tc_expand_half<R * TC_E_STAGE + TC_E_A, true>(b0, cx.sts_addr);
-    tc_expand_half<R * TC_E_STAGE + TC_E_A + 128 * 128, true>(b1, cx.sts_addr);
-    if (TC_A_IN_TMEM) { tc_wait_st(); tc_fence_before(); }
+    tc_fence_after();
+    tc_expand_a_half(a, cx.a_taddr + (uint32_t)(R * TC_A_COLS));
+    tc_expand_b_half<R * TC_E_STAGE>(b0, cx.sts_addr);
+    tc_expand_b_half<R * TC_E_STAGE + 128 * 128>(b1, cx.sts_addr);
+    tc_wait_st();
+    tc_fence_before();
     fence_proxy_async_smem();
     __syncwarp();
     if (cx.lane == 0) mbar_arrive(e_full);
@@ -284,7 +272,7 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(tc_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* gbase = tc_smem_raw + (base - raw);
-    const uint32_t e_ring = base;                                    // TC_ESTAGES x 48 KB
+    const uint32_t e_ring = base;                                    // TC_ESTAGES x 32 KB (expanded B)
     const uint32_t p_ring = base + TC_ESTAGES * TC_E_STAGE;          // TC_PSTAGES x 24 KB
     const uint32_t bars = p_ring + TC_PSTAGES * TC_P_STAGE;
     uint8_t* gp_ring = gbase + TC_ESTAGES * TC_E_STAGE;
@@ -359,20 +347,11 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 ok = mbar_wait(e_full(r), (i / TC_ESTAGES) & 1, abort_flag, 2);
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t adesc = tc_smem_desc(e_ring + r * TC_E_STAGE);
-                const uint64_t bdesc = tc_smem_desc(e_ring + r * TC_E_STAGE + TC_E_A);
+                const uint64_t bdesc = tc_smem_desc(e_ring + r * TC_E_STAGE);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)      // 32 bytes of K per instruction: +2 in the encoded address
-#ifdef BB_EXP_NO_MMA      // timing experiment only: results are wrong
-                    if (i == 0 && k == 0)
-#endif
-                {
-                    if (TC_A_IN_TMEM)
-                        tc_mma_i8_ts(tmem, tmem + (uint32_t)(TC_ACC_COLS + r * TC_A_COLS + 8 * k), bdesc + 2u * k, TC_IDESC,
-                                     (i > 0 || k > 0) ? 1u : 0u);
-                    else
-                        tc_mma_i8(tmem, adesc + 2u * k, bdesc + 2u * k, TC_IDESC, (i > 0 || k > 0) ? 1u : 0u);
-                }
+                for (int k = 0; k < 4; ++k)      // 32 bytes of K per instruction: +2 in the encoded address, +8 TMEM columns
+                    tc_mma_i8_ts(tmem, tmem + (uint32_t)(TC_ACC_COLS + r * TC_A_COLS + 8 * k), bdesc + 2u * k, TC_IDESC,
+                                 (i > 0 || k > 0) ? 1u : 0u);
                 tc_commit(e_empty(r));
             }
             if (ok) tc_commit(acc_full);
@@ -394,16 +373,13 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
         for (int c = 0; c < 4; ++c)          // chunk 4*half + c of the 128-byte operand row under SWIZZLE_128B
             cx.sts_addr[c] = e_ring + (uint32_t)(erow * 128 + (((4 * half + c) ^ (erow & 7)) << 4));
-        int arow = erow;
-        if (TC_A_IN_TMEM)
-        {   // A through TMEM: a thread can only write its own TMEM lane, 32 * (warp % 4) + lane
-            arow = (gwarp & 3) * 32 + lane;
-            const int ahalf = gwarp >> 2;
+        // A: a thread can only write its own TMEM lane, 32 * (warp % 4) + lane: it expands that
+        // row of A, the half of the k-block given by gwarp / 4
+        const int arow = (gwarp & 3) * 32 + lane, ahalf = gwarp >> 2;
 #pragma unroll
-            for (int kb = 0; kb < 4; ++kb)
-                cx.a_lds_off[kb] = (uint32_t)(arow * TC_PK + (((kb ^ (arow >> 1)) & 3) << 4) + ahalf * 8);
-            cx.a_taddr = tmem + ((uint32_t)((gwarp & 3) * 32) << 16) + (uint32_t)(TC_ACC_COLS + ahalf * 16);
-        }
+        for (int kb = 0; kb < 4; ++kb)
+            cx.a_lds_off[kb] = (uint32_t)(arow * TC_PK + (((kb ^ (arow >> 1)) & 3) << 4) + ahalf * 8);
+        cx.a_taddr = tmem + ((uint32_t)((gwarp & 3) * 32) << 16) + (uint32_t)(TC_ACC_COLS + ahalf * 16);
         bool ok = true;
         for (int32_t i0 = 0; i0 < nkb && ok; i0 += 12)
             ok = group == 0 ? tc_expander_steps<0, 0>(cx, i0, nkb, (uint32_t)((i0 / 12) & 1))

@@ -184,8 +184,21 @@ def xnor_matmul_scale_sign_pack(A, B, scale, K: int, mode: int) -> torch.Tensor:
     return out
 
 
-def signed_bundle(W, V, D: int) -> torch.Tensor:
-    raise RuntimeError("signed_bundle: not built in brute_b200 (outside the bit1 GEMM/pack/popcount/attention path)")
+def signed_bundle(W: torch.Tensor, V: torch.Tensor, D: int) -> torch.Tensor:
+    _check(W.dim() == 3 and V.dim() == 3, "signed_bundle: W (B,M,N), V packed (B,N,Dp)")
+    _check(W.dtype == torch.int8, "signed_bundle: W must be int8")
+    B, M, N = W.shape
+    Dp = V.size(2)
+    _check(V.size(0) == B and V.size(1) == N, "signed_bundle: W (B,M,N) / V (B,N,Dp) batch or N mismatch")
+    _check(V.dtype == torch.int64 and 0 <= int(D) <= 64 * Dp, "signed_bundle: V must be int64 packed with D <= 64*Dp")
+    Wc, Vc = W.contiguous(), V.contiguous()
+    out = torch.empty((B, M, Dp), dtype=torch.int64, device=V.device)
+    if out.numel():
+        with torch.cuda.device(V.device):
+            L.check(_lib.brute_b200_signed_bundle(Wc.data_ptr() if Wc.numel() else None,
+                                                  Vc.data_ptr() if Vc.numel() else None, out.data_ptr(),
+                                                  B, M, N, Dp, int(D), _stream(V)), "signed_bundle")
+    return out
 
 
 # ---------------------------------------------------------------------------
@@ -372,6 +385,7 @@ def _register_fakes() -> None:
     reg("brute::select_packed")(lambda cond, A, B: torch.empty_like(A))
     reg("brute::row_any")(lambda A: A.new_empty(A.shape[:-1], dtype=torch.bool))
     reg("brute::row_all")(lambda A, last_dim_bits: A.new_empty(A.shape[:-1], dtype=torch.bool))
+    reg("brute::signed_bundle")(lambda W, V, D: V.new_empty((W.shape[0], W.shape[1], V.shape[2]), dtype=torch.int64))
     reg("brute::binary_attention")(lambda Qp, Kp, V, causal, scale: torch.empty_like(V))
 
 

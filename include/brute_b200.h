@@ -179,6 +179,14 @@ int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B,
                                          int64_t M, int64_t N, int64_t Kp, int64_t K,
                                          int mode, int impl, void* stream);
 
+/* ---- signed vote bundle ------------------------------------------------ */
+/* W int8 [B, M, N], V packed [B, N, Dp] words, D logical bits (D <= 64*Dp) ->
+ * out packed [B, M, Dp]: bit(b,m,d) = (sum_n W[b,m,n] * pm1(V[b,n,d]) >= 0), pad bits 0.
+ * Replaces cbrute::cuda::signed_bundle, cbrute/cuda/ops_cuda.cu:224-241 and k_signed_bundle,
+ * cbrute/cuda/kernels/signed_bundle.cuh:18-54 (CPU statement: cbrute/cpu/ops_cpu.cpp:164-213). */
+int brute_b200_signed_bundle(const int8_t* W, const uint64_t* V, uint64_t* out,
+                             int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D, void* stream);
+
 /* ---- binary attention -------------------------------------------------- */
 /* Qp, Kp_ [B, H, S, D/64] words (sign-binarised Q and K), V and O bf16
  * [B, H, S, D]; score(i,j) = (D - 2*popcount(q_i ^ k_j)) * scale, optional

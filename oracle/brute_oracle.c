@@ -349,6 +349,36 @@ void oracle_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B, cons
 }
 
 /* ------------------------------------------------------------------------
+ * signed_bundle: out[b,m,d] = sign(sum_n W[b,m,n] * pm1(V[b,n,d])), sign(0) = +1 (bit set), pad
+ * bits 0. Follows cbrute/cpu/ops_cpu.cpp:164-213 (int32 accumulator per (b,m), V read from its
+ * packed words, zero weights skipped).
+ * ---------------------------------------------------------------------- */
+void oracle_signed_bundle(const int8_t* W, const uint64_t* V, uint64_t* out,
+                          int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D) {
+#pragma omp parallel for schedule(static)
+    for (int64_t bm = 0; bm < B * M; ++bm) {
+        const int64_t b = bm / M;
+        int32_t* acc = (int32_t*)calloc((size_t)(Dp * 64 + 1), sizeof(int32_t));
+        const int8_t* wrow = W + bm * N;
+        for (int64_t n = 0; n < N; ++n) {
+            const int32_t w = wrow[n];
+            if (w == 0) continue;
+            const uint64_t* vrow = V + (b * N + n) * Dp;
+            for (int64_t dp = 0; dp < Dp; ++dp)
+                for (int bit = 0; bit < 64; ++bit)
+                    acc[dp * 64 + bit] += ((vrow[dp] >> bit) & 1ull) ? w : -w;
+        }
+        for (int64_t dp = 0; dp < Dp; ++dp) {
+            uint64_t word = 0;
+            for (int bit = 0; bit < 64; ++bit)
+                if (dp * 64 + bit < D && acc[dp * 64 + bit] >= 0) word |= 1ull << bit;
+            out[bm * Dp + dp] = word;
+        }
+        free(acc);
+    }
+}
+
+/* ------------------------------------------------------------------------
  * Binary attention: NO reference implementation exists (one docstring mention,
  * brute/fast.py:122-124); parity UNPINNED. Composition of reference semantics:
  * per (b,h): S = xnor_popcount_matmul(Q, K, D) (cbrute/cpu/ops_cpu.cpp:119-156)

@@ -52,6 +52,7 @@ def lib():
         L.oracle_row_all.argtypes = [p, p, i64, i64, i64]
         L.oracle_xnor_gemm.argtypes = [p, p, p, i64, i64, i64, i64, i64]
         L.oracle_xnor_gemm_scale_sign_pack.argtypes = [p, p, p, p, i64, i64, i64, i64, i32]
+        L.oracle_signed_bundle.argtypes = [p, p, p, i64, i64, i64, i64, i64]
         L.oracle_binary_attention.argtypes = [p, p, p, p, i64, i64, i64, i32, f32]
         _lib = L
     return _lib
@@ -221,6 +222,18 @@ def xnor_gemm_scale_sign_pack(A, B, scale, K: int, mode: int) -> np.ndarray:
     out = np.zeros((M, (N + 63) // 64), dtype=np.uint64)
     if M and N:
         lib().oracle_xnor_gemm_scale_sign_pack(_ptr(A), _ptr(B), _ptr(scale), _ptr(out), M, N, Kp, int(K), int(mode))
+    return out
+
+
+def signed_bundle(W: np.ndarray, V: np.ndarray, D: int) -> np.ndarray:
+    """W int8 [B, M, N], V packed [B, N, Dp] -> packed votes [B, M, Dp]."""
+    W = _c(W, np.int8)
+    V = _u64(V)
+    B, M, N = W.shape
+    Dp = V.shape[2]
+    out = np.zeros((B, M, Dp), dtype=np.uint64)
+    if out.size:
+        lib().oracle_signed_bundle(_ptr(W), _ptr(V), _ptr(out), B, M, N, Dp, int(D))
     return out
 
 

@@ -149,6 +149,8 @@ def install_oracle_cpu_ops():
     lib.impl("row_any", lambda A: torch.from_numpy(co.row_any(t2n(A))))
     lib.impl("row_all", lambda A, bits: torch.from_numpy(co.row_all(t2n(A), bits)))
 
+    lib.impl("signed_bundle", lambda W, V, D: n2t(co.signed_bundle(t2n(W), t2n(V), D), torch.int64))
+
     def randomize(out):
         out.random_()
         return out

@@ -330,6 +330,27 @@ def test_mlp_config4_chain(ops, co):
 
 
 # ---------------------------------------------------------------------------
+# signed_bundle
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("B,M,N,D", [(1, 1, 1, 1), (2, 5, 7, 70), (1, 33, 130, 128), (3, 64, 256, 64),
+                                     (2, 100, 1000, 200), (1, 32, 128, 4096)])
+def test_signed_bundle(ops, co, B, M, N, D):
+    import brute_b200 as brute
+    g = gen(B + M + N + D)
+    W = torch.randint(-3, 4, (B, M, N), generator=g, dtype=torch.int64).to(torch.int8)
+    v = torch.rand((B, N, D), generator=g) < 0.5
+    vp = ops.pack_bool(v.to(DEV))
+    got = ops.signed_bundle(W.to(DEV), vp, D)
+    assert np.array_equal(u64(got), co.signed_bundle(W.numpy(), u64(vp), D))
+    # through the front-end helper, against the +-1 integer contraction
+    out = brute.fast.signed_bundle(W.to(DEV), brute.Tensor(v.to(DEV), dtype=brute.bit1))
+    acc = torch.einsum("bmn,bnd->bmd", W.float(), v.float() * 2 - 1)
+    assert out.dtype == brute.bit1 and torch.equal(out.bool().as_subclass(torch.Tensor).cpu(), acc >= 0)
+    with pytest.raises(RuntimeError, match="must be int8"):
+        ops.signed_bundle(W.to(DEV).int(), vp, D)
+
+
+# ---------------------------------------------------------------------------
 # attention (parity unpinned: no reference kernel; oracle = composition)
 # ---------------------------------------------------------------------------
 ATT_TOL = 2e-2      # relative to the largest |output|, the tolerance the task states for bf16

@@ -151,3 +151,14 @@ def test_attention_vs_numpy(causal):
     got = co.binary_attention(co.pack_bool(q), co.pack_bool(k), v, causal, D ** -0.5)
     want = no.binary_attention(q, k, v, causal, D ** -0.5)
     assert np.abs(got - want).max() < 1e-5
+
+
+def test_signed_bundle_vs_numpy():
+    # out = sign(sum_n W * pm1(V)), sign(0) = +1, pad bits 0 (reference cbrute/cpu/ops_cpu.cpp:164-213)
+    rng = np.random.default_rng(21)
+    for B, M, N, D in [(1, 1, 1, 1), (2, 5, 7, 70), (1, 33, 130, 128), (3, 4, 16, 64)]:
+        W = rng.integers(-3, 4, size=(B, M, N)).astype(np.int8)
+        v = rng.random((B, N, D)) < 0.5
+        got = co.signed_bundle(W, co.pack_bool(v), D)
+        acc = np.einsum("bmn,bnd->bmd", W.astype(np.int32), np.where(v, 1, -1).astype(np.int32))
+        assert np.array_equal(got, no.pack_bool(acc >= 0)), (B, M, N, D)
