@@ -1,6 +1,6 @@
 """Benchmark of the brute.bit1 hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--gemm-impl auto|popc|b1|i8]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--gemm-impl auto|popc|b1|i8|i8x2]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Headline workload: the large square binary GEMM, M = N = K = 16384 bit1 operands
@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gemm-impl", default="auto", choices=["auto", "popc", "b1", "i8"])
+    ap.add_argument("--gemm-impl", default="auto", choices=["auto", "popc", "b1", "i8", "i8x2"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--size", type=int, default=16384, help="M=N=K (profiling runs use smaller sizes)")
@@ -211,7 +211,7 @@ def run_ours(args):
     from brute_b200 import _lib as L
     from brute_b200.kernels import shard_bounds
     ops = torch.ops.brute
-    impl = {"auto": L.GEMM_AUTO, "popc": L.GEMM_POPC, "b1": L.GEMM_MMA_B1, "i8": L.GEMM_TCGEN05}[args.gemm_impl]
+    impl = {"auto": L.GEMM_AUTO, "popc": L.GEMM_POPC, "b1": L.GEMM_MMA_B1, "i8": L.GEMM_TCGEN05, "i8x2": L.GEMM_TCGEN05_PAIR}[args.gemm_impl]
     size = args.size
     m = n = k = size
     kp = k // 64
@@ -261,7 +261,7 @@ def run_ours(args):
     # roofline of the dominant kernel (this rank's launch)
     my_ms = sum(times) / args.steps
     my_macs = float(m) * n_loc * k
-    if args.gemm_impl in ("auto", "i8"):
+    if args.gemm_impl in ("auto", "i8", "i8x2"):
         # tcgen05 kind::i8: 2 int8 ops per bit-MAC; int8 dense runs at twice the bf16 rate on B200
         achieved = 2 * my_macs / (my_ms * 1e-3) / 1e12
         peak = 2 * peaks["bf16_tflops"]

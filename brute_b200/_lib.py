@@ -17,7 +17,7 @@ OK = 0
 SIGN_GT0, SIGN_GE0 = 0, 1
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 OP_AND, OP_OR, OP_XOR, OP_XNOR, OP_ANDNOT = 0, 1, 2, 3, 4
-GEMM_AUTO, GEMM_POPC, GEMM_MMA_B1, GEMM_TCGEN05 = 0, 1, 2, 3
+GEMM_AUTO, GEMM_POPC, GEMM_MMA_B1, GEMM_TCGEN05, GEMM_TCGEN05_PAIR = 0, 1, 2, 3, 4
 
 _i64, _p, _i32, _f32 = C.c_int64, C.c_void_p, C.c_int, C.c_float
 

@@ -3,7 +3,7 @@
 #include "common.cuh"
 #include "gemm_popc.cuh"
 #include "gemm_mma_b1.cuh"
-#include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_pair.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -73,6 +73,7 @@ static int env_impl() {
         if (!std::strcmp(e, "popc")) v = BRUTE_GEMM_POPC;
         else if (!std::strcmp(e, "b1") || !std::strcmp(e, "mma_b1")) v = BRUTE_GEMM_MMA_B1;
         else if (!std::strcmp(e, "i8") || !std::strcmp(e, "tcgen05")) v = BRUTE_GEMM_TCGEN05;
+        else if (!std::strcmp(e, "i8x2") || !std::strcmp(e, "tcgen05_pair")) v = BRUTE_GEMM_TCGEN05_PAIR;
     }
     cached = v;
     return v;
@@ -85,6 +86,7 @@ static int dispatch(const GemmArgs& g, int impl, cudaStream_t st) {
         if (e == BRUTE_GEMM_POPC) impl = e;
         else if (e == BRUTE_GEMM_MMA_B1 && mma_b1_accepts(g)) impl = e;
         else if (e == BRUTE_GEMM_TCGEN05 && tc5_accepts(g.A, g.B, g.M, g.N, g.Kp)) impl = e;
+        else if (e == BRUTE_GEMM_TCGEN05_PAIR && tc5_accepts(g.A, g.B, g.M, g.N, g.Kp) && tc5_pair_accepts(g.M, g.N)) impl = e;
     }
     if (impl == BRUTE_GEMM_AUTO) {
         // Small problems do not fill the tensor-core tiles; the CUDA-core path
@@ -98,6 +100,8 @@ static int dispatch(const GemmArgs& g, int impl, cudaStream_t st) {
         case BRUTE_GEMM_MMA_B1: return run_mma_b1(g, st);
         case BRUTE_GEMM_TCGEN05:
             return tc5_run(g.A, g.B, g.M, g.N, g.Kp, g.K, g.C, g.ldc, g.scale, g.out, g.mode, g.pack, st);
+        case BRUTE_GEMM_TCGEN05_PAIR:
+            return tc5_pair_run(g.A, g.B, g.M, g.N, g.Kp, g.K, g.C, g.ldc, g.scale, g.out, g.mode, g.pack, st);
         default: return BRUTE_ERR_INVALID_ARG;
     }
 }
@@ -111,7 +115,7 @@ extern "C" int brute_b200_xnor_gemm(const uint64_t* A, const uint64_t* B, int32_
                                     int impl, void* stream) {
     BB_REQUIRE(M >= 0 && N >= 0 && Kp >= 0 && K >= 0 && K <= 64 * Kp, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(K < (1ll << 30) && M < (1ll << 31) && N < (1ll << 31), BRUTE_ERR_UNSUPPORTED);
-    BB_REQUIRE(impl >= BRUTE_GEMM_AUTO && impl <= BRUTE_GEMM_TCGEN05, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(impl >= BRUTE_GEMM_AUTO && impl <= BRUTE_GEMM_TCGEN05_PAIR, BRUTE_ERR_INVALID_ARG);
     if (M == 0 || N == 0) return BRUTE_OK;
     BB_REQUIRE(C != nullptr && ldc >= N, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE((reinterpret_cast<uintptr_t>(C) & 3u) == 0, BRUTE_ERR_MISALIGNED);
@@ -129,7 +133,7 @@ extern "C" int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uin
     BB_REQUIRE(M >= 0 && N >= 0 && Kp >= 0 && K >= 0 && K <= 64 * Kp, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(K < (1ll << 30) && M < (1ll << 31) && N < (1ll << 31), BRUTE_ERR_UNSUPPORTED);
     BB_REQUIRE(mode == BRUTE_SIGN_GT0 || mode == BRUTE_SIGN_GE0, BRUTE_ERR_INVALID_ARG);
-    BB_REQUIRE(impl >= BRUTE_GEMM_AUTO && impl <= BRUTE_GEMM_TCGEN05, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(impl >= BRUTE_GEMM_AUTO && impl <= BRUTE_GEMM_TCGEN05_PAIR, BRUTE_ERR_INVALID_ARG);
     if (M == 0 || N == 0) return BRUTE_OK;
     BB_REQUIRE(scale != nullptr && out != nullptr, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(aligned8(out) && (reinterpret_cast<uintptr_t>(scale) & 3u) == 0, BRUTE_ERR_MISALIGNED);

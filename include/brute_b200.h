@@ -61,6 +61,7 @@ extern "C" {
 #define BRUTE_GEMM_POPC     1   /* CUDA-core __popcll, register blocked, any shape */
 #define BRUTE_GEMM_MMA_B1   2   /* legacy mma.sync m16n8k256 .b1 and.popc          */
 #define BRUTE_GEMM_TCGEN05  3   /* tcgen05.mma kind::i8 on in-kernel expanded bits  */
+#define BRUTE_GEMM_TCGEN05_PAIR 4 /* the same on cta_group::2: two SMs share a 256x256 tile; needs M > 128 */
 
 /* ---- library ----------------------------------------------------------- */
 const char* brute_b200_strerror(int code);

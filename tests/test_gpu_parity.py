@@ -232,6 +232,32 @@ def test_gemm_vs_oracle(ops, co, impl_name, M, K, N):
     assert status_ok()
 
 
+PAIR_SHAPES = [(129, 128, 1), (130, 256, 258), (256, 2048, 512), (300, 640, 700), (513, 384, 129),
+               (257, 128 * 13, 255), (1024, 4096, 1024), (384, 128 * 25, 300), (2048, 128, 2048)]
+
+
+@pytest.mark.parametrize("M,K,N", PAIR_SHAPES)
+def test_gemm_pair_vs_oracle(ops, co, M, K, N):
+    # two CTAs (cta_group::2) per 256 x 256 tile: ragged M and N, K-block counts that leave the
+    # 12-step unroll and the 4-block packed stage at every remainder
+    from brute_b200 import _lib as L
+    a = torch.randint(0, 2, (M, K), generator=gen(M + K)).bool()
+    b = torch.randint(0, 2, (N, K), generator=gen(N + K + 1)).bool()
+    ap, bp = ops.pack_bool(a.to(DEV)), ops.pack_bool(b.to(DEV))
+    want = co.xnor_gemm(u64(ap), u64(bp), K)
+    for _ in range(2):      # twice: the second launch meets the first one's tensor-memory release
+        got = ops.xnor_popcount_matmul_impl(ap, bp, K, L.GEMM_TCGEN05_PAIR).cpu().numpy()
+        assert np.array_equal(got, want)
+    assert status_ok()
+
+
+def test_gemm_pair_needs_two_row_blocks(ops):
+    from brute_b200 import _lib as L
+    a = torch.zeros((128, 2), dtype=torch.int64, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.xnor_popcount_matmul_impl(a, a, 128, L.GEMM_TCGEN05_PAIR)
+
+
 @pytest.mark.parametrize("M,K,N", [(3, 13, 5), (9, 100, 12), (33, 257, 66), (8, 65, 8), (32, 1, 32), (40, 777, 50)])
 def test_gemm_k_not_multiple_of_64(ops, co, M, K, N):
     # K tails, as the reference fuzzes them (tests/fuzz/test_fuzz_matmul.py:15-34); odd word
@@ -282,6 +308,9 @@ def test_gemm_large_properties(ops):
     assert tuple(c.shape) == (16384, 16384)
     slab = ops.xnor_popcount_matmul_impl(a[:512], b[:4096], K, impls()["popc"])
     assert torch.equal(c[:512, :4096], slab)
+    from brute_b200 import _lib as L
+    for impl in (L.GEMM_TCGEN05, L.GEMM_TCGEN05_PAIR):
+        assert torch.equal(ops.xnor_popcount_matmul_impl(a, b, K, impl), c)
     # linearity in the hamming domain: C(a, b) + C(a, ~b) == 0
     c2 = ops.xnor_popcount_matmul(a[:1024], torch.bitwise_not(b[:2048]), K)
     assert int((c[:1024, :2048] + c2).abs().max()) == 0
@@ -291,7 +320,7 @@ def test_gemm_large_properties(ops):
     assert status_ok()
 
 
-@pytest.mark.parametrize("impl_name", ["popc", "mma_b1", "tcgen05"])
+@pytest.mark.parametrize("impl_name", ["popc", "mma_b1", "tcgen05", "tcgen05_pair"])
 @pytest.mark.parametrize("mode", [0, 1])
 def test_mlp_layer(ops, co, impl_name, mode):
     from brute_b200 import _lib as L
@@ -304,7 +333,7 @@ def test_mlp_layer(ops, co, impl_name, mode):
     out = torch.empty((M, (N + 63) // 64), dtype=torch.int64, device=DEV)
     rc = L.load().brute_b200_xnor_gemm_scale_sign_pack(
         ap.data_ptr(), wp.data_ptr(), scale.to(DEV).data_ptr(), out.data_ptr(), M, N, K // 64, K, mode,
-        impls()[impl_name], torch.cuda.current_stream().cuda_stream)
+        {**impls(), "tcgen05_pair": L.GEMM_TCGEN05_PAIR}[impl_name], torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     assert np.array_equal(u64(out), want)
     assert np.array_equal(u64(ops.xnor_matmul_scale_sign_pack(ap, wp, scale.to(DEV), K, mode)), want)
