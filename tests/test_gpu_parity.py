@@ -233,7 +233,8 @@ def test_gemm_vs_oracle(ops, co, impl_name, M, K, N):
 
 
 PAIR_SHAPES = [(129, 128, 1), (130, 256, 258), (256, 2048, 512), (300, 640, 700), (513, 384, 129),
-               (257, 128 * 13, 255), (1024, 4096, 1024), (384, 128 * 25, 300), (2048, 128, 2048)]
+               (257, 128 * 13, 255), (1024, 4096, 1024), (384, 128 * 25, 300), (2048, 128, 2048),
+               (2048, 384, 4096), (1500, 1152, 5003), (4100, 256, 2052)]   # more tiles than SM pairs
 
 
 @pytest.mark.parametrize("M,K,N", PAIR_SHAPES)
