@@ -91,7 +91,8 @@ static int dispatch(const GemmArgs& g, int impl, cudaStream_t st) {
     if (impl == BRUTE_GEMM_AUTO) {
         // Small problems do not fill the tensor-core tiles; the CUDA-core path
         // has no shape rules at all.
-        if (tc5_accepts(g.A, g.B, g.M, g.N, g.Kp) && g.M * g.N >= 128 * 256) impl = BRUTE_GEMM_TCGEN05;
+        if (tc5_accepts(g.A, g.B, g.M, g.N, g.Kp) && g.M * g.N >= 128 * 256)
+            impl = tc5_pair_prefers(g.M, g.N) ? BRUTE_GEMM_TCGEN05_PAIR : BRUTE_GEMM_TCGEN05;
         else if (mma_b1_accepts(g) && g.M * g.N >= 64 * 64) impl = BRUTE_GEMM_MMA_B1;
         else impl = BRUTE_GEMM_POPC;
     }

@@ -483,6 +483,13 @@ static bool tc5_pair_accepts(int64_t M, int64_t N) {
     return M > TP_BM && tiles < (1ll << 30) && M < (1ll << 31) - 2 * TP_BM && N < (1ll << 31) - TP_BN;
 }
 
+// AUTO takes the pair kernel once its 256 x 256 tiles can occupy most of the SM pairs; below
+// that the one-CTA kernel's 128 x 256 tiles spread a small problem over twice as many SMs.
+static bool tc5_pair_prefers(int64_t M, int64_t N) {
+    const int64_t tiles = ((M + 2 * TP_BM - 1) / (2 * TP_BM)) * ((N + TP_BN - 1) / TP_BN);
+    return tc5_pair_accepts(M, N) && tiles >= 48;
+}
+
 template <int STORE>
 static int tc5_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                            int64_t M, int64_t N, int32_t nkb, int32_t klogical, int32_t tiles_m, int32_t ntiles,
