@@ -159,7 +159,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.02)
+            self._stop.wait(0.005)
 
     def start(self):
         if self.nv is not None:
@@ -280,17 +280,15 @@ def run_ours(args):
     #      H2D of both operands, the op, D2H of the int32 result
     e2e = None
     if rank == 0 or world > 1:
+        from brute_b200.kernels import host_matmul
         hA = A.cpu().pin_memory()
         hB = B.cpu().pin_memory()
         hC = torch.empty((m, n_loc), dtype=torch.int32).pin_memory()
-        dA = torch.empty_like(A)
-        dB = torch.empty_like(B)
 
         def e2e_step():
-            dA.copy_(hA, non_blocking=True)
-            dB.copy_(hB, non_blocking=True)
-            c = ops.xnor_popcount_matmul_impl(dA, dB, k, impl)
-            hC.copy_(c, non_blocking=True)
+            # the public host-buffer call: H2D of B and of A block by block, the GEMM of each
+            # block, D2H of that block of C, overlapped on three streams
+            host_matmul(hA, hB, k, out=hC, device=dev, impl=impl)
 
         e_steps = max(3, min(args.steps, 5))
         e_times = time_steps(e2e_step, e_steps, 1, flush, sync)

@@ -19,7 +19,7 @@ from .functional import (  # noqa: E402
 )
 from .fast import *  # noqa: E402,F401,F403
 from . import cuda_graphs, fast, streams  # noqa: E402
-from .kernels import binary_attention, binary_linear, pack_sign, sharded_matmul  # noqa: E402
+from .kernels import binary_attention, binary_linear, host_matmul, pack_sign, sharded_matmul  # noqa: E402
 
 nn = None
 optim = None

@@ -5,7 +5,10 @@
                       scale, re-binarisation, re-pack, fused in the GEMM epilogue;
 * ``binary_attention`` sign-binarised Q.K^T scored by popcount, fp32 softmax, @ V;
 * ``sharded_matmul``  the xnor GEMM with B's rows (output features) split across
-                      the ranks of a ``torch.distributed`` group, optional all-gather.
+                      the ranks of a ``torch.distributed`` group, optional all-gather;
+* ``host_matmul``     the xnor GEMM on operands and a result in HOST memory: the copies in, the
+                      GEMM of each block of A's rows and the copy of that block of C back to the
+                      host run on three streams and overlap.
 """
 from __future__ import annotations
 
@@ -84,3 +87,58 @@ def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group
     dist.all_gather_into_tensor(stacked, padded, group=group)
     blocks = stacked.view(world, M, wmax)
     return torch.cat([blocks[r, :, :widths[r]] for r in range(world)], dim=1)
+
+
+_host_streams = {}
+
+
+def host_matmul(a_host: torch.Tensor, b_host: torch.Tensor, K: int, out: Optional[torch.Tensor] = None,
+                device=None, rows_per_block: int = 2048, impl: int = 0) -> torch.Tensor:
+    """Packed A [M, Kp] and B [N, Kp] in host memory -> int32 C [M, N] in host memory (`out`,
+    or a new pinned tensor). Pinned operands make every copy asynchronous.
+
+    The int32 result is 32x the size of the packed operands, so its way back over PCIe is what
+    an end-to-end call waits for. B goes to the device once; A goes up in blocks of
+    `rows_per_block` rows, each block's GEMM runs as soon as its rows have landed, and its block
+    of C leaves on a third stream while the next GEMM runs. Work is ordered after the caller's
+    current stream and the current stream waits for the last copy, so CUDA events recorded
+    around the call on the current stream bracket all of it. Call `torch.cuda.synchronize()` (or
+    synchronise the current stream) before reading `out` on the host.
+    """
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    M, Kp = a_host.shape
+    N = b_host.shape[0]
+    if b_host.shape[1] != Kp:
+        raise RuntimeError("host_matmul: packed K mismatch")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int32).pin_memory()
+    if tuple(out.shape) != (M, N) or out.dtype != torch.int32 or out.is_cuda or not out.is_contiguous():
+        raise RuntimeError("host_matmul: out must be a contiguous int32 [M, N] host tensor")
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    if key not in _host_streams:
+        _host_streams[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    s_in, s_out = _host_streams[key]
+    cur = torch.cuda.current_stream(dev)
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    with torch.cuda.stream(s_in):
+        d_b = b_host.to(dev, non_blocking=True)
+        d_b.record_stream(cur)
+    step = max(1, int(rows_per_block))
+    for lo in range(0, M, step):
+        hi = min(M, lo + step)
+        with torch.cuda.stream(s_in):
+            d_a = a_host[lo:hi].to(dev, non_blocking=True)
+            d_a.record_stream(cur)
+            landed = torch.cuda.Event()
+            landed.record(s_in)
+        cur.wait_event(landed)
+        c = _ops.xnor_popcount_matmul_impl(d_a, d_b, int(K), int(impl))
+        done = torch.cuda.Event()
+        done.record(cur)
+        s_out.wait_event(done)
+        with torch.cuda.stream(s_out):
+            out[lo:hi].copy_(c, non_blocking=True)
+        c.record_stream(s_out)
+    cur.wait_stream(s_out)
+    return out

@@ -252,6 +252,26 @@ def test_gemm_pair_vs_oracle(ops, co, M, K, N):
     assert status_ok()
 
 
+def test_host_matmul_overlapped(ops, co):
+    # host operands and result, blocks of rows on three streams; ragged last block
+    import brute_b200 as brute
+    M, K, N = 1000, 1024, 700
+    a = torch.randint(-2 ** 63, 2 ** 63 - 1, (M, K // 64), generator=gen(5), dtype=torch.int64).pin_memory()
+    b = torch.randint(-2 ** 63, 2 ** 63 - 1, (N, K // 64), generator=gen(6), dtype=torch.int64).pin_memory()
+    want = co.xnor_gemm(a.numpy(), b.numpy(), K)
+    out = torch.full((M, N), -1, dtype=torch.int32).pin_memory()
+    for rows in (2048, 300, 128):
+        out.fill_(-1)
+        got = brute.host_matmul(a, b, K, out=out, rows_per_block=rows)
+        torch.cuda.synchronize()
+        assert got is out and np.array_equal(out.numpy(), want), rows
+    fresh = brute.host_matmul(a, b, K)
+    torch.cuda.synchronize()
+    assert fresh.is_pinned() and np.array_equal(fresh.numpy(), want)
+    with pytest.raises(RuntimeError, match="out must be"):
+        brute.host_matmul(a, b, K, out=torch.empty((M, N + 1), dtype=torch.int32))
+
+
 def test_gemm_pair_needs_two_row_blocks(ops):
     from brute_b200 import _lib as L
     a = torch.zeros((128, 2), dtype=torch.int64, device=DEV)
