@@ -37,6 +37,9 @@ UNIT = "TOPS (1 bit-MAC = 1 op)"
 WORKLOAD = "xnor-popcount GEMM M=N=K=16384 bit1, uint64-packed, int32 out (BASELINE config 3)"
 
 
+NCU_DRAM_BYTES_16384 = 1.313e9     # profiles/gemm_tcgen05_pair_16384.md
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -265,9 +268,15 @@ def run_ours(args):
         # tcgen05 kind::i8: 2 int8 ops per bit-MAC; int8 dense runs at twice the bf16 rate on B200
         achieved = 2 * my_macs / (my_ms * 1e-3) / 1e12
         peak = 2 * peaks["bf16_tflops"]
+        # DRAM bytes of one 16384^3 launch from the committed ncu capture of this kernel
+        # (dram__bytes_read.sum + dram__bytes_write.sum), scaled by the outputs this launch writes
+        traffic = NCU_DRAM_BYTES_16384 * (float(m) * n_loc) / (16384.0 * 16384.0) if size == 16384 else None
+        pipe = 148 * 8192 * 2 * 1.965e9 / 1e12     # int8 MACs/clk/SM x 2 ops x SMs x max SM clock
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s (int8, 2 per bit-MAC)",
-                "frac": achieved / peak, "traffic": None,
-                "peak_source": f"2 x bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json",
+                "frac": achieved / peak, "traffic": traffic,
+                "peak_source": f"2 x bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json (no int8 figure in the file; "
+                               "a cuBLAS bf16 GEMM does not saturate its pipe, so a fraction above 1 is possible)",
+                "frac_of_pipe_rate": achieved / pipe,
                 "algorithmic_bytes_per_launch": 8 * kp * (m + n_loc) + 4 * m * n_loc}
     else:
         alg = 8 * kp * (m + n_loc) + 4 * m * n_loc

@@ -133,7 +133,8 @@ int brute_b200_hamming_words(const uint64_t* a, const uint64_t* b, int32_t* out,
 
 /* ---- bitwise ----------------------------------------------------------- */
 /* out = a OP b over [rows, words_per_row]; `last_dim_bits` is only read by
- * XNOR, which clears each row's pad bits. out may alias a or b.
+ * XNOR, which clears each row's pad bits. out may be exactly a or exactly b
+ * (in place: every word is read and written by the same thread); partial overlap is not allowed.
  * Replaces the ATen int64 bitwise launches of brute/tensor.py:564-598,1494-1537
  * and brute/fast.py:37-83 (eq = xor + bit1_not_packed fused into one XNOR). */
 int brute_b200_bitwise(int op, const uint64_t* a, const uint64_t* b, uint64_t* out,
