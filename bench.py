@@ -339,7 +339,15 @@ def run_ours(args):
         # the same sample on the GPU must give the same integers
         c_gpu = ops.xnor_popcount_matmul_impl(torch.from_numpy(a_np).to(dev), torch.from_numpy(b_np).to(dev), k, impl)
         assert np.array_equal(c_gpu.cpu().numpy(), c_np), "GPU result differs from the CPU baseline's"
-        cpu_base = {"value": rows * rows * k / dt / 1e12, "unit": UNIT, "cores": co.num_threads(), "kind": "port",
+        # BASELINE config 2 on the host: float threshold + pack of 2^26 elements
+        x_np = rng.standard_normal((1 << 10, 1 << 16), dtype=np.float32)     # rows are the oracle's unit of threading
+        co.pack_sign_f32(x_np[:16], 1)
+        t0 = time.perf_counter()
+        co.pack_sign_f32(x_np, 1)
+        dt_pack = time.perf_counter() - t0
+        del x_np
+        cpu_base = {"pack_sign_f32_2^26_GB/s": (4.125 * (1 << 26)) / dt_pack / 1e9,
+                    "value": rows * rows * k / dt / 1e12, "unit": UNIT, "cores": co.num_threads(), "kind": "port",
                     "sample": f"{rows}x{rows} outputs, full K={k}, {dt:.2f} s", "host_cpus": os.cpu_count(),
                     "vpopcntdq": co.has_vpopcntdq()}
 
@@ -381,6 +389,30 @@ def secondary_workloads(dev, peaks, flush, sync):
     x = torch.randn(n, generator=g, device=dev)
     bw("pack_sign_f32_2^30", lambda: ops.pack_sign(x, 1), 4 * n + n // 8)
     p = ops.pack_sign(x, 1)
+
+    # BASELINE config 2 sweep: fp32 [2^k], k = 10..30, threshold x >= 0. Small sizes are bound by
+    # the dispatch of one op from Python, so each size is timed twice: as an eager call and as the
+    # replay of a CUDA graph that holds the one kernel (L2 flushed before every timed launch).
+    sweep = {"k": [], "eager_us": [], "graph_us": [], "graph_GB/s": []}
+    side = torch.cuda.Stream(dev)
+    for k in range(10, 31):
+        xk = x[: 1 << k]
+        eager = statistics.median(time_steps(lambda: ops.pack_sign(xk, 1), 7, 3, flush, sync))
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                ops.pack_sign(xk, 1)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            held = ops.pack_sign(xk, 1)
+        replay = statistics.median(time_steps(graph.replay, 7, 3, flush, sync))
+        del graph, held
+        sweep["k"].append(k)
+        sweep["eager_us"].append(round(eager * 1e3, 2))
+        sweep["graph_us"].append(round(replay * 1e3, 2))
+        sweep["graph_GB/s"].append(round((4 * (1 << k) + (1 << k) // 8) / (replay * 1e-3) / 1e9, 1))
+    out["pack_sign_f32_sweep"] = sweep
     del x
     q = torch.randint(-2 ** 63, 2 ** 63 - 1, (n // 64,), generator=g, dtype=torch.int64, device=dev)
     bw("unpack_bool_2^30", lambda: ops.unpack_bool(p, [n]), n // 8 + n)
@@ -415,6 +447,18 @@ def secondary_workloads(dev, peaks, flush, sync):
     macs = 2 * 8192.0 * 4096 * 16384
     out["mlp_8192x4096x16384x4096"] = {"ms": ms, "tops": macs / (ms * 1e-3) / 1e12}
     del xs, w1, w2
+
+    # signed_bundle: int8 votes [256, 1024, 1024] x bit1 values [256, 1024, 128] -> bit1 [256, 1024, 128]
+    Bb, Mb, Nb, Db = 256, 1024, 1024, 128
+    wv = torch.randint(-3, 4, (Bb, Mb, Nb), generator=g, device=dev, dtype=torch.int8)
+    vv = torch.randint(-2 ** 63, 2 ** 63 - 1, (Bb, Nb, Db // 64), generator=g, dtype=torch.int64, device=dev)
+    ts = time_steps(lambda: ops.signed_bundle(wv, vv, Db), 5, 2, flush, sync)
+    ms = statistics.median(ts)
+    alg = Bb * Mb * Nb + Bb * Nb * Db // 8 + Bb * Mb * Db // 8
+    out["signed_bundle_256x1024x1024x128"] = {
+        "ms": ms, "int8_x_bit_tmacs": float(Bb) * Mb * Nb * Db / (ms * 1e-3) / 1e12,
+        "algorithmic_bytes": alg, "GB/s": alg / (ms * 1e-3) / 1e9, "frac_of_hbm": alg / (ms * 1e-3) / 1e9 / hbm}
+    del wv, vv
 
     # binary attention B=8 H=32 S=4096 D=128 causal (BASELINE config 5)
     Bq, H, S, D = 8, 32, 4096, 128
