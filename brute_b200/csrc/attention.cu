@@ -20,6 +20,8 @@
 // stage and the P@V MMA. V fragments come from ldmatrix.trans on a 16-byte
 // XOR-swizzled tile.
 #include "common.cuh"
+#include <cstdlib>
+#include <cstring>
 
 namespace bb {
 
@@ -404,7 +406,225 @@ k_binary_attention_fwd_table(const uint64_t* __restrict__ Qp, const uint64_t* __
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Table softmax with the SCORES on the tensor cores as well.
+//
+// The keys of a tile are expanded once per CTA from packed bits to int8 in shared memory
+// (bit 1 -> -2, bit 0 -> +2), the queries once per warp into m16n8k32 A-fragments (bit 1 -> +1,
+// bit 0 -> -1), so that mma.sync s8 x s8 accumulates acc = 4*h - 2*D for Hamming distance h.
+// T[h] is a float table, so acc + 2*D IS the byte offset of T[h]: a score costs one shared-memory
+// load and half a bf16x2 convert, against ~18 XOR/POPC/ALU instructions on the CUDA cores. The
+// accumulator layout of the score MMA is the A-fragment layout of the P.V MMA, so P still never
+// leaves registers. The row sums come from one more MMA per 16 keys against a column of ones,
+// which sums exactly the bf16-rounded weights that enter P.V. The d positions inside every
+// 32-bit word are permuted (byte 4j+i <- bit 8i+j) identically for Q and K.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 4 bits (j, 8+j, 16+j, 24+j of h) -> 4 int8: query side +1 / -1, key side -2 / +2
+__device__ __forceinline__ uint32_t at_enc_q(uint32_t h, int j) { return 0xFFFFFFFFu ^ (((h >> j) & 0x01010101u) * 0xFEu); }
+__device__ __forceinline__ uint32_t at_enc_k(uint32_t h, int j) { return 0x02020202u ^ (((h >> j) & 0x01010101u) * 0xFCu); }
+
+template <int W> constexpr int at_mma_smem() { return 2 * AT_BN * 64 * W + 2 * AT_BN * 128 * W + 4 * (64 * W + 4); }
+
+template <int W>
+__global__ void __launch_bounds__(AT_THREADS, 2)
+k_binary_attention_fwd_mma(const uint64_t* __restrict__ Qp, const uint64_t* __restrict__ Kp,
+                           const __nv_bfloat16* __restrict__ V, __nv_bfloat16* __restrict__ O,
+                           int64_t S, int causal, float neg2c_log2 /* -2*scale*log2(e) */, float bias_log2,
+                           int64_t q_tiles) {
+    constexpr int D = 64 * W;
+    constexpr int VROW = D * 2, VCH = D / 8, NT = D / 8;
+    constexpr int KROW = D;                     // bytes per expanded key row
+    constexpr int KS = D / 32;                  // k-steps of the score MMA = 32-bit words per row
+    extern __shared__ __align__(128) uint8_t at_smem[];
+    uint8_t* Ke = at_smem;                                   // [2][AT_BN][KROW] int8, 16-byte chunks swizzled
+    uint8_t* Vs = at_smem + 2 * AT_BN * KROW;                // [2][AT_BN][VROW] bf16, 16-byte chunks swizzled
+    float* T = reinterpret_cast<float*>(Vs + 2 * AT_BN * VROW);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t qt = q_tiles - 1 - (int64_t)blockIdx.x;    // heavy (late) causal tiles first
+    const int64_t bh = blockIdx.y;
+    const int64_t q0 = qt * AT_BM;
+    const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * W);
+    const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Kp + bh * S * W);
+    const __nv_bfloat16* Vb = V + bh * S * D;
+    __nv_bfloat16* Ob = O + bh * S * D;
+
+    if (tid <= D) T[tid] = exp2f(neg2c_log2 * (float)tid - bias_log2);
+    const char* Tc = reinterpret_cast<const char*>(T) + 2 * D;     // acc = 4*h - 2*D -> T[h]
+
+    const int64_t row_lo = q0 + warp * 16 + g, row_hi = row_lo + 8;
+    uint32_t qa[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        const uint32_t lo = row_lo < S ? __ldg(Qw + row_lo * KS + ks) : 0u;
+        const uint32_t hi = row_hi < S ? __ldg(Qw + row_hi * KS + ks) : 0u;
+        qa[ks][0] = at_enc_q(lo, t);     qa[ks][1] = at_enc_q(hi, t);
+        qa[ks][2] = at_enc_q(lo, 4 + t); qa[ks][3] = at_enc_q(hi, 4 + t);
+    }
+
+    const int64_t kend = causal ? (q0 + AT_BM < S ? q0 + AT_BM : S) : S;
+    const int64_t ntiles = (kend + AT_BN - 1) / AT_BN;
+    const uint32_t ke_base = (uint32_t)__cvta_generic_to_shared(Ke);
+    const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(Vs);
+
+    // this thread's packed word of a key tile: key ekey, 32-bit word ew
+    const bool expander = tid < AT_BN * KS;
+    const int ekey = tid / KS, ew = tid % KS;
+    auto key_swz = [](int key) { return W == 2 ? (key & 7) : ((key >> 1) & 3); };
+    auto load_k = [&](int64_t tile) -> uint32_t {
+        const int64_t k = tile * AT_BN + ekey;
+        return (expander && k < S) ? __ldg(Kw + k * KS + ew) : 0u;
+    };
+    auto expand_k = [&](int buf, uint32_t h) {
+        if (!expander) return;
+        uint8_t* row = Ke + (buf * AT_BN + ekey) * KROW;
+        const int sw = key_swz(ekey);
+        *reinterpret_cast<uint4*>(row + (((2 * ew) ^ sw) << 4)) =
+            make_uint4(at_enc_k(h, 0), at_enc_k(h, 1), at_enc_k(h, 2), at_enc_k(h, 3));
+        *reinterpret_cast<uint4*>(row + (((2 * ew + 1) ^ sw) << 4)) =
+            make_uint4(at_enc_k(h, 4), at_enc_k(h, 5), at_enc_k(h, 6), at_enc_k(h, 7));
+    };
+    auto load_v = [&](int buf, int64_t tile) {
+        const int64_t k0 = tile * AT_BN;
+#pragma unroll
+        for (int it = 0; it < (AT_BN * VCH) / AT_THREADS; ++it) {
+            const int idx = tid + it * AT_THREADS;
+            const int row = idx / VCH, ch = idx % VCH;
+            const bool ok = k0 + row < S;
+            const int sch = (ch & ~7) | ((ch ^ row) & 7);
+            at_cp_async16(vs_base + buf * AT_BN * VROW + row * VROW + sch * 16,
+                          Vb + (ok ? (k0 + row) * D + ch * 8 : 0), ok ? 16 : 0);
+        }
+    };
+
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float ol[4] = {0.f, 0.f, 0.f, 0.f};         // row sums: P against a column of ones
+    constexpr uint32_t ONES = 0x3F803F80u;      // bf16 (1.0, 1.0)
+
+    uint32_t knext = 0u;
+    if (ntiles > 0) {
+        load_v(0, 0);
+        expand_k(0, load_k(0));
+        if (ntiles > 1) knext = load_k(1);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    for (int64_t tile = 0; tile < ntiles; ++tile) {
+        const int buf = (int)(tile & 1);
+        if (tile + 1 < ntiles) {
+            load_v(buf ^ 1, tile + 1);
+            expand_k(buf ^ 1, knext);            // read again only after the barrier that ends this iteration
+            if (tile + 2 < ntiles) knext = load_k(tile + 2);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+
+        const int64_t k0 = tile * AT_BN;
+        const bool active = !(causal && k0 > q0 + warp * 16 + 15);
+        if (active) {
+            const bool need_mask = (causal && k0 + AT_BN - 1 > q0 + warp * 16) || (k0 + AT_BN > S);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                int c[4][4];
+#pragma unroll
+                for (int nbi = 0; nbi < 4; ++nbi) {
+                    c[nbi][0] = c[nbi][1] = c[nbi][2] = c[nbi][3] = 0;
+                    const int krow = 8 * (4 * half + nbi) + (lane & 7);
+                    const uint32_t rowaddr = ke_base + (uint32_t)((buf * AT_BN + krow) * KROW);
+                    const int sw = key_swz(krow);
+#pragma unroll
+                    for (int cq = 0; cq < KS / 2; ++cq) {
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4(rowaddr + (uint32_t)((((4 * cq + (lane >> 3))) ^ sw) << 4), b0, b1, b2, b3);
+                        mma_s8_16832(c[nbi], qa[2 * cq], b0, b1);
+                        mma_s8_16832(c[nbi], qa[2 * cq + 1], b2, b3);
+                    }
+                }
+#pragma unroll
+                for (int kbi = 0; kbi < 2; ++kbi) {
+                    const int kb = 2 * half + kbi;
+                    float p[2][4];          // [n-block of the pair][accumulator slot]
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float v = *reinterpret_cast<const float*>(Tc + c[2 * kbi + x][e]);
+                            if (need_mask) {
+                                const int64_t kidx = k0 + kb * 16 + x * 8 + 2 * t + (e & 1);
+                                const int64_t row = (e & 2) ? row_hi : row_lo;
+                                if (kidx >= S || (causal && kidx > row)) v = 0.f;
+                            }
+                            p[x][e] = v;
+                        }
+                    }
+                    const uint32_t a0 = pack_bf16x2(p[0][0], p[0][1]);
+                    const uint32_t a1 = pack_bf16x2(p[0][2], p[0][3]);
+                    const uint32_t a2 = pack_bf16x2(p[1][0], p[1][1]);
+                    const uint32_t a3 = pack_bf16x2(p[1][2], p[1][3]);
+                    mma_bf16_16816(ol, a0, a1, a2, a3, ONES, ONES);
+                    const int vrow = kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                    for (int j = 0; j < NT; j += 2) {
+                        const int ch = j + (lane >> 4);
+                        const int sch = (ch & ~7) | ((ch ^ vrow) & 7);
+                        uint32_t b0, b1, b2, b3;
+                        ldmatrix_x4_trans(vs_base + buf * AT_BN * VROW + vrow * VROW + sch * 16, b0, b1, b2, b3);
+                        mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+                        mma_bf16_16816(o[j + 1], a0, a1, a2, a3, b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    // normalise, stage the 128 x D output tile through the V buffers, coalesced 16-byte stores
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float l = ol[2 * h];
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int r = warp * 16 + g + 8 * h;
+        uint8_t* srow = Vs + r * VROW;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const int sch = (j & ~7) | ((j ^ r) & 7);
+            *reinterpret_cast<uint32_t*>(srow + sch * 16 + t * 4) =
+                pack_bf16x2(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < (AT_BM * VCH) / AT_THREADS; ++it) {
+        const int idx = tid + it * AT_THREADS;
+        const int r = idx / VCH, ch = idx % VCH;
+        const int sch = (ch & ~7) | ((ch ^ r) & 7);
+        if (q0 + r < S) {
+            const uint4 v = *reinterpret_cast<const uint4*>(Vs + r * VROW + sch * 16);
+            *reinterpret_cast<uint4*>(Ob + (q0 + r) * D + ch * 8) = v;
+        }
+    }
+}
+
 }  // namespace bb
+
+#include "attention_tcgen05.cuh"
+
+namespace bb { int at_status_bridge() { return tc5_device_status(); } }
 
 using namespace bb;
 
@@ -430,8 +650,35 @@ extern "C" int brute_b200_binary_attention_fwd(const uint64_t* Qp, const uint64_
     if (span_log2 <= 100.0f) {
         const float neg2c = -2.0f * scale_log2;
         const float bias = scale_log2 < 0.f ? neg2c * (float)D : 0.f;      // keeps max(T) == 1
-        if (D == 128) k_binary_attention_fwd_table<2><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
-        else          k_binary_attention_fwd_table<1><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
+        // BRUTE_ATTENTION_IMPL = tcgen05 (default for D = 128) | mma (mma.sync scores) | popc (CUDA-core scores)
+        static const char* env_impl = std::getenv("BRUTE_ATTENTION_IMPL");
+        const bool want_popc = env_impl && !std::strcmp(env_impl, "popc");
+        const bool want_mma = env_impl && !std::strcmp(env_impl, "mma");
+        if (D == 128 && !want_popc && !want_mma) {
+            const int rc = ax_run(Qp, Kp_, V, O, B * H, S, causal, neg2c, bias, st);
+            if (rc != BRUTE_ERR_DRIVER) return rc;      // no tensor-map encoder: fall through to mma.sync
+        }
+        if (want_popc) {
+            if (D == 128) k_binary_attention_fwd_table<2><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
+            else          k_binary_attention_fwd_table<1><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
+            return launch_status();
+        }
+        static bool attr_set[2] = {false, false};
+        if (D == 128) {
+            if (!attr_set[1]) {
+                if (cudaFuncSetAttribute(k_binary_attention_fwd_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_mma_smem<2>()) != cudaSuccess)
+                    return BRUTE_ERR_LAUNCH;
+                attr_set[1] = true;
+            }
+            k_binary_attention_fwd_mma<2><<<grid, AT_THREADS, at_mma_smem<2>(), st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
+        } else {
+            if (!attr_set[0]) {
+                if (cudaFuncSetAttribute(k_binary_attention_fwd_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_mma_smem<1>()) != cudaSuccess)
+                    return BRUTE_ERR_LAUNCH;
+                attr_set[0] = true;
+            }
+            k_binary_attention_fwd_mma<1><<<grid, AT_THREADS, at_mma_smem<1>(), st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
+        }
         return launch_status();
     }
     if (D == 128) k_binary_attention_fwd<2><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, scale_log2, q_tiles);

@@ -1,0 +1,368 @@
+// Fused binary attention forward on the 5th-generation tensor cores (D = 128).
+//
+// Both contractions run on tcgen05.mma with accumulators in tensor memory:
+//   S = Q.K^T   kind::i8, M128 N64 K32 x 4. Q (+1/-1) is expanded once per CTA into TMEM and is the
+//               A operand; the K tile (64 keys) is expanded from packed bits to int8 (-2/+2) in
+//               shared memory, K-major SWIZZLE_128B. The accumulator is 4*h - 2*D for Hamming
+//               distance h, i.e. the byte offset of T[h] from the middle of the float table.
+//   O += P.V    kind::f16 (bf16), M128 N128 K16 x 4. P is the A operand, read from TMEM; V arrives by
+//               TMA as two [64 keys x 64 d] SWIZZLE_128B boxes and is the B operand in MN-major
+//               form, so the row-major V of the caller needs no transpose.
+// Softmax is the table form: P = T[h] (bf16-exact entries, T <= 1), no running maximum, no exp and
+// no rescaling of O, so O simply accumulates in TMEM over all key tiles and is divided by the row
+// sum at the end. One thread owns one query row = one TMEM lane: it reads its 64 scores with
+// tcgen05.ld, looks them up, adds them to its row sum, packs bf16 pairs and writes them back with
+// tcgen05.st. Rounding matches the mma.sync kernels: the row sum adds exactly the bf16 weights that
+// enter P.V.
+//
+// CTA = 128 query rows of one (batch, head); 256 threads; 256 TMEM columns (S 64, P 32, Q 32,
+// O 128), so two CTAs share an SM and one's softmax overlaps the other's MMAs.
+//   warp 0      TMA producer for V (3-deep ring).
+//   warp 1      MMA issuer, TMEM owner.
+//   warps 2-3   K expanders (double-buffered int8 tile).
+//   warps 4-7   softmax, then the epilogue (tcgen05.ld of O, 1/l, bf16, 16-byte stores).
+// Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag and the device
+// status word, and all roles fall through to the common exit where the TMEM is freed.
+#pragma once
+#include "tcgen05_common.cuh"
+
+namespace bb {
+
+constexpr int AX_BM = 128, AX_BN = 64, AX_D = 128, AX_THREADS = 256;
+constexpr int AX_NV = 3;                                   // V stages
+constexpr int AX_V_HALF = AX_BN * 128;                     // [64 keys][64 d] bf16 = 8 KB
+constexpr int AX_V_STAGE = 2 * AX_V_HALF;                  // 16 KB
+constexpr int AX_KE_TILE = AX_BN * AX_D;                   // int8 [64 keys][128 d] = 8 KB
+constexpr int AX_COL_S = 0, AX_COL_P = 64, AX_COL_Q = 96, AX_COL_O = 128, AX_TMEM_COLS = 256;
+constexpr int AX_OFF_KE = AX_NV * AX_V_STAGE;              // 48 KB
+constexpr int AX_OFF_T = AX_OFF_KE + 2 * AX_KE_TILE;       // 64 KB
+constexpr int AX_OFF_BARS = AX_OFF_T + 1024;
+constexpr int AX_SMEM = AX_OFF_BARS + 256 + 1024;          // + alignment slack
+
+// kind::i8: D s32, A and B signed int8, K-major both, M 128, N 64
+constexpr uint32_t AX_IDESC_QK = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AX_BN >> 3) << 17) | ((uint32_t)(AX_BM >> 4) << 24);
+// kind::f16: D f32, A and B bf16, A K-major (TMEM), B MN-major, M 128, N 128
+constexpr uint32_t AX_IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AX_D >> 3) << 17) | ((uint32_t)(AX_BM >> 4) << 24);
+
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        :: "r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+// V stage as the B operand of P.V: MN-major SWIZZLE_128B. 64 d (128 bytes) are contiguous; the
+// next 64 d are AX_V_HALF bytes further (leading byte offset); 8 keys form a 1024-byte atom and
+// the next 8 keys follow it (stride byte offset).
+__device__ __forceinline__ uint64_t ax_v_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(AX_V_HALF >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// 4 bits (j, 8+j, 16+j, 24+j of h) -> 4 int8: query side +1 / -1, key side -2 / +2
+__device__ __forceinline__ uint32_t ax_enc_q(uint32_t h, int j) { return 0xFFFFFFFFu ^ (((h >> j) & 0x01010101u) * 0xFEu); }
+__device__ __forceinline__ uint32_t ax_enc_k(uint32_t h, int j) { return 0x02020202u ^ (((h >> j) & 0x01010101u) * 0xFCu); }
+
+__global__ void __launch_bounds__(AX_THREADS, 2)
+k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
+                               const uint64_t* __restrict__ Qp, const uint64_t* __restrict__ Kp,
+                               __nv_bfloat16* __restrict__ O,
+                               int64_t S, int causal, float neg2c_log2 /* -2*scale*log2(e) */, float bias_log2,
+                               int64_t q_tiles) {
+    extern __shared__ uint8_t ax_smem_raw[];
+    __shared__ int s_skip;
+    if (threadIdx.x == 0) s_skip = *(volatile int*)&g_tc_status;
+    __syncthreads();
+    if (s_skip != 0) return;                            // an earlier CTA gave up: do not queue behind it
+
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(ax_smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = ax_smem_raw + (base - raw);
+    const uint32_t v_ring = base, ke_ring = base + AX_OFF_KE, bars = base + AX_OFF_BARS;
+    uint8_t* gke = gbase + AX_OFF_KE;
+    float* T = reinterpret_cast<float*>(gbase + AX_OFF_T);
+    uint8_t* gbars = gbase + AX_OFF_BARS;
+    auto v_full   = [&](int s) { return bars + 8u * s; };
+    auto v_empty  = [&](int s) { return bars + 8u * (AX_NV + s); };
+    auto ke_full  = [&](int s) { return bars + 8u * (2 * AX_NV + s); };
+    auto ke_empty = [&](int s) { return bars + 8u * (2 * AX_NV + 2 + s); };
+    const uint32_t s_full = bars + 8u * (2 * AX_NV + 4), s_free = s_full + 8u, p_full = s_full + 16u, p_free = s_full + 24u;
+    const uint32_t q_full = s_full + 32u, o_full = s_full + 40u, drain_bar = s_full + 48u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (2 * AX_NV + 4 + 7));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (2 * AX_NV + 4 + 7) + 4);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t qt = q_tiles - 1 - (int64_t)blockIdx.x;          // heavy (late) causal tiles first
+    const int64_t bh = blockIdx.y;
+    const int64_t q0 = qt * AX_BM;
+    const int64_t kend = causal ? (q0 + AX_BM < S ? q0 + AX_BM : S) : S;
+    const int32_t ntiles = (int32_t)((kend + AX_BN - 1) / AX_BN);  // >= 1 because q0 < S
+
+    // weights are bf16-exact, so the fp32 row sum adds exactly what the P.V MMA multiplies
+    if (tid <= AX_D) T[tid] = __bfloat162float(__float2bfloat16_rn(exp2f(neg2c_log2 * (float)tid - bias_log2)));
+    if (tid == 0) {
+        for (int s = 0; s < AX_NV; ++s) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(ke_full(s), 2); mbar_init(ke_empty(s), 1); }
+        mbar_init(s_full, 1); mbar_init(s_free, 4); mbar_init(p_full, 4); mbar_init(p_free, 1);
+        mbar_init(q_full, 4); mbar_init(o_full, 1); mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"((uint32_t)__cvta_generic_to_shared((const void*)tmem_slot)), "r"((uint32_t)AX_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ================= TMA producer: V tiles =================
+        if (lane == 0) {
+            bool ok = true;
+            int32_t issued = 0;
+            for (int32_t j = 0; j < ntiles && ok; ++j) {
+                const int s = j % AX_NV;
+                ok = mbar_wait(v_empty(s), ((j / AX_NV) & 1) ^ 1, abort_flag, 11);
+                if (!ok) break;
+                mbar_expect_tx(v_full(s), AX_V_STAGE);
+                tma_load_3d(v_ring + s * AX_V_STAGE, &tmV, 0, j * AX_BN, (int32_t)bh, v_full(s));
+                tma_load_3d(v_ring + s * AX_V_STAGE + AX_V_HALF, &tmV, 64, j * AX_BN, (int32_t)bh, v_full(s));
+                issued = j + 1;
+            }
+            if (!ok) {
+                const int32_t first = issued > AX_NV ? issued - AX_NV : 0;
+                for (int32_t j = first; j < issued; ++j) {
+                    const uint64_t t0 = tc_globaltimer();
+                    while (!mbar_try(v_full(j % AX_NV), (j / AX_NV) & 1) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            bool ok = mbar_wait(q_full, 0, abort_flag, 12);
+            auto issue_qk = [&](int32_t j) -> bool {
+                const int b = j & 1;
+                if (!mbar_wait(ke_full(b), (j >> 1) & 1, abort_flag, 13)) return false;
+                if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, 14)) return false;
+                tc_fence_after();
+                const uint64_t kdesc = tc_smem_desc(ke_ring + b * AX_KE_TILE);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)      // 32 bytes of d per instruction
+                    tc_mma_i8_ts(tmem + AX_COL_S, tmem + (uint32_t)(AX_COL_Q + 8 * k), kdesc + 2u * k, AX_IDESC_QK, k > 0 ? 1u : 0u);
+                tc_commit(s_full);
+                tc_commit(ke_empty(b));
+                return true;
+            };
+            auto issue_pv = [&](int32_t j) -> bool {
+                const int s = j % AX_NV;
+                if (!mbar_wait(v_full(s), (j / AX_NV) & 1, abort_flag, 15)) return false;
+                if (!mbar_wait(p_full, j & 1, abort_flag, 16)) return false;
+                tc_fence_after();
+                const uint64_t vdesc = ax_v_desc(v_ring + s * AX_V_STAGE);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)      // 16 keys per instruction = two 1024-byte atoms
+                    tc_mma_f16_ts(tmem + AX_COL_O, tmem + (uint32_t)(AX_COL_P + 8 * k), vdesc + (uint64_t)(128u * k), AX_IDESC_PV,
+                                  (j > 0 || k > 0) ? 1u : 0u);
+                tc_commit(p_free);
+                tc_commit(v_empty(s));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int32_t j = 0; j < ntiles && ok; ++j) {
+                if (j + 1 < ntiles) ok = issue_qk(j + 1);
+                if (ok) ok = issue_pv(j);
+            }
+            if (ok) tc_commit(o_full);
+            tc_commit(drain_bar);
+            const uint64_t t0 = tc_globaltimer();
+            while (!mbar_try(drain_bar, 0) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
+        }
+    } else if (warp < 4) {
+        // ================= K expanders: packed bits -> int8 tile, K-major SWIZZLE_128B =================
+        const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Kp + bh * S * 2);
+        const int half = warp - 2;                        // keys [32 half, 32 half + 32) of the tile
+        // lane -> (key, word): 128 words per half tile, 4 per lane, coalesced
+        uint32_t cur[4];
+        auto load_tile = [&](int32_t j, uint32_t (&w)[4]) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = lane + 32 * i;            // 0..127
+                const int64_t key = (int64_t)j * AX_BN + 32 * half + (idx >> 2);
+                w[i] = key < S ? __ldg(Kw + key * 4 + (idx & 3)) : 0u;
+            }
+        };
+        load_tile(0, cur);
+        bool ok = true;
+        for (int32_t j = 0; j < ntiles && ok; ++j) {
+            const int b = j & 1;
+            uint32_t nxt[4] = {0u, 0u, 0u, 0u};
+            if (j + 1 < ntiles) load_tile(j + 1, nxt);
+            ok = __all_sync(0xffffffffu, mbar_wait(ke_empty(b), ((j >> 1) & 1) ^ 1, abort_flag, 17));
+            if (!ok) break;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int idx = lane + 32 * i;
+                const int key = 32 * half + (idx >> 2), w = idx & 3;
+                uint8_t* row = gke + b * AX_KE_TILE + key * 128;
+                const int sw = key & 7;
+                *reinterpret_cast<uint4*>(row + (((2 * w) ^ sw) << 4)) =
+                    make_uint4(ax_enc_k(cur[i], 0), ax_enc_k(cur[i], 1), ax_enc_k(cur[i], 2), ax_enc_k(cur[i], 3));
+                *reinterpret_cast<uint4*>(row + (((2 * w + 1) ^ sw) << 4)) =
+                    make_uint4(ax_enc_k(cur[i], 4), ax_enc_k(cur[i], 5), ax_enc_k(cur[i], 6), ax_enc_k(cur[i], 7));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ke_full(b));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
+        }
+    } else {
+        // ================= softmax (one thread = one query row = one TMEM lane), then epilogue =================
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int64_t row = q0 + r;
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        {
+            // Q row: 128 bits -> 128 int8 = 32 columns
+            const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * 2);
+            uint32_t qe[32];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t h = row < S ? __ldg(Qw + row * 4 + w) : 0u;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) qe[8 * w + j] = ax_enc_q(h, j);
+            }
+            tc_st32(lane_base + AX_COL_Q, qe);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);
+        }
+        const char* Tc = reinterpret_cast<const char*>(T) + 2 * AX_D;      // acc = 4*h - 2*D -> T[h]
+        float l = 0.f;
+        bool ok = true;
+        for (int32_t j = 0; j < ntiles && ok; ++j) {
+            const int64_t k0 = (int64_t)j * AX_BN;
+            const bool need_mask = (causal && k0 + AX_BN - 1 > q0) || (k0 + AX_BN > S);
+            ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, 18));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sa[32], sb[32], pk[32];
+            tc_ld32(lane_base + AX_COL_S, sa);
+            tc_ld32(lane_base + AX_COL_S + 32, sb);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);         // the next tile's scores may overwrite S
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float p0 = *reinterpret_cast<const float*>(Tc + (int)sa[i]);
+                float p1 = *reinterpret_cast<const float*>(Tc + (int)sa[i + 1]);
+                if (need_mask) {
+                    if (k0 + i >= S || (causal && k0 + i > row)) p0 = 0.f;
+                    if (k0 + i + 1 >= S || (causal && k0 + i + 1 > row)) p1 = 0.f;
+                }
+                l += p0 + p1;
+                pk[i >> 1] = (__float_as_uint(p0) >> 16) | (__float_as_uint(p1) & 0xFFFF0000u);   // entries are bf16-exact
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float p0 = *reinterpret_cast<const float*>(Tc + (int)sb[i]);
+                float p1 = *reinterpret_cast<const float*>(Tc + (int)sb[i + 1]);
+                if (need_mask) {
+                    if (k0 + 32 + i >= S || (causal && k0 + 32 + i > row)) p0 = 0.f;
+                    if (k0 + 32 + i + 1 >= S || (causal && k0 + 32 + i + 1 > row)) p1 = 0.f;
+                }
+                l += p0 + p1;
+                pk[16 + (i >> 1)] = (__float_as_uint(p0) >> 16) | (__float_as_uint(p1) & 0xFFFF0000u);
+            }
+            // P of the previous tile has been consumed by its P.V MMAs
+            ok = __all_sync(0xffffffffu, mbar_wait(p_free, (j & 1) ^ 1, abort_flag, 19));
+            if (!ok) break;
+            tc_fence_after();
+            tc_st32(lane_base + AX_COL_P, pk);
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, 20));
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* orow = O + (bh * S + row) * AX_D;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tc_ld32(lane_base + AX_COL_O + 32 * c, v);
+                tc_wait_ld();
+                if (row < S) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 o4;
+                        o4.x = pack_bf16x2(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                        o4.y = pack_bf16x2(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                        o4.z = pack_bf16x2(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+                        o4.w = pack_bf16x2(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + 32 * c + i) = o4;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"((uint32_t)AX_TMEM_COLS) : "memory");
+    }
+}
+
+// V [BH, S, 128] bf16 as a 3-D tensor, box = [64 d, 64 keys, 1], SWIZZLE_128B: keys past S read as zero
+static bool ax_make_v_map(CUtensorMap* tm, const void* V, int64_t BH, int64_t S) {
+    PFN_tmapEncodeTiled enc = tc5_encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)AX_D, (cuuint64_t)S, (cuuint64_t)BH};
+    const cuuint64_t strides[2] = {(cuuint64_t)AX_D * 2u, (cuuint64_t)S * AX_D * 2u};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)AX_BN, 1u};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(V), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int ax_run(const uint64_t* Qp, const uint64_t* Kp, const void* V, void* O, int64_t BH, int64_t S,
+                  int causal, float neg2c_log2, float bias_log2, cudaStream_t st) {
+    CUtensorMap tmV;
+    BB_REQUIRE(S < (1ll << 31) - AX_BM && ax_make_v_map(&tmV, V, BH, S), BRUTE_ERR_DRIVER);
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_binary_attention_fwd_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, AX_SMEM) != cudaSuccess)
+            return BRUTE_ERR_LAUNCH;
+        attr_set = true;
+    }
+    const int64_t q_tiles = (S + AX_BM - 1) / AX_BM;
+    const dim3 grid((unsigned)q_tiles, (unsigned)BH);
+    k_binary_attention_fwd_tcgen05<<<grid, AX_THREADS, AX_SMEM, st>>>(tmV, Qp, Kp, static_cast<__nv_bfloat16*>(O), S, causal,
+                                                                    neg2c_log2, bias_log2, q_tiles);
+    return launch_status();
+}
+
+}  // namespace bb
