@@ -651,7 +651,7 @@ extern "C" int brute_b200_binary_attention_fwd(const uint64_t* Qp, const uint64_
         const float neg2c = -2.0f * scale_log2;
         const float bias = scale_log2 < 0.f ? neg2c * (float)D : 0.f;      // keeps max(T) == 1
         // BRUTE_ATTENTION_IMPL = tcgen05 (default for D = 128) | mma (mma.sync scores) | popc (CUDA-core scores)
-        static const char* env_impl = std::getenv("BRUTE_ATTENTION_IMPL");
+        const char* env_impl = std::getenv("BRUTE_ATTENTION_IMPL");     // read per call: tests switch it
         const bool want_popc = env_impl && !std::strcmp(env_impl, "popc");
         const bool want_mma = env_impl && !std::strcmp(env_impl, "mma");
         if (D == 128 && !want_popc && !want_mma) {

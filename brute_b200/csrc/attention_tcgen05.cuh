@@ -10,17 +10,18 @@
 //               form, so the row-major V of the caller needs no transpose.
 // Softmax is the table form: P = T[h] (bf16-exact entries, T <= 1), no running maximum, no exp and
 // no rescaling of O, so O simply accumulates in TMEM over all key tiles and is divided by the row
-// sum at the end. One thread owns one query row = one TMEM lane: it reads its 64 scores with
-// tcgen05.ld, looks them up, adds them to its row sum, packs bf16 pairs and writes them back with
-// tcgen05.st. Rounding matches the mma.sync kernels: the row sum adds exactly the bf16 weights that
+// sum at the end. Two threads own one query row = one TMEM lane (32 of the tile's 64 keys each):
+// a thread reads its 32 scores with tcgen05.ld, looks them up, adds them to its part of the row
+// sum, packs bf16 pairs and writes them back with tcgen05.st. Rounding matches the mma.sync kernels: the row sum adds exactly the bf16 weights that
 // enter P.V.
 //
-// CTA = 128 query rows of one (batch, head); 256 threads; 256 TMEM columns (S 64, P 32, Q 32,
+// CTA = 128 query rows of one (batch, head); 384 threads; 256 TMEM columns (S 64, P 32, Q 32,
 // O 128), so two CTAs share an SM and one's softmax overlaps the other's MMAs.
 //   warp 0      TMA producer for V (3-deep ring).
 //   warp 1      MMA issuer, TMEM owner.
 //   warps 2-3   K expanders (double-buffered int8 tile).
-//   warps 4-7   softmax, then the epilogue (tcgen05.ld of O, 1/l, bf16, 16-byte stores).
+//   warps 4-11  softmax, then the epilogue (tcgen05.ld of O, 1/l, bf16, 16-byte stores): warps w and
+//               w + 4 share a TMEM lane quarter and split the key (then the output) columns.
 // Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag and the device
 // status word, and all roles fall through to the common exit where the TMEM is freed.
 #pragma once
@@ -28,7 +29,8 @@
 
 namespace bb {
 
-constexpr int AX_BM = 128, AX_BN = 64, AX_D = 128, AX_THREADS = 256;
+constexpr int AX_BM = 128, AX_BN = 64, AX_D = 128, AX_THREADS = 384;
+constexpr int AX_SOFTMAX_WARPS = 8;
 constexpr int AX_NV = 3;                                   // V stages
 constexpr int AX_V_HALF = AX_BN * 128;                     // [64 keys][64 d] bf16 = 8 KB
 constexpr int AX_V_STAGE = 2 * AX_V_HALF;                  // 16 KB
@@ -36,7 +38,8 @@ constexpr int AX_KE_TILE = AX_BN * AX_D;                   // int8 [64 keys][128
 constexpr int AX_COL_S = 0, AX_COL_P = 64, AX_COL_Q = 96, AX_COL_O = 128, AX_TMEM_COLS = 256;
 constexpr int AX_OFF_KE = AX_NV * AX_V_STAGE;              // 48 KB
 constexpr int AX_OFF_T = AX_OFF_KE + 2 * AX_KE_TILE;       // 64 KB
-constexpr int AX_OFF_BARS = AX_OFF_T + 1024;
+constexpr int AX_OFF_L = AX_OFF_T + 1024;                  // row-sum parts [2][128] floats
+constexpr int AX_OFF_BARS = AX_OFF_L + 1024;
 constexpr int AX_SMEM = AX_OFF_BARS + 256 + 1024;          // + alignment slack
 
 // kind::i8: D s32, A and B signed int8, K-major both, M 128, N 64
@@ -93,6 +96,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     const uint32_t v_ring = base, ke_ring = base + AX_OFF_KE, bars = base + AX_OFF_BARS;
     uint8_t* gke = gbase + AX_OFF_KE;
     float* T = reinterpret_cast<float*>(gbase + AX_OFF_T);
+    float* l_part = reinterpret_cast<float*>(gbase + AX_OFF_L);
     uint8_t* gbars = gbase + AX_OFF_BARS;
     auto v_full   = [&](int s) { return bars + 8u * s; };
     auto v_empty  = [&](int s) { return bars + 8u * (AX_NV + s); };
@@ -115,8 +119,8 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     if (tid == 0) {
         for (int s = 0; s < AX_NV; ++s) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(ke_full(s), 2); mbar_init(ke_empty(s), 1); }
-        mbar_init(s_full, 1); mbar_init(s_free, 4); mbar_init(p_full, 4); mbar_init(p_free, 1);
-        mbar_init(q_full, 4); mbar_init(o_full, 1); mbar_init(drain_bar, 1);
+        mbar_init(s_full, 1); mbar_init(s_free, AX_SOFTMAX_WARPS); mbar_init(p_full, AX_SOFTMAX_WARPS); mbar_init(p_free, 1);
+        mbar_init(q_full, AX_SOFTMAX_WARPS); mbar_init(o_full, 1); mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async_smem();
@@ -234,84 +238,80 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
         }
     } else {
-        // ================= softmax (one thread = one query row = one TMEM lane), then epilogue =================
-        const int quarter = warp & 3;
+        // ================= softmax (two threads per query row = TMEM lane), then epilogue =================
+        const int quarter = warp & 3, grp = (warp - 4) >> 2;       // grp: which 32 of the tile's 64 keys
         const int r = quarter * 32 + lane;
         const int64_t row = q0 + r;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         {
-            // Q row: 128 bits -> 128 int8 = 32 columns
+            // Q row: this thread's 64 bits -> 64 int8 = 16 columns
             const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * 2);
-            uint32_t qe[32];
+            uint32_t qe[16];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const uint32_t h = row < S ? __ldg(Qw + row * 4 + w) : 0u;
+            for (int w = 0; w < 2; ++w) {
+                const uint32_t h = row < S ? __ldg(Qw + row * 4 + 2 * grp + w) : 0u;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) qe[8 * w + j] = ax_enc_q(h, j);
             }
-            tc_st32(lane_base + AX_COL_Q, qe);
+            tc_st16(lane_base + AX_COL_Q + 16 * grp, qe);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(q_full);
         }
-        const char* Tc = reinterpret_cast<const char*>(T) + 2 * AX_D;      // acc = 4*h - 2*D -> T[h]
+        const uint32_t tc_addr = (uint32_t)__cvta_generic_to_shared(T) + 2 * AX_D;      // acc = 4*h - 2*D -> T[h]
         float l = 0.f;
         bool ok = true;
         for (int32_t j = 0; j < ntiles && ok; ++j) {
-            const int64_t k0 = (int64_t)j * AX_BN;
-            const bool need_mask = (causal && k0 + AX_BN - 1 > q0) || (k0 + AX_BN > S);
+            const int64_t k0 = (int64_t)j * AX_BN + 32 * grp;       // first key of this thread's 32
+            const bool need_mask = (causal && k0 + 31 > q0) || (k0 + 32 > S);
             ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, 18));
             if (!ok) break;
             tc_fence_after();
-            uint32_t sa[32], sb[32], pk[32];
-            tc_ld32(lane_base + AX_COL_S, sa);
-            tc_ld32(lane_base + AX_COL_S + 32, sb);
+            uint32_t sc[32], pk[16];
+            tc_ld32(lane_base + AX_COL_S + 32 * grp, sc);
             tc_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);         // the next tile's scores may overwrite S
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                float p0 = *reinterpret_cast<const float*>(Tc + (int)sa[i]);
-                float p1 = *reinterpret_cast<const float*>(Tc + (int)sa[i + 1]);
+                float p0, p1;
+                asm("ld.shared.f32 %0, [%1];" : "=f"(p0) : "r"(tc_addr + sc[i]));
+                asm("ld.shared.f32 %0, [%1];" : "=f"(p1) : "r"(tc_addr + sc[i + 1]));
                 if (need_mask) {
                     if (k0 + i >= S || (causal && k0 + i > row)) p0 = 0.f;
                     if (k0 + i + 1 >= S || (causal && k0 + i + 1 > row)) p1 = 0.f;
                 }
                 l += p0 + p1;
-                pk[i >> 1] = (__float_as_uint(p0) >> 16) | (__float_as_uint(p1) & 0xFFFF0000u);   // entries are bf16-exact
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float p0 = *reinterpret_cast<const float*>(Tc + (int)sb[i]);
-                float p1 = *reinterpret_cast<const float*>(Tc + (int)sb[i + 1]);
-                if (need_mask) {
-                    if (k0 + 32 + i >= S || (causal && k0 + 32 + i > row)) p0 = 0.f;
-                    if (k0 + 32 + i + 1 >= S || (causal && k0 + 32 + i + 1 > row)) p1 = 0.f;
-                }
-                l += p0 + p1;
-                pk[16 + (i >> 1)] = (__float_as_uint(p0) >> 16) | (__float_as_uint(p1) & 0xFFFF0000u);
+                // entries are bf16-exact: the pair is the two upper halves
+                pk[i >> 1] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
             }
             // P of the previous tile has been consumed by its P.V MMAs
             ok = __all_sync(0xffffffffu, mbar_wait(p_free, (j & 1) ^ 1, abort_flag, 19));
             if (!ok) break;
             tc_fence_after();
-            tc_st32(lane_base + AX_COL_P, pk);
+            tc_st16(lane_base + AX_COL_P + 16 * grp, pk);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, 20));
-        if (ok) {
+        // the two halves of a row exchange their sums; one verdict for all softmax warps first
+        l_part[grp * AX_BM + r] = l;
+        uint32_t bad;
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                     : "=r"(bad) : "r"((uint32_t)(!ok)), "n"(AX_SOFTMAX_WARPS * 32) : "memory");
+        if (!bad) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* orow = O + (bh * S + row) * AX_D;
+            const float lsum = l_part[r] + l_part[AX_BM + r];
+            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            __nv_bfloat16* orow = O + (bh * S + row) * AX_D + 64 * grp;      // this thread's 64 of the 128 columns
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t v[32];
-                tc_ld32(lane_base + AX_COL_O + 32 * c, v);
+                tc_ld32(lane_base + AX_COL_O + 64 * grp + 32 * c, v);
                 tc_wait_ld();
                 if (row < S) {
 #pragma unroll

@@ -425,6 +425,31 @@ def test_attention_vs_oracle(ops, co, B, H, S, D, causal):
     assert np.abs(got - want).max() <= ATT_TOL * max(np.abs(want).max(), 1e-6)
 
 
+@pytest.mark.parametrize("S,causal,scale", [(2048, True, None), (1111, False, None), (640, True, -0.05), (512, True, 0.5)])
+def test_attention_kernels_agree(ops, co, monkeypatch, S, causal, scale):
+    # D = 128 has three kernels (tcgen05, mma.sync scores, CUDA-core scores) that round the weights
+    # to bf16 the same way and differ only in the order of fp32 sums; scale 0.5 is too steep for the
+    # table and takes the online-softmax kernel whatever the setting
+    import brute_b200 as brute
+    g = gen(S)
+    q = torch.randn((1, 4, S, 128), generator=g)
+    k = torch.randn((1, 4, S, 128), generator=g)
+    v = torch.randn((1, 4, S, 128), generator=g).to(torch.bfloat16).to(DEV)
+    qb, kb = brute.pack_sign(q.to(DEV), ge0=True), brute.pack_sign(k.to(DEV), ge0=True)
+    outs = {}
+    for impl in ("tcgen05", "mma", "popc"):
+        monkeypatch.setenv("BRUTE_ATTENTION_IMPL", impl)
+        outs[impl] = brute.binary_attention(qb, kb, v, causal=causal, scale=scale).float()
+    monkeypatch.delenv("BRUTE_ATTENTION_IMPL")
+    ref = outs["popc"]
+    for impl in ("tcgen05", "mma"):
+        assert float((outs[impl] - ref).abs().max()) <= 1e-2 * float(ref.abs().max()), impl
+    want = co.binary_attention(co.pack_sign_f32(q.numpy(), 1), co.pack_sign_f32(k.numpy(), 1),
+                               v.float().cpu().numpy(), causal, 128 ** -0.5 if scale is None else scale)
+    assert np.abs(outs["tcgen05"].cpu().numpy() - want).max() <= ATT_TOL * np.abs(want).max()
+    assert status_ok()
+
+
 def test_attention_first_row_is_v0(ops):
     # causal: query 0 sees only key 0, so the output row is exactly V[0]
     import brute_b200 as brute
