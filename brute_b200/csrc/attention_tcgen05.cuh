@@ -1,13 +1,18 @@
 // Fused binary attention forward on the 5th-generation tensor cores (D = 128).
 //
 // Both contractions run on tcgen05.mma with accumulators in tensor memory:
-//   S = Q.K^T   kind::i8, M128 N64 K32 x 4. Q (+1/-1) is expanded once per CTA into TMEM and is the
-//               A operand; the K tile (64 keys) is expanded from packed bits to int8 (-2/+2) in
-//               shared memory, K-major SWIZZLE_128B. The accumulator is 4*h - 2*D for Hamming
-//               distance h, i.e. the byte offset of T[h] from the middle of the float table.
+//   S = Q.K^T   kind::i8, M128 N64 K32 x 4. Q (+1/-1) is expanded once per CTA and the K tile
+//               (64 keys, -2/+2) once per tile from packed bits to int8 in shared memory, both
+//               K-major SWIZZLE_128B. The accumulator is 4*h - 2*D for Hamming distance h, i.e.
+//               the byte offset of T[h] from the middle of the float table.
 //   O += P.V    kind::f16 (bf16), M128 N128 K16 x 4. P is the A operand, read from TMEM; V arrives by
 //               TMA as two [64 keys x 64 d] SWIZZLE_128B boxes and is the B operand in MN-major
 //               form, so the row-major V of the caller needs no transpose.
+// S is double buffered in tensor memory and P is written over the S it came from (a thread's bf16
+// weights go into the first half of the columns it just read), so the score MMA of tile j+2 is
+// issued right behind the P.V MMA of tile j: the tensor pipe executes in order, which is all the
+// buffer reuse needs, and the round trip softmax -> MMA issuer -> tcgen05.commit -> softmax is off
+// the softmax threads' critical path.
 // Softmax is the table form: P = T[h] (bf16-exact entries, T <= 1), no running maximum, no exp and
 // no rescaling of O, so O simply accumulates in TMEM over all key tiles and is divided by the row
 // sum at the end. Two threads own one query row = one TMEM lane (32 of the tile's 64 keys each):
@@ -15,8 +20,8 @@
 // sum, packs bf16 pairs and writes them back with tcgen05.st. Rounding matches the mma.sync kernels: the row sum adds exactly the bf16 weights that
 // enter P.V.
 //
-// CTA = 128 query rows of one (batch, head); 384 threads; 256 TMEM columns (S 64, P 32, Q 32,
-// O 128), so two CTAs share an SM and one's softmax overlaps the other's MMAs.
+// CTA = 128 query rows of one (batch, head); 384 threads; 256 TMEM columns (S/P 2 x 64, O 128),
+// so two CTAs share an SM.
 //   warp 0      TMA producer for V (3-deep ring).
 //   warp 1      MMA issuer, TMEM owner.
 //   warps 2-3   K expanders (double-buffered int8 tile).
@@ -35,9 +40,11 @@ constexpr int AX_NV = 3;                                   // V stages
 constexpr int AX_V_HALF = AX_BN * 128;                     // [64 keys][64 d] bf16 = 8 KB
 constexpr int AX_V_STAGE = 2 * AX_V_HALF;                  // 16 KB
 constexpr int AX_KE_TILE = AX_BN * AX_D;                   // int8 [64 keys][128 d] = 8 KB
-constexpr int AX_COL_S = 0, AX_COL_P = 64, AX_COL_Q = 96, AX_COL_O = 128, AX_TMEM_COLS = 256;
+constexpr int AX_COL_S = 0 /* two buffers of 64 */, AX_COL_O = 128, AX_TMEM_COLS = 256;
+constexpr int AX_Q_TILE = AX_BM * AX_D;                    // int8 [128 rows][128 d] = 16 KB
 constexpr int AX_OFF_KE = AX_NV * AX_V_STAGE;              // 48 KB
-constexpr int AX_OFF_T = AX_OFF_KE + 2 * AX_KE_TILE;       // 64 KB
+constexpr int AX_OFF_Q = AX_OFF_KE + 2 * AX_KE_TILE;       // 64 KB
+constexpr int AX_OFF_T = AX_OFF_Q + AX_Q_TILE;             // 80 KB
 constexpr int AX_OFF_L = AX_OFF_T + 1024;                  // row-sum parts [2][128] floats
 constexpr int AX_OFF_BARS = AX_OFF_L + 1024;
 constexpr int AX_SMEM = AX_OFF_BARS + 256 + 1024;          // + alignment slack
@@ -51,6 +58,12 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[shared-memory descriptor] * B[shared-memory descriptor]
+__device__ __forceinline__ void tc_mma_i8_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, int32_t c2, uint32_t bar) {
     asm volatile(
@@ -93,8 +106,9 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(ax_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* gbase = ax_smem_raw + (base - raw);
-    const uint32_t v_ring = base, ke_ring = base + AX_OFF_KE, bars = base + AX_OFF_BARS;
+    const uint32_t v_ring = base, ke_ring = base + AX_OFF_KE, q_tile = base + AX_OFF_Q, bars = base + AX_OFF_BARS;
     uint8_t* gke = gbase + AX_OFF_KE;
+    uint8_t* gq = gbase + AX_OFF_Q;
     float* T = reinterpret_cast<float*>(gbase + AX_OFF_T);
     float* l_part = reinterpret_cast<float*>(gbase + AX_OFF_L);
     uint8_t* gbars = gbase + AX_OFF_BARS;
@@ -102,8 +116,10 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     auto v_empty  = [&](int s) { return bars + 8u * (AX_NV + s); };
     auto ke_full  = [&](int s) { return bars + 8u * (2 * AX_NV + s); };
     auto ke_empty = [&](int s) { return bars + 8u * (2 * AX_NV + 2 + s); };
-    const uint32_t s_full = bars + 8u * (2 * AX_NV + 4), s_free = s_full + 8u, p_full = s_full + 16u, p_free = s_full + 24u;
-    const uint32_t q_full = s_full + 32u, o_full = s_full + 40u, drain_bar = s_full + 48u;
+    const uint32_t s_full0 = bars + 8u * (2 * AX_NV + 4), p_full0 = s_full0 + 16u;      // [2] each, by S/P buffer
+    auto s_full = [&](int b) { return s_full0 + 8u * b; };
+    auto p_full = [&](int b) { return p_full0 + 8u * b; };
+    const uint32_t q_full = s_full0 + 32u, o_full = s_full0 + 40u, drain_bar = s_full0 + 48u;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (2 * AX_NV + 4 + 7));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (2 * AX_NV + 4 + 7) + 4);
 
@@ -119,7 +135,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     if (tid == 0) {
         for (int s = 0; s < AX_NV; ++s) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(ke_full(s), 2); mbar_init(ke_empty(s), 1); }
-        mbar_init(s_full, 1); mbar_init(s_free, AX_SOFTMAX_WARPS); mbar_init(p_full, AX_SOFTMAX_WARPS); mbar_init(p_free, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(s_full(b), 1); mbar_init(p_full(b), AX_SOFTMAX_WARPS); }
         mbar_init(q_full, AX_SOFTMAX_WARPS); mbar_init(o_full, 1); mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -161,37 +177,41 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         // ================= MMA issuer =================
         if (lane == 0) {
             bool ok = mbar_wait(q_full, 0, abort_flag, 12);
+            const uint64_t qdesc = tc_smem_desc(q_tile);
             auto issue_qk = [&](int32_t j) -> bool {
+                // Writes S buffer j % 2. Its last reader is the P.V MMA of tile j - 2, issued before
+                // this one, and the tensor pipe runs in issue order.
                 const int b = j & 1;
                 if (!mbar_wait(ke_full(b), (j >> 1) & 1, abort_flag, 13)) return false;
-                if (j > 0 && !mbar_wait(s_free, (j - 1) & 1, abort_flag, 14)) return false;
                 tc_fence_after();
                 const uint64_t kdesc = tc_smem_desc(ke_ring + b * AX_KE_TILE);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)      // 32 bytes of d per instruction
-                    tc_mma_i8_ts(tmem + AX_COL_S, tmem + (uint32_t)(AX_COL_Q + 8 * k), kdesc + 2u * k, AX_IDESC_QK, k > 0 ? 1u : 0u);
-                tc_commit(s_full);
+                    tc_mma_i8_ss(tmem + (uint32_t)(AX_COL_S + 64 * b), qdesc + 2u * k, kdesc + 2u * k, AX_IDESC_QK, k > 0 ? 1u : 0u);
+                tc_commit(s_full(b));
                 tc_commit(ke_empty(b));
                 return true;
             };
             auto issue_pv = [&](int32_t j) -> bool {
-                const int s = j % AX_NV;
+                const int s = j % AX_NV, b = j & 1;
                 if (!mbar_wait(v_full(s), (j / AX_NV) & 1, abort_flag, 15)) return false;
-                if (!mbar_wait(p_full, j & 1, abort_flag, 16)) return false;
+                if (!mbar_wait(p_full(b), (j >> 1) & 1, abort_flag, 16)) return false;
                 tc_fence_after();
                 const uint64_t vdesc = ax_v_desc(v_ring + s * AX_V_STAGE);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)      // 16 keys per instruction = two 1024-byte atoms
-                    tc_mma_f16_ts(tmem + AX_COL_O, tmem + (uint32_t)(AX_COL_P + 8 * k), vdesc + (uint64_t)(128u * k), AX_IDESC_PV,
-                                  (j > 0 || k > 0) ? 1u : 0u);
-                tc_commit(p_free);
+                for (int k = 0; k < 4; ++k) {    // 16 keys per instruction = two 1024-byte atoms of V
+                    // P of keys [16k, 16k+16): 8 columns, inside the S columns of the thread that wrote them
+                    const uint32_t pcol = (uint32_t)(AX_COL_S + 64 * b + 32 * (k >> 1) + 8 * (k & 1));
+                    tc_mma_f16_ts(tmem + AX_COL_O, tmem + pcol, vdesc + (uint64_t)(128u * k), AX_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+                }
                 tc_commit(v_empty(s));
                 return true;
             };
             if (ok) ok = issue_qk(0);
+            if (ok && ntiles > 1) ok = issue_qk(1);
             for (int32_t j = 0; j < ntiles && ok; ++j) {
-                if (j + 1 < ntiles) ok = issue_qk(j + 1);
-                if (ok) ok = issue_pv(j);
+                ok = issue_pv(j);
+                if (ok && j + 2 < ntiles) ok = issue_qk(j + 2);
             }
             if (ok) tc_commit(o_full);
             tc_commit(drain_bar);
@@ -244,18 +264,19 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         const int64_t row = q0 + r;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         {
-            // Q row: this thread's 64 bits -> 64 int8 = 16 columns
+            // Q row: this thread's 64 bits -> 64 int8 = chunks 4 grp .. 4 grp + 3 of the 128-byte operand row
             const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * 2);
-            uint32_t qe[16];
+            uint8_t* qrow = gq + r * 128;
 #pragma unroll
             for (int w = 0; w < 2; ++w) {
                 const uint32_t h = row < S ? __ldg(Qw + row * 4 + 2 * grp + w) : 0u;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) qe[8 * w + j] = ax_enc_q(h, j);
+                const int ch = 4 * grp + 2 * w;
+                *reinterpret_cast<uint4*>(qrow + ((ch ^ (r & 7)) << 4)) =
+                    make_uint4(ax_enc_q(h, 0), ax_enc_q(h, 1), ax_enc_q(h, 2), ax_enc_q(h, 3));
+                *reinterpret_cast<uint4*>(qrow + (((ch + 1) ^ (r & 7)) << 4)) =
+                    make_uint4(ax_enc_q(h, 4), ax_enc_q(h, 5), ax_enc_q(h, 6), ax_enc_q(h, 7));
             }
-            tc_st16(lane_base + AX_COL_Q + 16 * grp, qe);
-            tc_wait_st();
-            tc_fence_before();
+            fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(q_full);
         }
@@ -265,15 +286,14 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         for (int32_t j = 0; j < ntiles && ok; ++j) {
             const int64_t k0 = (int64_t)j * AX_BN + 32 * grp;       // first key of this thread's 32
             const bool need_mask = (causal && k0 + 31 > q0) || (k0 + 32 > S);
-            ok = __all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag, 18));
+            const int b = j & 1;
+            const uint32_t my_cols = lane_base + (uint32_t)(AX_COL_S + 64 * b + 32 * grp);
+            ok = __all_sync(0xffffffffu, mbar_wait(s_full(b), (j >> 1) & 1, abort_flag, 18));
             if (!ok) break;
             tc_fence_after();
             uint32_t sc[32], pk[16];
-            tc_ld32(lane_base + AX_COL_S + 32 * grp, sc);
+            tc_ld32(my_cols, sc);
             tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free);         // the next tile's scores may overwrite S
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
                 float p0, p1;
@@ -287,15 +307,12 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                 // entries are bf16-exact: the pair is the two upper halves
                 pk[i >> 1] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
             }
-            // P of the previous tile has been consumed by its P.V MMAs
-            ok = __all_sync(0xffffffffu, mbar_wait(p_free, (j & 1) ^ 1, abort_flag, 19));
-            if (!ok) break;
-            tc_fence_after();
-            tc_st16(lane_base + AX_COL_P + 16 * grp, pk);
+            // over the first 16 of the 32 columns this thread has just read
+            tc_st16(my_cols, pk);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full(b));
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, 20));
         // the two halves of a row exchange their sums; one verdict for all softmax warps first
