@@ -53,7 +53,7 @@ def parse_args():
     ap.add_argument("--op", default="gemm",
                     help="time ONE op alone (for profiler captures): gemm | pack_sign | pack_bool | unpack_bool | "
                          "unpack_pm1 | popcount_total | hamming_total | word_popcount | xor | not | attention | mlp | "
-                         "pack_bool_4097 | unpack_bool_4097 | memset")
+                         "pack_bool_4097 | unpack_bool_4097 | memset | transpose_bits | any_dim0")
     ap.add_argument("--log2-bits", type=int, default=28, help="size of the bandwidth ops under --op")
     ap.add_argument("--att", default="2,8,4096,128", help="B,H,S,D of --op attention")
     return ap.parse_args()
@@ -425,7 +425,10 @@ def secondary_workloads(dev, peaks, flush, sync):
     bw("word_popcount_2^30", lambda: ops.popcount(p), n // 8 + n // 16)
     bw("xor_2^30", lambda: ops.bitwise_packed(p, q, 2, n), 3 * n // 8)
     bw("not_2^30", lambda: ops.bit1_not_packed(p, n), 2 * n // 8)
-    del p, q
+    p2 = p.view(32768, 512)
+    bw("transpose_bits_32768x32768", lambda: ops.transpose_packed(p2, 32768, 32768), 2 * n // 8)
+    bw("any_dim0_4096x2^18", lambda: ops.reduce_rows_packed(p.view(4096, 4096), 0, True), n // 8 + (1 << 18) // 8)
+    del p, q, p2
     xb = torch.rand((4096, 4097), generator=g, device=dev) < 0.3
     bw("pack_bool_4096x4097", lambda: ops.pack_bool(xb), 4096 * 4097 + 4096 * 65 * 8)
     pb = ops.pack_bool(xb)
@@ -514,6 +517,9 @@ def run_single_op(args):
             "word_popcount": (lambda: ops.popcount(p), n // 8 + n // 16),
             "xor": (lambda: ops.bitwise_packed(p, q, 2, n), 3 * n // 8),
             "not": (lambda: ops.bit1_not_packed(p, n), 2 * n // 8),
+            "transpose_bits": (lambda: ops.transpose_packed(p.view(1 << (args.log2_bits // 2), -1), 1 << (args.log2_bits // 2),
+                                                           64 * ((n // 64) >> (args.log2_bits // 2))), 2 * n // 8),
+            "any_dim0": (lambda: ops.reduce_rows_packed(p.view(4096, -1), 0, True), n // 8 + n // 8 // 4096),
         }
         if args.op == "pack_bool":
             xb = ops.unpack_bool(p, [n])

@@ -44,6 +44,8 @@ _DEF.define("row_all(Tensor A, int last_dim_bits) -> Tensor")
 _DEF.define("xnor_popcount_matmul_impl(Tensor A, Tensor B, int K, int impl) -> Tensor")
 _DEF.define("xnor_matmul_scale_sign_pack(Tensor A, Tensor B, Tensor scale, int K, int mode) -> Tensor")
 _DEF.define("binary_attention(Tensor Qp, Tensor Kp, Tensor V, bool causal, float scale) -> Tensor")
+_DEF.define("transpose_packed(Tensor packed, int rows, int cols) -> Tensor")
+_DEF.define("reduce_rows_packed(Tensor packed, int dim, bool use_or) -> Tensor")
 
 _PACK_WIDTH = 64
 _SIGN_DTYPES = {torch.float32: L.DT_F32, torch.bfloat16: L.DT_BF16, torch.float16: L.DT_F16}
@@ -317,6 +319,46 @@ def row_all(A: torch.Tensor, last_dim_bits: int) -> torch.Tensor:
     return out
 
 
+def transpose_packed(packed: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    """packed [..., rows, ceil(cols/64)] -> packed [..., cols, ceil(rows/64)]: the bit matrices transposed."""
+    _check(packed.dim() >= 2 and packed.dtype == torch.int64, "transpose_packed: input must be int64 with >= 2 dims")
+    rows, cols = int(rows), int(cols)
+    _check(packed.size(-2) == rows and packed.size(-1) == _words(cols),
+           "transpose_packed: packed shape must be [..., rows, ceil(cols/64)]")
+    pc = packed.contiguous()
+    batch = 1
+    for d in pc.shape[:-2]:
+        batch *= int(d)
+    out = torch.empty(tuple(pc.shape[:-2]) + (cols, _words(rows)), dtype=torch.int64, device=pc.device)
+    if out.numel():
+        with torch.cuda.device(pc.device):
+            L.check(_lib.brute_b200_transpose_bits(pc.data_ptr(), out.data_ptr(), batch, rows, cols, _stream(pc)),
+                    "transpose_packed")
+    return out
+
+
+def reduce_rows_packed(packed: torch.Tensor, dim: int, use_or: bool) -> torch.Tensor:
+    """OR (any) or AND (all) over a non-packed dimension of a packed buffer, in one pass."""
+    _check(packed.dtype == torch.int64 and packed.dim() >= 2, "reduce_rows_packed: input must be int64 with >= 2 dims")
+    nd = packed.dim()
+    d = int(dim) if int(dim) >= 0 else nd + int(dim)
+    _check(0 <= d < nd - 1, "reduce_rows_packed: dim must be a non-packed dimension")
+    pc = packed.contiguous()
+    outer = 1
+    for s_ in pc.shape[:d]:
+        outer *= int(s_)
+    inner = 1
+    for s_ in pc.shape[d + 1:]:
+        inner *= int(s_)
+    out = torch.empty(tuple(pc.shape[:d]) + tuple(pc.shape[d + 1:]), dtype=torch.int64, device=pc.device)
+    if out.numel():
+        with torch.cuda.device(pc.device):
+            L.check(_lib.brute_b200_reduce_rows(L.OP_OR if use_or else L.OP_AND, pc.data_ptr() if pc.numel() else None,
+                                                out.data_ptr(), outer, int(pc.size(d)), inner, _stream(pc)),
+                    "reduce_rows_packed")
+    return out
+
+
 def randomize_bits(out: torch.Tensor) -> torch.Tensor:
     out.random_()          # cbrute/cuda/ops_cuda.cu:340, a plain ATen call
     return out
@@ -352,6 +394,7 @@ _CUDA_IMPLS = {
     "pack_sign": pack_sign, "bitwise_packed": bitwise_packed, "select_packed": select_packed,
     "row_any": row_any, "row_all": row_all, "xnor_popcount_matmul_impl": xnor_popcount_matmul_impl,
     "xnor_matmul_scale_sign_pack": xnor_matmul_scale_sign_pack, "binary_attention": binary_attention,
+    "transpose_packed": transpose_packed, "reduce_rows_packed": reduce_rows_packed,
 }
 _IMPL = torch.library.Library("brute", "IMPL", "CUDA")
 for _name, _fn in _CUDA_IMPLS.items():
@@ -387,6 +430,11 @@ def _register_fakes() -> None:
     reg("brute::row_all")(lambda A, last_dim_bits: A.new_empty(A.shape[:-1], dtype=torch.bool))
     reg("brute::signed_bundle")(lambda W, V, D: V.new_empty((W.shape[0], W.shape[1], V.shape[2]), dtype=torch.int64))
     reg("brute::binary_attention")(lambda Qp, Kp, V, causal, scale: torch.empty_like(V))
+    reg("brute::transpose_packed")(
+        lambda packed, rows, cols: packed.new_empty(tuple(packed.shape[:-2]) + (cols, _words(rows)), dtype=torch.int64))
+    reg("brute::reduce_rows_packed")(
+        lambda packed, dim, use_or: packed.new_empty(tuple(s for i, s in enumerate(packed.shape) if i != dim % packed.dim()),
+                                                     dtype=torch.int64))
 
 
 try:

@@ -212,10 +212,25 @@ class Tensor(torch.Tensor):
             return cache
         ver = _plain(self)._version
         if cache is None or d.get("_packed_ver") != ver:
-            cache = _pack_bool(_plain(self))
+            cache = self._packed_from_transposed_source()
+            if cache is None:
+                cache = _pack_bool(_plain(self))
             d["_packed_buf_cache"] = cache
             d["_packed_ver"] = ver
         return cache
+
+    def _packed_from_transposed_source(self) -> Optional[torch.Tensor]:
+        """A transpose of the last two dimensions whose source still has (or can make) its packed
+        words: transpose the bit matrices in the packed domain instead of packing the bool view."""
+        src = self.__dict__.get("_t_source")
+        if src is None or not _is_b1(src) or src.dim() < 2 or src.dim() != self.dim():
+            return None
+        if tuple(src.shape[:-2]) != tuple(self.shape[:-2]) or src.shape[-1] != self.shape[-2] or src.shape[-2] != self.shape[-1]:
+            return None
+        sp = src._packed_buf_contig()
+        if sp is None:
+            return None
+        return _ops.transpose_packed(sp, int(src.shape[-2]), int(src.shape[-1]))
 
     @_packed_buf.setter
     def _packed_buf(self, val: Optional[torch.Tensor]) -> None:
@@ -646,7 +661,8 @@ class Tensor(torch.Tensor):
         one remembers its source for the matmul fast path."""
         self._ensure_bool_valid()
         inst = Tensor._make_bit1(_plain(self).transpose(d0, d1), lazy_pack=True)
-        if self.dim() == 2:
+        nd = self.dim()
+        if {d0, d1} == {nd - 2, nd - 1}:
             inst.__dict__["_t_source"] = self
         return inst
 
@@ -932,19 +948,9 @@ def _h_sum(func, args, kwargs, b1):
 
 
 def _reduce_leading(packed: torch.Tensor, dim: int, use_or: bool) -> torch.Tensor:
-    """OR / AND over a non-packed axis by halving: O(log n) word-wise launches."""
-    if dim != 0:
-        order = [dim] + [i for i in range(packed.dim()) if i != dim]
-        packed = packed.permute(*order).contiguous()
-    op = torch.bitwise_or if use_or else torch.bitwise_and
-    while packed.shape[0] > 1:
-        m = packed.shape[0]
-        half = m // 2
-        merged = op(packed[:half], packed[half:2 * half])
-        if m & 1:
-            merged[0:1] = op(merged[0:1], packed[m - 1:m])
-        packed = merged
-    return packed[0]
+    """OR / AND over a non-packed, non-empty axis of the packed words in one fused pass
+    (the reference halves the axis log2(n) times with ATen launches, brute/tensor.py:1440-1457)."""
+    return _ops.reduce_rows_packed(packed, dim, use_or)
 
 
 @_fast(*_ALL_FUNCS, *_ANY_FUNCS)
@@ -975,6 +981,8 @@ def _h_all_any(func, args, kwargs, b1):
             res = res.unsqueeze(-1)
         return Tensor._make_plain(res) if res.dim() == 0 else Tensor._make_bit1(res)
     if 0 <= d < nd - 1:
+        if a.shape[d] == 0:
+            return NotImplemented       # identity of an empty axis: leave it to the bool path
         out = _reduce_leading(a._packed_buf_contig(), d, is_any)
         shape = list(a.shape)
         if keepdim:

@@ -159,6 +159,21 @@ int brute_b200_row_any(const uint64_t* a, uint8_t* out, int64_t rows,
 int brute_b200_row_all(const uint64_t* a, uint8_t* out, int64_t rows,
                        int64_t words_per_row, int64_t last_dim_bits, void* stream);
 
+/* ---- layout on packed words ------------------------------------------- */
+/* Bit-matrix transpose: in [batch, R, ceil(C/64)] -> out [batch, C, ceil(R/64)],
+ * out bit (c, r) = in bit (r, c); pad bits of `out` are 0. in and out must not overlap.
+ * Replaces the unpack -> bool transpose -> re-pack round trip that the reference takes
+ * whenever a transpose moves the packed axis (brute/tensor.py:699-775, 1112-1121). */
+int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out,
+                              int64_t batch, int64_t R, int64_t C, void* stream);
+
+/* OR (BRUTE_OP_OR) or AND (BRUTE_OP_AND) over the middle axis of in [outer, R, inner]
+ * words -> out [outer, inner] words: any()/all() over a non-packed dimension in one pass.
+ * R == 0 gives the identity (0 / all ones). The output is preset by a memset on `stream`.
+ * Replaces the log2(R) halving loop of ATen launches, brute/tensor.py:1440-1457. */
+int brute_b200_reduce_rows(int op, const uint64_t* in, uint64_t* out,
+                           int64_t outer, int64_t R, int64_t inner, void* stream);
+
 /* ---- xnor-popcount GEMM ------------------------------------------------ */
 /* A [M, Kp] words, B [N, Kp] words (rows of B are output features), K logical
  * bits (K <= 64*Kp, pad bits 0) -> C [M, N] int32 with row pitch ldc elements,

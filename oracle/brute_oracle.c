@@ -415,3 +415,31 @@ void oracle_binary_attention(const uint64_t* Qp, const uint64_t* Kp_, const floa
             free(p);
         }
 }
+
+
+/* Bit-matrix transpose of packed rows. The reference has no packed transpose: a transpose that
+ * moves the packed axis unpacks, transposes the bools and packs again (brute/tensor.py:699-775,
+ * 1112-1121); this is that composition bit by bit. in [batch, R, ceil(C/64)] -> out [batch, C, ceil(R/64)]. */
+void oracle_transpose_bits(const uint64_t* in, uint64_t* out, int64_t batch, int64_t R, int64_t C) {
+    const int64_t wi = (C + 63) / 64, wo = (R + 63) / 64;
+    memset(out, 0, (size_t)(batch * C * wo) * 8);
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t r = 0; r < R; ++r)
+            for (int64_t c = 0; c < C; ++c)
+                if ((in[(b * R + r) * wi + (c >> 6)] >> (c & 63)) & 1ull)
+                    out[(b * C + c) * wo + (r >> 6)] |= 1ull << (r & 63);
+}
+
+/* any / all over a non-packed axis: OR / AND of the packed words (brute/tensor.py:1440-1457 does
+ * it by halving). op: 1 = OR, 0 = AND (the BRUTE_OP_* codes). in [outer, R, inner] -> out [outer, inner]. */
+void oracle_reduce_rows(int op, const uint64_t* in, uint64_t* out, int64_t outer, int64_t R, int64_t inner) {
+    for (int64_t o = 0; o < outer; ++o)
+        for (int64_t i = 0; i < inner; ++i) {
+            uint64_t acc = op == 1 ? 0ull : ~0ull;
+            for (int64_t r = 0; r < R; ++r) {
+                const uint64_t v = in[(o * R + r) * inner + i];
+                acc = op == 1 ? (acc | v) : (acc & v);
+            }
+            out[o * inner + i] = acc;
+        }
+}

@@ -54,6 +54,8 @@ def lib():
         L.oracle_xnor_gemm_scale_sign_pack.argtypes = [p, p, p, p, i64, i64, i64, i64, i32]
         L.oracle_signed_bundle.argtypes = [p, p, p, i64, i64, i64, i64, i64]
         L.oracle_binary_attention.argtypes = [p, p, p, p, i64, i64, i64, i32, f32]
+        L.oracle_transpose_bits.argtypes = [p, p, i64, i64, i64]
+        L.oracle_reduce_rows.argtypes = [i32, p, p, i64, i64, i64]
         _lib = L
     return _lib
 
@@ -245,4 +247,26 @@ def binary_attention(Qp, Kp, V, causal: bool, scale: float) -> np.ndarray:
     out = np.zeros_like(V)
     if out.size:
         lib().oracle_binary_attention(_ptr(Qp), _ptr(Kp), _ptr(V), _ptr(out), B * H, S, D, int(bool(causal)), float(scale))
+    return out
+
+
+def transpose_bits(packed: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    """packed [..., rows, ceil(cols/64)] -> packed [..., cols, ceil(rows/64)]."""
+    p = _u64(packed)
+    batch = int(np.prod(p.shape[:-2], dtype=np.int64)) if p.ndim > 2 else 1
+    out = np.zeros(p.shape[:-2] + (int(cols), (int(rows) + 63) // 64), dtype=np.uint64)
+    if out.size:
+        lib().oracle_transpose_bits(_ptr(p), _ptr(out), batch, int(rows), int(cols))
+    return out
+
+
+def reduce_rows(packed: np.ndarray, dim: int, use_or: bool) -> np.ndarray:
+    """OR / AND of packed words over a non-packed axis."""
+    p = _u64(packed)
+    d = dim % p.ndim
+    outer = int(np.prod(p.shape[:d], dtype=np.int64))
+    inner = int(np.prod(p.shape[d + 1:], dtype=np.int64))
+    out = np.zeros(p.shape[:d] + p.shape[d + 1:], dtype=np.uint64)
+    if out.size:
+        lib().oracle_reduce_rows(1 if use_or else 0, _ptr(p), _ptr(out), outer, int(p.shape[d]), inner)
     return out

@@ -150,6 +150,8 @@ def install_oracle_cpu_ops():
     lib.impl("row_all", lambda A, bits: torch.from_numpy(co.row_all(t2n(A), bits)))
 
     lib.impl("signed_bundle", lambda W, V, D: n2t(co.signed_bundle(t2n(W), t2n(V), D), torch.int64))
+    lib.impl("transpose_packed", lambda packed, rows, cols: n2t(co.transpose_bits(t2n(packed.contiguous()), rows, cols), torch.int64))
+    lib.impl("reduce_rows_packed", lambda packed, dim, use_or: n2t(co.reduce_rows(t2n(packed.contiguous()), dim, use_or), torch.int64))
 
     def randomize(out):
         out.random_()

@@ -380,6 +380,44 @@ def test_mlp_config4_chain(ops, co):
 
 
 # ---------------------------------------------------------------------------
+# layout: bit-matrix transpose, any/all over a non-packed axis
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (64, 64), (65, 63), (130, 257), (256, 256), (257, 1000), (1000, 257),
+                                   (2, 3, 70, 129), (5, 300, 64), (4096, 4097), (1, 100000), (100000, 1)])
+def test_transpose_packed(ops, co, shape):
+    import brute_b200 as brute
+    x = torch.rand(shape, generator=gen(sum(shape))) < 0.5
+    p = ops.pack_bool(x.to(DEV))
+    got = ops.transpose_packed(p, shape[-2], shape[-1])
+    assert tuple(got.shape) == shape[:-2] + (shape[-1], (shape[-2] + 63) // 64)
+    assert np.array_equal(u64(got), co.pack_bool(x.transpose(-1, -2).contiguous().numpy()))
+    assert np.array_equal(u64(got), co.transpose_bits(u64(p), shape[-2], shape[-1]))
+    # involution, and the front end takes this path for .transpose(-1, -2) of a packed tensor
+    assert torch.equal(ops.transpose_packed(got, shape[-1], shape[-2]), p)
+    b = brute.Tensor(x.to(DEV), dtype=brute.bit1)
+    bt = b.transpose(-1, -2)
+    assert torch.equal(bt._packed_buf, got)
+    assert torch.equal(bt.bool().as_subclass(torch.Tensor).cpu(), x.transpose(-1, -2))
+
+
+@pytest.mark.parametrize("shape,dim", [((5, 70), 0), ((1, 3), 0), ((4, 6, 130), 1), ((4, 6, 130), 0), ((2, 1, 64), 1),
+                                       ((1000, 4097), 0), ((3, 100000, 65), 1), ((70000, 64), 0)])
+def test_reduce_rows_packed(ops, co, shape, dim):
+    import brute_b200 as brute
+    x = torch.rand(shape, generator=gen(sum(shape))) < 0.999
+    x[..., 0] = False        # some all-false columns for any()
+    p = ops.pack_bool(x.to(DEV))
+    for use_or, ref in ((True, x.any(dim=dim)), (False, x.all(dim=dim))):
+        got = ops.reduce_rows_packed(p, dim, use_or)
+        assert np.array_equal(u64(got), co.pack_bool(ref.numpy())), use_or
+    b = brute.Tensor(x.to(DEV), dtype=brute.bit1)
+    assert torch.equal(b.any(dim=dim).bool().as_subclass(torch.Tensor).cpu(), x.any(dim=dim))
+    assert torch.equal(b.all(dim=dim).bool().as_subclass(torch.Tensor).cpu(), x.all(dim=dim))
+    with pytest.raises(RuntimeError, match="non-packed"):
+        ops.reduce_rows_packed(p, len(shape) - 1, True)
+
+
+# ---------------------------------------------------------------------------
 # signed_bundle
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("B,M,N,D", [(1, 1, 1, 1), (2, 5, 7, 70), (1, 33, 130, 128), (3, 64, 256, 64),

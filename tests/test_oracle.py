@@ -162,3 +162,20 @@ def test_signed_bundle_vs_numpy():
         got = co.signed_bundle(W, co.pack_bool(v), D)
         acc = np.einsum("bmn,bnd->bmd", W.astype(np.int32), np.where(v, 1, -1).astype(np.int32))
         assert np.array_equal(got, no.pack_bool(acc >= 0)), (B, M, N, D)
+
+
+def test_transpose_bits_vs_numpy():
+    rng = np.random.default_rng(31)
+    for shape in [(1, 1), (3, 5), (64, 64), (65, 63), (130, 257), (2, 3, 70, 129)]:
+        x = rng.random(shape) < 0.5
+        got = co.transpose_bits(co.pack_bool(x), shape[-2], shape[-1])
+        assert np.array_equal(got, no.pack_bool(np.swapaxes(x, -1, -2))), shape
+
+
+def test_reduce_rows_vs_numpy():
+    rng = np.random.default_rng(32)
+    for shape, dim in [((5, 70), 0), ((1, 3), 0), ((4, 6, 130), 1), ((4, 6, 130), 0), ((2, 1, 64), 1)]:
+        x = rng.random(shape) < 0.7
+        p = co.pack_bool(x)
+        assert np.array_equal(co.reduce_rows(p, dim, True), no.pack_bool(x.any(axis=dim))), (shape, dim)
+        assert np.array_equal(co.reduce_rows(p, dim, False), no.pack_bool(x.all(axis=dim))), (shape, dim)
