@@ -156,7 +156,10 @@ class Tensor(torch.Tensor):
         bool storage is allocated uninitialised and marked dirty."""
         dirty = bool_view is None
         if dirty:
-            bool_t = torch.empty(list(logical_shape), dtype=torch.bool, device=packed.device)
+            # One byte of storage broadcast to the logical shape: a lazy result that is never read
+            # as bool costs no memory (the reference allocates a full bool tensor here,
+            # brute/tensor.py:316, 1 GiB at 2^30 bits). _ensure_bool_valid swaps real storage in.
+            bool_t = torch.empty((), dtype=torch.bool, device=packed.device).expand(list(logical_shape))
         else:
             assert bool_view.dtype == torch.bool, "bool_view must be torch.bool"
             bool_t = _plain(bool_view)
@@ -185,7 +188,13 @@ class Tensor(torch.Tensor):
                 unpacked = _ops.unpack_bool(src, [1]).reshape(())
             else:
                 unpacked = _ops.unpack_bool(src, shape)
-            base.copy_(unpacked)
+            if base.numel() > 1 and 0 in base.stride():
+                # the placeholder was a broadcast byte: adopt the real storage (on the tensor itself,
+                # not on the plain alias, which has its own sizes and strides)
+                torch.Tensor.set_(self, unpacked)
+                base = _plain(self)
+            else:
+                base.copy_(unpacked)
             ver = base._version
         d["_bool_dirty"] = False
         d["_packed_ver"] = ver          # the copy_ bumped the version: re-pin

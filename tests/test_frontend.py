@@ -297,3 +297,47 @@ def test_empty_and_zero_dim(brute):
         assert tuple(x.shape) == shape and int(x.popcount()) == 0
     s = brute.Tensor(torch.tensor(True, device=DEV), dtype=brute.bit1)
     assert s.dim() == 0 and int(s.popcount()) == 1 and bool(as_bool(~s)) is False
+
+
+# ---------------------------------------------------------------------------
+# packed serialisation, packed-domain transpose and leading-axis reductions
+# ---------------------------------------------------------------------------
+def test_save_load_packed_roundtrip(brute, tmp_path):
+    x = rnd((37, 1003), 11)
+    y = rnd((5,), 12)
+    state = {"w": b1(brute, x), "nested": [b1(brute, y), torch.arange(4)], "step": 7}
+    path = tmp_path / "state.pt"
+    brute.save_packed(state, path)
+    back = brute.load_packed(path, device=DEV)
+    assert back["step"] == 7 and torch.equal(cpu(back["nested"][1]), torch.arange(4))
+    assert back["w"].dtype == brute.bit1 and tuple(back["w"].shape) == (37, 1003)
+    assert str(back["w"].device).startswith(DEV)
+    assert torch.equal(as_bool(back["w"]), x.cpu()) and torch.equal(as_bool(back["nested"][0]), y.cpu())
+    # 64 bits per stored word instead of 8 per bool byte
+    bool_path = tmp_path / "bool.pt"
+    torch.save({"w": x.cpu()}, bool_path)
+    assert path.stat().st_size < bool_path.stat().st_size / 5
+    with pytest.raises(ValueError, match="reserved"):
+        brute.save_packed({"__bit1__": 1}, tmp_path / "bad.pt")
+
+
+def test_transpose_keeps_packed_domain(brute):
+    x = rnd((3, 70, 130), 13)
+    b = b1(brute, x)
+    for dims in ((-1, -2), (1, 2)):
+        bt = b.transpose(*dims)
+        assert tuple(bt.shape) == (3, 130, 70)
+        assert torch.equal(as_bool(bt), x.transpose(*dims).cpu())
+        want = torch.ops.brute.pack_bool(x.transpose(*dims).contiguous())
+        assert torch.equal(bt._packed_buf, want)
+    m = rnd((65, 129), 14)
+    assert torch.equal(as_bool(b1(brute, m).t() ^ b1(brute, m.t().contiguous())), torch.zeros(129, 65, dtype=torch.bool))
+
+
+def test_any_all_over_leading_dims(brute):
+    x = rnd((6, 9, 131), 15, p=0.8)
+    b = b1(brute, x)
+    for dim in (0, 1, -2, -3):
+        for keepdim in (False, True):
+            assert torch.equal(as_bool(b.any(dim=dim, keepdim=keepdim)), x.any(dim=dim, keepdim=keepdim).cpu())
+            assert torch.equal(as_bool(b.all(dim=dim, keepdim=keepdim)), x.all(dim=dim, keepdim=keepdim).cpu())
