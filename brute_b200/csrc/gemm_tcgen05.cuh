@@ -116,15 +116,20 @@ __device__ __forceinline__ bool tc_expander_step(ExpanderCtx& cx, uint32_t p_par
     const uint2 a  = lds64<S * TC_P_STAGE>(cx.p_ring + cx.a_lds_off[KB]);
     const uint2 b0 = lds64<S * TC_P_STAGE + TC_P_A>(src);
     const uint2 b1 = lds64<S * TC_P_STAGE + TC_P_A + 128 * TC_PK>(src);
+    cx.pc_a  += __popc(a.x) + __popc(a.y);
+    cx.pc_b0 += __popc(b0.x) + __popc(b0.y);
+    cx.pc_b1 += __popc(b1.x) + __popc(b1.y);
     if (KB == G + 2) {
+        // Release the packed slot only AFTER the loaded words have been used: the popcounts above
+        // cannot issue before the loads have returned, so the arrive that follows them cannot
+        // overtake a load that is still queued behind this kernel's heavy shared-memory store
+        // traffic. (Arriving straight after issuing the loads let the next TMA write reach the
+        // slot first in about one tile of 10^5.)
         // The packed slot is only ever refilled for a LATER stage, and a stage that short of
         // 4 k-blocks is the last one, so an arrival that a tail skips is never waited for.
         __syncwarp();
         if (cx.lane == 0) mbar_arrive(p_empty);
     }
-    cx.pc_a  += __popc(a.x) + __popc(a.y);
-    cx.pc_b0 += __popc(b0.x) + __popc(b0.y);
-    cx.pc_b1 += __popc(b1.x) + __popc(b1.y);
     if (!__all_sync(0xffffffffu, mbar_wait(e_empty, E_PARITY, cx.abort_flag, 4))) return false;
     tc_fence_after();
     tc_expand_a_half(a, cx.a_taddr + (uint32_t)(R * TC_A_COLS));

@@ -160,10 +160,12 @@ __device__ __forceinline__ bool tp_expander_step(PairExpanderCtx& cx) {
     cx.pf_mask ^= 1u << S;
     const uint4 a = lds128<S * TP_P_STAGE>(cx.a_src);
     const uint4 b = lds128<S * TP_P_STAGE + TP_P_A>(cx.b_src);
-    __syncwarp();
-    if (cx.lane == 0) mbar_arrive(p_empty);
     cx.pc_a += __popc(a.x) + __popc(a.y) + __popc(a.z) + __popc(a.w);
     cx.pc_b += __popc(b.x) + __popc(b.y) + __popc(b.z) + __popc(b.w);
+    // the slot is released after the first USE of the loaded words, never straight after the loads
+    // were issued: see the one-CTA kernel
+    __syncwarp();
+    if (cx.lane == 0) mbar_arrive(p_empty);
     if (!__all_sync(0xffffffffu, mbar_wait(e_empty, (cx.ee_mask >> R) & 1u, cx.abort_flag, 4))) return false;
     cx.ee_mask ^= 1u << R;
     tc_fence_after();

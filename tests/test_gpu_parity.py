@@ -341,6 +341,25 @@ def test_gemm_large_properties(ops):
     assert status_ok()
 
 
+@pytest.mark.parametrize("impl_name", ["tcgen05", "tcgen05_pair"])
+def test_gemm_repeatable_under_load(ops, impl_name):
+    # 8192 tiles per launch, 60 launches, every one compared with the CUDA-core kernel: the
+    # pipelines hand shared-memory slots between TMA, expander warps and the tensor core, and a
+    # slot released one instruction too early shows up as one wrong tile in about 10^5
+    from brute_b200 import _lib as L
+    K = 16384
+    g = gen(11)
+    a = torch.randint(-2 ** 63, 2 ** 63 - 1, (16384, K // 64), generator=g, dtype=torch.int64).to(DEV)
+    b = torch.randint(-2 ** 63, 2 ** 63 - 1, (16384, K // 64), generator=g, dtype=torch.int64).to(DEV)
+    ref = ops.xnor_popcount_matmul_impl(a, b, K, L.GEMM_POPC)
+    impl = {"tcgen05": L.GEMM_TCGEN05, "tcgen05_pair": L.GEMM_TCGEN05_PAIR}[impl_name]
+    for it in range(60):
+        c = ops.xnor_popcount_matmul_impl(a, b, K, impl)
+        assert torch.equal(c, ref), f"launch {it}"
+        del c
+    assert status_ok()
+
+
 @pytest.mark.parametrize("impl_name", ["popc", "mma_b1", "tcgen05", "tcgen05_pair"])
 @pytest.mark.parametrize("mode", [0, 1])
 def test_mlp_layer(ops, co, impl_name, mode):
