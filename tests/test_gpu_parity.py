@@ -507,6 +507,20 @@ def test_attention_kernels_agree(ops, co, monkeypatch, S, causal, scale):
     assert status_ok()
 
 
+def test_attention_repeatable_under_load(ops):
+    # no atomics anywhere in the kernel: 30 launches of BASELINE config 5 must agree bit for bit
+    # (a buffer handed over too early in the TMEM / shared-memory pipeline would show up here)
+    import brute_b200 as brute
+    g = gen(8)
+    q = brute.pack_sign(torch.randn((8, 32, 4096, 128), generator=g).to(DEV), ge0=True)
+    k = brute.pack_sign(torch.randn((8, 32, 4096, 128), generator=g).to(DEV), ge0=True)
+    v = torch.randn((8, 32, 4096, 128), generator=g).to(torch.bfloat16).to(DEV)
+    ref = brute.binary_attention(q, k, v, causal=True)
+    for it in range(30):
+        assert torch.equal(brute.binary_attention(q, k, v, causal=True), ref), f"launch {it}"
+    assert status_ok()
+
+
 def test_attention_first_row_is_v0(ops):
     # causal: query 0 sees only key 0, so the output row is exactly V[0]
     import brute_b200 as brute
