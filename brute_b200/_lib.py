@@ -14,6 +14,7 @@ LIB_PATH = _PKG / "libbrute_b200.so"
 
 # keep in step with include/brute_b200.h
 OK = 0
+ERR_INVALID_ARG, ERR_MISALIGNED, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_WORKSPACE, ERR_DEVICE_WAIT, ERR_DRIVER = -1, -2, -3, -4, -5, -6, -7
 SIGN_GT0, SIGN_GE0 = 0, 1
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 OP_AND, OP_OR, OP_XOR, OP_XNOR, OP_ANDNOT = 0, 1, 2, 3, 4
@@ -42,11 +43,14 @@ SIGNATURES = {
     "brute_b200_xnor_gemm": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _p],
     "brute_b200_xnor_gemm_scale_sign_pack": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32, _p],
     "brute_b200_signed_bundle": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p],
+    "brute_b200_signed_bundle_workspace_bytes": [_i64, _i64, _i64],
+    "brute_b200_signed_bundle_ws": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _i64, _p],
     "brute_b200_transpose_bits": [_p, _p, _i64, _i64, _i64, _p],
     "brute_b200_reduce_rows": [_i32, _p, _p, _i64, _i64, _i64, _p],
     "brute_b200_binary_attention_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _f32, _p],
 }
-_RESTYPES = {"brute_b200_strerror": C.c_char_p, "brute_b200_query_caps": C.c_uint32}
+_RESTYPES = {"brute_b200_strerror": C.c_char_p, "brute_b200_query_caps": C.c_uint32,
+             "brute_b200_signed_bundle_workspace_bytes": C.c_int64}
 
 _lib = None
 

@@ -8,7 +8,7 @@
 // so that 4 consecutive n of one byte column are one 32-bit load, and the 8 bits of that column
 // spread into 8 dp4a operands with a shift and a mask each (0.75 ALU op per MAC). Each thread
 // keeps 8 accumulators (its 8 bits of the word), not 64.
-#include "common.cuh"
+#include "signed_bundle_tcgen05.cuh"
 
 namespace bb {
 
@@ -78,4 +78,32 @@ extern "C" int brute_b200_signed_bundle(const int8_t* W, const uint64_t* V, uint
     const dim3 grid((unsigned)Dp, (unsigned)((M + SB_ROWS - 1) / SB_ROWS), (unsigned)B);
     k_signed_bundle<<<grid, SB_THREADS, 0, as_stream(stream)>>>(W, V, out, M, N, Dp, D);
     return launch_status();
+}
+
+namespace bb { int sb_status_bridge() { return tc5_device_status(); } }
+
+extern "C" int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out, int64_t batch, int64_t R, int64_t C, void* stream);
+
+extern "C" int64_t brute_b200_signed_bundle_workspace_bytes(int64_t B, int64_t N, int64_t D) {
+    if (B <= 0 || N <= 0 || D <= 0) return 0;
+    return B * D * ((N + 63) / 64) * 8;          // V transposed: [B, D, ceil(N/64)] words
+}
+
+extern "C" int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, uint64_t* out,
+                                           int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D,
+                                           void* workspace, int64_t workspace_bytes, void* stream) {
+    BB_REQUIRE(B >= 0 && M >= 0 && N >= 0 && Dp >= 0 && D >= 0 && D <= 64 * Dp, BRUTE_ERR_INVALID_ARG);
+    if (B * M * Dp == 0) return BRUTE_OK;
+    if (!st_accepts(W, B, M, N, D))              // shapes outside the TMA rules: the CUDA-core kernel, no workspace
+        return brute_b200_signed_bundle(W, V, out, B, M, N, Dp, D, stream);
+    BB_REQUIRE(out != nullptr && W != nullptr && V != nullptr, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(V) && aligned8(out), BRUTE_ERR_MISALIGNED);
+    BB_REQUIRE(workspace != nullptr && workspace_bytes >= brute_b200_signed_bundle_workspace_bytes(B, N, D),
+               BRUTE_ERR_WORKSPACE);
+    BB_REQUIRE(aligned8(workspace), BRUTE_ERR_MISALIGNED);
+    uint64_t* Vt = static_cast<uint64_t*>(workspace);
+    // V [B, N, Dp] holds D valid bits per row: transpose the [N x D] bit matrices into [D x N]
+    const int rc = brute_b200_transpose_bits(V, Vt, B, N, D, stream);
+    if (rc != BRUTE_OK) return rc;
+    return st_run(W, Vt, out, B, M, N, Dp, D, as_stream(stream));
 }

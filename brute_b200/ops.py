@@ -197,9 +197,13 @@ def signed_bundle(W: torch.Tensor, V: torch.Tensor, D: int) -> torch.Tensor:
     out = torch.empty((B, M, Dp), dtype=torch.int64, device=V.device)
     if out.numel():
         with torch.cuda.device(V.device):
-            L.check(_lib.brute_b200_signed_bundle(Wc.data_ptr() if Wc.numel() else None,
-                                                  Vc.data_ptr() if Vc.numel() else None, out.data_ptr(),
-                                                  B, M, N, Dp, int(D), _stream(V)), "signed_bundle")
+            # the library allocates nothing: the scratch for the bit-transposed V comes from here
+            ws_bytes = int(_lib.brute_b200_signed_bundle_workspace_bytes(B, N, int(D)))
+            ws = torch.empty(max(ws_bytes, 8) // 8, dtype=torch.int64, device=V.device)
+            L.check(_lib.brute_b200_signed_bundle_ws(Wc.data_ptr() if Wc.numel() else None,
+                                                     Vc.data_ptr() if Vc.numel() else None, out.data_ptr(),
+                                                     B, M, N, Dp, int(D), ws.data_ptr(), ws_bytes, _stream(V)),
+                    "signed_bundle")
     return out
 
 

@@ -204,6 +204,17 @@ int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B,
 int brute_b200_signed_bundle(const int8_t* W, const uint64_t* V, uint64_t* out,
                              int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D, void* stream);
 
+/* The same result on the tensor cores: V is bit-transposed into `workspace` and the vote becomes an
+ * int8 GEMM that streams W once (HBM bound). `workspace` must hold
+ * brute_b200_signed_bundle_workspace_bytes(B, N, D) bytes of device memory, 8-byte aligned; the
+ * library allocates nothing, so the caller provides it (BRUTE_ERR_WORKSPACE if it is missing or too
+ * small). Shapes the tensor path does not take (W not 16-byte aligned, N not a multiple of 16, N < 128,
+ * M < 64) run the kernel of brute_b200_signed_bundle and ignore the workspace. Same reference lines. */
+int64_t brute_b200_signed_bundle_workspace_bytes(int64_t B, int64_t N, int64_t D);
+int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, uint64_t* out,
+                                int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D,
+                                void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ---- binary attention -------------------------------------------------- */
 /* Qp, Kp_ [B, H, S, D/64] words (sign-binarised Q and K), V and O bf16
  * [B, H, S, D]; score(i,j) = (D - 2*popcount(q_i ^ k_j)) * scale, optional

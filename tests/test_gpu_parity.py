@@ -440,11 +440,15 @@ def test_reduce_rows_packed(ops, co, shape, dim):
 # signed_bundle
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("B,M,N,D", [(1, 1, 1, 1), (2, 5, 7, 70), (1, 33, 130, 128), (3, 64, 256, 64),
-                                     (2, 100, 1000, 200), (1, 32, 128, 4096)])
+                                     (2, 100, 1000, 200), (1, 32, 128, 4096),
+                                     # tensor-core path (N % 16 == 0, N >= 128, M >= 64): ragged M, N, D
+                                     (2, 128, 256, 128), (1, 200, 1024, 70), (3, 64, 128, 200), (1, 1000, 2048, 128),
+                                     (2, 130, 144, 64), (1, 257, 4096 + 16, 129), (4, 64, 128, 1)])
 def test_signed_bundle(ops, co, B, M, N, D):
     import brute_b200 as brute
     g = gen(B + M + N + D)
-    W = torch.randint(-3, 4, (B, M, N), generator=g, dtype=torch.int64).to(torch.int8)
+    lo, hi = (-3, 4) if (B + M) % 2 else (-128, 128)        # small votes (many ties) or the full int8 range
+    W = torch.randint(lo, hi, (B, M, N), generator=g, dtype=torch.int64).to(torch.int8)
     v = torch.rand((B, N, D), generator=g) < 0.5
     vp = ops.pack_bool(v.to(DEV))
     got = ops.signed_bundle(W.to(DEV), vp, D)
@@ -455,6 +459,33 @@ def test_signed_bundle(ops, co, B, M, N, D):
     assert out.dtype == brute.bit1 and torch.equal(out.bool().as_subclass(torch.Tensor).cpu(), acc >= 0)
     with pytest.raises(RuntimeError, match="must be int8"):
         ops.signed_bundle(W.to(DEV).int(), vp, D)
+
+
+def test_signed_bundle_workspace_contract(ops, co):
+    # the C entry point allocates nothing: without enough scratch it refuses, and says so
+    from brute_b200 import _lib as L
+    lib = L.load()
+    B, M, N, D = 2, 128, 256, 128
+    g = gen(9)
+    W = torch.randint(-5, 6, (B, M, N), generator=g, dtype=torch.int64).to(torch.int8).to(DEV)
+    vp = ops.pack_bool((torch.rand((B, N, D), generator=g) < 0.5).to(DEV))
+    out = torch.zeros((B, M, 2), dtype=torch.int64, device=DEV)
+    need = int(lib.brute_b200_signed_bundle_workspace_bytes(B, N, D))
+    assert need == B * D * (N // 64) * 8
+    ws = torch.empty(need // 8, dtype=torch.int64, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    args = (W.data_ptr(), vp.data_ptr(), out.data_ptr(), B, M, N, 2, D)
+    assert lib.brute_b200_signed_bundle_ws(*args, None, 0, st) == L.ERR_WORKSPACE
+    assert lib.brute_b200_signed_bundle_ws(*args, ws.data_ptr(), need - 8, st) == L.ERR_WORKSPACE
+    assert "scratch" in L.strerror(L.ERR_WORKSPACE)
+    assert lib.brute_b200_signed_bundle_ws(*args, ws.data_ptr(), need, st) == 0
+    assert np.array_equal(u64(out), co.signed_bundle(W.cpu().numpy(), u64(vp), D))
+    # a shape outside the tensor path needs no workspace at all
+    W2 = W[:, :, :100].contiguous()
+    v2 = vp[:, :100].contiguous()
+    assert lib.brute_b200_signed_bundle_ws(W2.data_ptr(), v2.data_ptr(), out.data_ptr(), B, M, 100, 2, D, None, 0, st) == 0
+    assert np.array_equal(u64(out), co.signed_bundle(W2.cpu().numpy(), u64(v2), D))
+    assert status_ok()
 
 
 # ---------------------------------------------------------------------------
