@@ -45,12 +45,15 @@ SIGNATURES = {
     "brute_b200_signed_bundle": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p],
     "brute_b200_signed_bundle_workspace_bytes": [_i64, _i64, _i64],
     "brute_b200_signed_bundle_ws": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _i64, _p],
+    "brute_b200_signed_bundle_static_max_bytes": [],
+    "brute_b200_signed_bundle_static": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p],
     "brute_b200_transpose_bits": [_p, _p, _i64, _i64, _i64, _p],
     "brute_b200_reduce_rows": [_i32, _p, _p, _i64, _i64, _i64, _p],
     "brute_b200_binary_attention_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _f32, _p],
 }
 _RESTYPES = {"brute_b200_strerror": C.c_char_p, "brute_b200_query_caps": C.c_uint32,
-             "brute_b200_signed_bundle_workspace_bytes": C.c_int64}
+             "brute_b200_signed_bundle_workspace_bytes": C.c_int64,
+             "brute_b200_signed_bundle_static_max_bytes": C.c_int64}
 
 _lib = None
 

@@ -107,3 +107,37 @@ extern "C" int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, u
     if (rc != BRUTE_OK) return rc;
     return st_run(W, Vt, out, B, M, N, Dp, D, as_stream(stream));
 }
+
+// ---------------------------------------------------------------------------
+// The same call for callers that cannot hand over a workspace: the scratch for the bit-transposed V
+// is a fixed array in device memory that belongs to the library image.
+namespace bb {
+constexpr int64_t SB_STATIC_SCRATCH_BYTES = 1 << 20;            // 1 MiB: B * D * ceil(N/64) * 8 must fit
+static __device__ __align__(256) uint64_t g_sb_static_scratch[SB_STATIC_SCRATCH_BYTES / 8];
+constexpr int SB_MAX_DEVICES = 64;
+static uint64_t* g_sb_static_ptr[SB_MAX_DEVICES];               // device address of the array, per device
+}  // namespace bb
+
+extern "C" int64_t brute_b200_signed_bundle_static_max_bytes(void) { return SB_STATIC_SCRATCH_BYTES; }
+
+extern "C" int brute_b200_signed_bundle_static(const int8_t* W, const uint64_t* V, uint64_t* out,
+                                               int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D,
+                                               void* stream) {
+    BB_REQUIRE(B >= 0 && M >= 0 && N >= 0 && Dp >= 0 && D >= 0 && D <= 64 * Dp, BRUTE_ERR_INVALID_ARG);
+    if (B * M * Dp == 0) return BRUTE_OK;
+    if (!st_accepts(W, B, M, N, D))              // the CUDA-core kernel uses no scratch, whatever the size
+        return brute_b200_signed_bundle(W, V, out, B, M, N, Dp, D, stream);
+    const int64_t need = brute_b200_signed_bundle_workspace_bytes(B, N, D);
+    BB_REQUIRE(need <= SB_STATIC_SCRATCH_BYTES, BRUTE_ERR_WORKSPACE);
+    int dev = -1;
+    BB_REQUIRE(cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < SB_MAX_DEVICES, BRUTE_ERR_LAUNCH);
+    if (g_sb_static_ptr[dev] == nullptr) {
+        // once per device, with that device current: where this device keeps the array
+        void* p = nullptr;
+        BB_REQUIRE(cudaGetSymbolAddress(&p, g_sb_static_scratch) == cudaSuccess && p != nullptr, BRUTE_ERR_LAUNCH);
+        g_sb_static_ptr[dev] = static_cast<uint64_t*>(p);
+    }
+    // Nothing in the scratch has to start at zero: the transpose writes every word that the GEMM
+    // reads (all ceil(N/64) words of all D rows of all B batches, pad bits included).
+    return brute_b200_signed_bundle_ws(W, V, out, B, M, N, Dp, D, g_sb_static_ptr[dev], SB_STATIC_SCRATCH_BYTES, stream);
+}

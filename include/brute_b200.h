@@ -159,6 +159,23 @@ int brute_b200_row_any(const uint64_t* a, uint8_t* out, int64_t rows,
 int brute_b200_row_all(const uint64_t* a, uint8_t* out, int64_t rows,
                        int64_t words_per_row, int64_t last_dim_bits, void* stream);
 
+/* signed_bundle without a workspace argument and without any allocation: the scratch for the
+ * transposed V is a fixed 1 MiB array inside the library's device image (one per device), found
+ * once per device by a symbol lookup on the first call made with that device current. There is no
+ * counterpart in the reference; it exists for callers that may not allocate (or pass) device memory.
+ *  - B * D * ceil(N/64) * 8 must not exceed brute_b200_signed_bundle_static_max_bytes() (1 MiB),
+ *    otherwise BRUTE_ERR_WORKSPACE and nothing is launched;
+ *  - the array is shared by every call on a device: two calls whose kernels can overlap (different
+ *    streams, or host threads racing on one stream) overwrite each other's scratch. Keep calls to
+ *    this entry point on one stream per device, or order them with events;
+ *  - the first call on a device performs the symbol lookup, a runtime query that does not belong
+ *    inside a stream capture: make one call per device before capturing a CUDA graph that contains it.
+ * Result and argument rules are those of brute_b200_signed_bundle_ws. */
+int64_t brute_b200_signed_bundle_static_max_bytes(void);
+int brute_b200_signed_bundle_static(const int8_t* W, const uint64_t* V, uint64_t* out,
+                                    int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D,
+                                    void* stream);
+
 /* ---- layout on packed words ------------------------------------------- */
 /* Bit-matrix transpose: in [batch, R, ceil(C/64)] -> out [batch, C, ceil(R/64)],
  * out bit (c, r) = in bit (r, c); pad bits of `out` are 0. in and out must not overlap.
