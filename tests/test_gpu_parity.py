@@ -453,6 +453,8 @@ def test_signed_bundle(ops, co, B, M, N, D):
     vp = ops.pack_bool(v.to(DEV))
     got = ops.signed_bundle(W.to(DEV), vp, D)
     assert np.array_equal(u64(got), co.signed_bundle(W.numpy(), u64(vp), D))
+    for _ in range(5):          # same answer launch after launch (the tensor path pipelines TMA, expanders and MMAs)
+        assert torch.equal(ops.signed_bundle(W.to(DEV), vp, D), got)
     # through the front-end helper, against the +-1 integer contraction
     out = brute.fast.signed_bundle(W.to(DEV), brute.Tensor(v.to(DEV), dtype=brute.bit1))
     acc = torch.einsum("bmn,bnd->bmd", W.float(), v.float() * 2 - 1)
