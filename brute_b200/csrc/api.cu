@@ -1,7 +1,7 @@
 // Library-level entry points: error strings, capabilities, device status.
 #include "common.cuh"
 
-namespace bb { int tc5_status_bridge(); int at_status_bridge(); int sb_status_bridge(); }
+namespace bb { int tc5_status_bridge(); int at_status_bridge(); int sb_status_bridge(); int ly_status_bridge(); }
 
 extern "C" const char* brute_b200_strerror(int code) {
     switch (code) {
@@ -24,6 +24,7 @@ extern "C" uint32_t brute_b200_query_caps(void) {
 
 extern "C" int brute_b200_device_status(void) {
     // every translation unit with bounded in-kernel waits keeps its own status word
-    const int g = bb::tc5_status_bridge(), a = bb::at_status_bridge(), s = bb::sb_status_bridge();
-    return g != BRUTE_OK ? g : (a != BRUTE_OK ? a : s);
+    const int codes[4] = {bb::tc5_status_bridge(), bb::at_status_bridge(), bb::sb_status_bridge(), bb::ly_status_bridge()};
+    for (int c : codes) if (c != BRUTE_OK) return c;
+    return BRUTE_OK;
 }

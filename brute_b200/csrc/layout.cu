@@ -12,7 +12,7 @@
 // reduce_rows: in [outer, R, inner] words -> out [outer, inner] words, OR or AND over R. One
 // thread per inner word (coalesced), R cut into chunks across blockIdx.y, partial results merged
 // with 64-bit atomics into an output that the launcher presets (0 for OR, ~0 for AND).
-#include "common.cuh"
+#include "tcgen05_common.cuh"
 
 namespace bb {
 
@@ -114,6 +114,93 @@ k_transpose_bits(const uint64_t* __restrict__ in, uint64_t* __restrict__ out,
     }
 }
 
+// The same tile through TMA: strided 64-byte rows are what the bulk tensor copies are for. With
+// plain loads a warp touches 32 different 128-byte lines per instruction and the load/store unit,
+// not HBM, sets the pace (about 2 TB/s). Here one thread issues two [256 rows x 64 bytes] box loads,
+// the warps read their rows from SWIZZLE_64B shared memory without bank conflicts, and the transposed
+// tile leaves as two box stores; rows and words past the edges are zero filled on the way in and
+// clipped on the way out, so there is no edge code. Needs 16-byte row pitches on both sides.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 :: "l"(tm), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+constexpr int TB_TMA_SMEM = 2 * TB_TILE * 64 + 64 + 1024;
+
+__global__ void __launch_bounds__(TB_THREADS)
+k_transpose_bits_tma(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmOut,
+                     int64_t gx, int64_t gy, int64_t sgx) {
+    extern __shared__ uint8_t tb_smem_raw[];
+    const uint32_t raw = (uint32_t)__cvta_generic_to_shared(tb_smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t in_s = base, out_s = base + TB_TILE * 64, bar = out_s + TB_TILE * 64;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tb_smem_raw + (base - raw) + 2 * TB_TILE * 64 + 8);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t b = blockIdx.y;
+    const int64_t grp = (int64_t)blockIdx.x >> 6;
+    const int in_grp = (int)(blockIdx.x & 63);
+    const int64_t tx = (grp % sgx) * 8 + (in_grp & 7), ty = (grp / sgx) * 8 + (in_grp >> 3);
+    if (tx >= gx || ty >= gy) return;
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async_smem();
+        mbar_expect_tx(bar, TB_TILE * 64);
+        tma_load_3d(in_s, &tmIn, (int32_t)(tx * TB_BLOCKS), (int32_t)(ty * TB_TILE), (int32_t)b, bar);
+        tma_load_3d(in_s + 256 * 64, &tmIn, (int32_t)(tx * TB_BLOCKS), (int32_t)(ty * TB_TILE + 256), (int32_t)b, bar);
+    }
+    __syncthreads();
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(bar, 0, abort_flag, 31));
+    // shared-memory row = 64 bytes = 4 chunks of 16; chunk c of row r sits at c ^ ((r >> 1) & 3)
+    uint64_t lo[TB_BLOCKS], hi[TB_BLOCKS];
+    {
+        const int ra = 64 * warp + lane, rb = ra + 32;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint4 va, vb;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(va.x), "=r"(va.y), "=r"(va.z), "=r"(va.w)
+                         : "r"(in_s + (uint32_t)(ra * 64 + ((c ^ ((ra >> 1) & 3)) << 4))) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vb.x), "=r"(vb.y), "=r"(vb.z), "=r"(vb.w)
+                         : "r"(in_s + (uint32_t)(rb * 64 + ((c ^ ((rb >> 1) & 3)) << 4))) : "memory");
+            lo[2 * c] = (uint64_t)va.x | ((uint64_t)va.y << 32); lo[2 * c + 1] = (uint64_t)va.z | ((uint64_t)va.w << 32);
+            hi[2 * c] = (uint64_t)vb.x | ((uint64_t)vb.y << 32); hi[2 * c + 1] = (uint64_t)vb.z | ((uint64_t)vb.w << 32);
+        }
+    }
+#pragma unroll
+    for (int cb = 0; cb < TB_BLOCKS; ++cb) {
+        transpose64x64(lo[cb], hi[cb], lane);
+        // output tile row = input bit column; word `warp` of that row
+        const int oa = 64 * cb + lane, ob = oa + 32;
+        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" :: "r"(out_s + (uint32_t)(oa * 64 + (((warp >> 1) ^ ((oa >> 1) & 3)) << 4) + (warp & 1) * 8)),
+                     "r"((uint32_t)lo[cb]), "r"((uint32_t)(lo[cb] >> 32)) : "memory");
+        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" :: "r"(out_s + (uint32_t)(ob * 64 + (((warp >> 1) ^ ((ob >> 1) & 3)) << 4) + (warp & 1) * 8)),
+                     "r"((uint32_t)hi[cb]), "r"((uint32_t)(hi[cb] >> 32)) : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0 && ok) {
+        tma_store_3d(&tmOut, out_s, (int32_t)(ty * TB_BLOCKS), (int32_t)(tx * TB_TILE), (int32_t)b);
+        tma_store_3d(&tmOut, out_s + 256 * 64, (int32_t)(ty * TB_BLOCKS), (int32_t)(tx * TB_TILE + 256), (int32_t)b);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // the tile must outlive the stores' reads
+    }
+}
+
+// packed words [batch, rows, wpr] as a 3-D tensor of 8-byte elements, box = [8 words, 256 rows, 1], SWIZZLE_64B
+static bool tb_make_map(CUtensorMap* tm, const uint64_t* p, int64_t batch, int64_t rows, int64_t wpr) {
+    PFN_tmapEncodeTiled enc = tc5_encode_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)wpr, (cuuint64_t)rows, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)wpr * 8u, (cuuint64_t)(rows * wpr) * 8u};
+    const cuuint32_t box[3] = {(cuuint32_t)TB_BLOCKS, 256u, 1u};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<uint64_t*>(p), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <bool IS_OR>
 __global__ void __launch_bounds__(256)
 k_reduce_rows(const uint64_t* __restrict__ in, unsigned long long* __restrict__ out,
@@ -137,6 +224,8 @@ k_reduce_rows(const uint64_t* __restrict__ in, unsigned long long* __restrict__ 
 
 }  // namespace bb
 
+namespace bb { int ly_status_bridge() { return tc5_device_status(); } }
+
 using namespace bb;
 
 extern "C" int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out,
@@ -150,8 +239,23 @@ extern "C" int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out,
     const int64_t gx = (wpr_in + TB_BLOCKS - 1) / TB_BLOCKS, gy = (R + TB_TILE - 1) / TB_TILE;
     const int64_t sgx = (gx + 7) / 8, sgy = (gy + 7) / 8;
     BB_REQUIRE(sgx * sgy * 64 <= 0x7fffffffll && batch <= 65535, BRUTE_ERR_UNSUPPORTED);
-    k_transpose_bits<<<dim3((unsigned)(sgx * sgy * 64), (unsigned)batch), TB_THREADS, 0, as_stream(stream)>>>(
-        in, out, R, C, wpr_in, wpr_out, gx, gy, sgx);
+    const dim3 grid((unsigned)(sgx * sgy * 64), (unsigned)batch);
+    // TMA wants 16-byte aligned bases and row (and batch) pitches, and 32-bit coordinates
+    if ((wpr_in & 1) == 0 && (wpr_out & 1) == 0 && aligned16(in) && aligned16(out) &&
+        R < (1ll << 31) - TB_TILE && C < (1ll << 31) - TB_TILE) {
+        CUtensorMap tmIn, tmOut;
+        if (tb_make_map(&tmIn, in, batch, R, wpr_in) && tb_make_map(&tmOut, out, batch, C, wpr_out)) {
+            static bool attr_set = false;
+            if (!attr_set) {
+                if (cudaFuncSetAttribute(k_transpose_bits_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, TB_TMA_SMEM) != cudaSuccess)
+                    return BRUTE_ERR_LAUNCH;
+                attr_set = true;
+            }
+            k_transpose_bits_tma<<<grid, TB_THREADS, TB_TMA_SMEM, as_stream(stream)>>>(tmIn, tmOut, gx, gy, sgx);
+            return launch_status();
+        }
+    }
+    k_transpose_bits<<<grid, TB_THREADS, 0, as_stream(stream)>>>(in, out, R, C, wpr_in, wpr_out, gx, gy, sgx);
     return launch_status();
 }
 

@@ -402,7 +402,9 @@ def test_mlp_config4_chain(ops, co):
 # layout: bit-matrix transpose, any/all over a non-packed axis
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("shape", [(1, 1), (3, 5), (64, 64), (65, 63), (130, 257), (256, 256), (257, 1000), (1000, 257),
-                                   (2, 3, 70, 129), (5, 300, 64), (4096, 4097), (1, 100000), (100000, 1)])
+                                   (2, 3, 70, 129), (5, 300, 64), (4096, 4097), (1, 100000), (100000, 1),
+                                   # even word counts on both sides: the TMA kernel (ragged rows, ragged bits, batches)
+                                   (640, 384), (1000, 8192), (2, 3, 128, 256), (1408, 896), (5107, 6395), (65, 100)])
 def test_transpose_packed(ops, co, shape):
     import brute_b200 as brute
     x = torch.rand(shape, generator=gen(sum(shape))) < 0.5
