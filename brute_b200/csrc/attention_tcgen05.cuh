@@ -137,7 +137,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             int32_t issued = 0;
             for (int32_t j = 0; j < ntiles && ok; ++j) {
                 const int s = j % AX_NV;
-                ok = mbar_wait(v_empty(s), ((j / AX_NV) & 1) ^ 1, abort_flag, 11);
+                ok = mbar_wait_relaxed(v_empty(s), ((j / AX_NV) & 1) ^ 1, abort_flag, 11);
                 if (!ok) break;
                 mbar_expect_tx(v_full(s), AX_V_STAGE);
                 tma_load_3d(v_ring + s * AX_V_STAGE, &tmV, 0, j * AX_BN, (int32_t)bh, v_full(s));
@@ -217,7 +217,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             const int b = j & 1;
             uint32_t nxt[4] = {0u, 0u, 0u, 0u};
             if (j + 1 < ntiles) load_tile(j + 1, nxt);
-            ok = __all_sync(0xffffffffu, mbar_wait(ke_empty(b), ((j >> 1) & 1) ^ 1, abort_flag, 17));
+            ok = __all_sync(0xffffffffu, mbar_wait_relaxed(ke_empty(b), ((j >> 1) & 1) ^ 1, abort_flag, 17));
             if (!ok) break;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {

@@ -56,6 +56,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
 }
+// The same bounded wait for roles that are far ahead of their consumer (producers waiting for a
+// free slot): back off between polls so that the polling warp leaves the issue slots to the warps
+// on the critical path.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = tc_globaltimer();
+    uint32_t spins = 0;
+    while (true) {
+        __nanosleep(128);
+        if (mbar_try(bar, parity)) return true;
+        if (((++spins) & 0x3Fu) == 0) {
+            if (*abort_flag) return false;
+            if (tc_globaltimer() - t0 > TC_WAIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(&g_tc_status, 0, code);
+                return false;
+            }
+        }
+    }
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
