@@ -178,6 +178,24 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
+def pin_to_gpu_numa_node(index: int) -> None:
+    """Run this rank on the CPUs next to its GPU (a setting of this process only), so that the pinned
+    host buffers of the end-to-end leg are allocated on the GPU's own NUMA node and the ranks do not
+    all pull their results through one socket."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (int(w) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception:
+        pass
+
+
 def time_steps(fn, steps, warmup, flush, stream_sync):
     """Per-step CUDA events on the launching stream, L2 flushed between steps
     (outside the timed spans). Returns the list of step times in ms."""
@@ -208,6 +226,7 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        pin_to_gpu_numa_node(local_rank)
         dist.init_process_group("nccl", device_id=dev)
 
     import brute_b200  # noqa: F401  (fails loudly if the CUDA library is missing)
