@@ -447,6 +447,11 @@ def secondary_workloads(dev, peaks, flush, sync):
     p2 = p.view(32768, 512)
     bw("transpose_bits_32768x32768", lambda: ops.transpose_packed(p2, 32768, 32768), 2 * n // 8)
     bw("any_dim0_4096x2^18", lambda: ops.reduce_rows_packed(p.view(4096, 4096), 0, True), n // 8 + (1 << 18) // 8)
+    p3 = p.view(1024, -1)                  # 1024 rows of 2^20 bits; the -5 makes every row ragged
+    nrow = (1 << 20) - 5
+    bw("flip_last_axis_1024x(2^20-5)", lambda: ops.flip_packed(p3, nrow), 2 * n // 8)
+    bw("roll_last_axis_1024x(2^20-5)", lambda: ops.roll_packed(p3, nrow, 12345), 2 * n // 8)
+    del p3
     del p, q, p2
     xb = torch.rand((4096, 4097), generator=g, device=dev) < 0.3
     bw("pack_bool_4096x4097", lambda: ops.pack_bool(xb), 4096 * 4097 + 4096 * 65 * 8)

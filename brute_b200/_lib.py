@@ -49,6 +49,9 @@ SIGNATURES = {
     "brute_b200_signed_bundle_static": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p],
     "brute_b200_transpose_bits": [_p, _p, _i64, _i64, _i64, _p],
     "brute_b200_reduce_rows": [_i32, _p, _p, _i64, _i64, _i64, _p],
+    "brute_b200_flip_bits": [_p, _p, _i64, _i64, _p],
+    "brute_b200_roll_bits": [_p, _p, _i64, _i64, _i64, _p],
+    "brute_b200_gather_bits": [_p, _p, _p, _i64, _i64, _i64, _p],
     "brute_b200_binary_attention_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _f32, _p],
 }
 _RESTYPES = {"brute_b200_strerror": C.c_char_p, "brute_b200_query_caps": C.c_uint32,

@@ -222,6 +222,81 @@ k_reduce_rows(const uint64_t* __restrict__ in, unsigned long long* __restrict__ 
     else       { if (acc != ~0ull) atomicAnd(out + o * inner + i, acc); }
 }
 
+// ---------------------------------------------------------------------------
+// Moves along the packed axis, in the packed domain.
+//
+// flip and roll: every output word is a 64-bit WINDOW of the input row at some bit offset (for
+// flip the window is then bit-reversed), so one thread makes one output word from at most two
+// (roll across the end of the row: three) input words. HBM bound, 2 * n / 8 bytes.
+// gather (index_select on the last axis): the source bit of every output bit comes from an index
+// vector, so a warp builds 1024 output bits with 32 ballots: lane l looks up the bit for position
+// 32 t + l in round t and keeps the ballot of round t == l.
+
+// bits [p, p + 64) of a row of n bits stored in `row` (wpr words); positions outside [0, n) read as 0
+__device__ __forceinline__ uint64_t row_window(const uint64_t* __restrict__ row, int64_t wpr, int64_t n, int64_t p) {
+    if (p >= n || p <= -64) return 0ull;
+    const int64_t w = p >> 6;                  // floor division: p may be negative
+    const int sh = (int)(p & 63);
+    const uint64_t lo = (w >= 0 && w < wpr) ? __ldg(row + w) : 0ull;
+    uint64_t v = lo >> sh;
+    if (sh != 0) {
+        const uint64_t hi = (w + 1 >= 0 && w + 1 < wpr) ? __ldg(row + w + 1) : 0ull;
+        v |= hi << (64 - sh);
+    }
+    return v;                                  // pad bits of the input are 0, so nothing past n leaks in
+}
+
+template <bool FLIP>
+__global__ void __launch_bounds__(256)
+k_flip_roll_bits(const uint64_t* __restrict__ in, uint64_t* __restrict__ out,
+                 int64_t rows, int64_t n, int64_t wpr, int64_t shift /* roll: 0 <= shift < n */) {
+    const int64_t total = rows * wpr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / wpr, w = i - r * wpr;
+        const uint64_t* row = in + r * wpr;
+        uint64_t v;
+        if (FLIP) {
+            // out bit j = in bit n - 1 - j: output bits [64 w, 64 w + 64) are the window that ENDS at n - 64 w, reversed
+            v = __brevll(row_window(row, wpr, n, n - 64 * (w + 1)));
+        } else {
+            // out bit j = in bit (j - shift) mod n
+            int64_t p = 64 * w - shift;
+            if (p < 0) p += n;                                       // -n < 64 w - shift, since shift < n
+            v = row_window(row, wpr, n, p);
+            if (p + 64 > n) v |= row_window(row, wpr, n, p - n);     // the window runs over the end: wrap to bit 0
+        }
+        const int64_t valid = n - 64 * w;
+        if (valid < 64) v &= (1ull << valid) - 1ull;
+        out[i] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_gather_bits(const uint64_t* __restrict__ in, const int64_t* __restrict__ idx, uint32_t* __restrict__ out32,
+              int64_t rows, int64_t n_in, int64_t n_out, int64_t wpr_in, int64_t wpr_out, int64_t chunks_per_row) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t task = warp; task < rows * chunks_per_row; task += nwarps) {
+        const int64_t r = task / chunks_per_row, c = task - r * chunks_per_row;
+        const uint64_t* row = in + r * wpr_in;
+        uint32_t mine = 0;
+#pragma unroll 4
+        for (int t = 0; t < 32; ++t) {
+            const int64_t j = c * 1024 + t * 32 + lane;
+            uint32_t bit = 0;
+            if (j < n_out) {
+                const int64_t s = __ldg(idx + j);
+                if (s >= 0 && s < n_in) bit = (uint32_t)(__ldg(row + (s >> 6)) >> (s & 63)) & 1u;   // out of range reads as 0
+            }
+            const uint32_t word = __ballot_sync(0xffffffffu, bit);
+            if (lane == t) mine = word;
+        }
+        const int64_t w32 = c * 32 + lane;                     // 32-bit word index inside the output row
+        if (w32 < 2 * wpr_out) out32[r * 2 * wpr_out + w32] = mine;
+    }
+}
+
 }  // namespace bb
 
 namespace bb { int ly_status_bridge() { return tc5_device_status(); } }
@@ -285,5 +360,40 @@ extern "C" int brute_b200_reduce_rows(int op, const uint64_t* in, uint64_t* out,
         k_reduce_rows<true><<<grid, 256, 0, st>>>(in, reinterpret_cast<unsigned long long*>(out), R, inner, rows_per_chunk);
     else
         k_reduce_rows<false><<<grid, 256, 0, st>>>(in, reinterpret_cast<unsigned long long*>(out), R, inner, rows_per_chunk);
+    return launch_status();
+}
+
+extern "C" int brute_b200_flip_bits(const uint64_t* in, uint64_t* out, int64_t rows, int64_t n, void* stream) {
+    BB_REQUIRE(rows >= 0 && n >= 0, BRUTE_ERR_INVALID_ARG);
+    if (rows == 0 || n == 0) return BRUTE_OK;
+    BB_REQUIRE(in != nullptr && out != nullptr && in != out, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(in) && aligned8(out), BRUTE_ERR_MISALIGNED);
+    const int64_t wpr = (n + 63) / 64;
+    k_flip_roll_bits<true><<<stream_grid(rows * wpr, 256, 8), 256, 0, as_stream(stream)>>>(in, out, rows, n, wpr, 0);
+    return launch_status();
+}
+
+extern "C" int brute_b200_roll_bits(const uint64_t* in, uint64_t* out, int64_t rows, int64_t n, int64_t shift, void* stream) {
+    BB_REQUIRE(rows >= 0 && n >= 0, BRUTE_ERR_INVALID_ARG);
+    if (rows == 0 || n == 0) return BRUTE_OK;
+    BB_REQUIRE(in != nullptr && out != nullptr && in != out, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(in) && aligned8(out), BRUTE_ERR_MISALIGNED);
+    const int64_t wpr = (n + 63) / 64;
+    int64_t s = shift % n;
+    if (s < 0) s += n;
+    k_flip_roll_bits<false><<<stream_grid(rows * wpr, 256, 8), 256, 0, as_stream(stream)>>>(in, out, rows, n, wpr, s);
+    return launch_status();
+}
+
+extern "C" int brute_b200_gather_bits(const uint64_t* in, const int64_t* idx, uint64_t* out,
+                                      int64_t rows, int64_t n_in, int64_t n_out, void* stream) {
+    BB_REQUIRE(rows >= 0 && n_in >= 0 && n_out >= 0, BRUTE_ERR_INVALID_ARG);
+    if (rows == 0 || n_out == 0) return BRUTE_OK;
+    BB_REQUIRE(out != nullptr && idx != nullptr && (n_in == 0 || in != nullptr) && in != out, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(in) && aligned8(out) && aligned8(idx), BRUTE_ERR_MISALIGNED);
+    const int64_t wpr_in = (n_in + 63) / 64, wpr_out = (n_out + 63) / 64;
+    const int64_t chunks = (n_out + 1023) / 1024;
+    k_gather_bits<<<stream_grid(rows * chunks, 8, 8), 256, 0, as_stream(stream)>>>(
+        in, idx, reinterpret_cast<uint32_t*>(out), rows, n_in, n_out, wpr_in, wpr_out, chunks);
     return launch_status();
 }

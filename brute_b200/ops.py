@@ -46,6 +46,9 @@ _DEF.define("xnor_matmul_scale_sign_pack(Tensor A, Tensor B, Tensor scale, int K
 _DEF.define("binary_attention(Tensor Qp, Tensor Kp, Tensor V, bool causal, float scale) -> Tensor")
 _DEF.define("transpose_packed(Tensor packed, int rows, int cols) -> Tensor")
 _DEF.define("reduce_rows_packed(Tensor packed, int dim, bool use_or) -> Tensor")
+_DEF.define("flip_packed(Tensor packed, int n) -> Tensor")
+_DEF.define("roll_packed(Tensor packed, int n, int shift) -> Tensor")
+_DEF.define("gather_packed(Tensor packed, Tensor idx, int n_in) -> Tensor")
 
 _PACK_WIDTH = 64
 _SIGN_DTYPES = {torch.float32: L.DT_F32, torch.bfloat16: L.DT_BF16, torch.float16: L.DT_F16}
@@ -363,6 +366,51 @@ def reduce_rows_packed(packed: torch.Tensor, dim: int, use_or: bool) -> torch.Te
     return out
 
 
+def _packed_rows(packed: torch.Tensor, n: int, what: str):
+    _check(packed.dim() >= 1 and packed.dtype == torch.int64, f"{what}: input must be int64 with >= 1 dim")
+    _check(packed.size(-1) == _words(int(n)), f"{what}: last dimension must be ceil(n/64) words")
+    pc = packed.contiguous()
+    rows = pc.numel() // pc.size(-1) if pc.size(-1) else 0
+    return pc, rows
+
+
+def flip_packed(packed: torch.Tensor, n: int) -> torch.Tensor:
+    """Reverse the n bits of every row of a packed buffer (flip along the packed axis)."""
+    pc, rows = _packed_rows(packed, n, "flip_packed")
+    out = torch.empty_like(pc)
+    if out.numel():
+        with torch.cuda.device(pc.device):
+            L.check(_lib.brute_b200_flip_bits(pc.data_ptr(), out.data_ptr(), rows, int(n), _stream(pc)), "flip_packed")
+    return out
+
+
+def roll_packed(packed: torch.Tensor, n: int, shift: int) -> torch.Tensor:
+    """torch.roll along the packed axis: out bit j = in bit (j - shift) mod n."""
+    pc, rows = _packed_rows(packed, n, "roll_packed")
+    out = torch.empty_like(pc)
+    if out.numel():
+        with torch.cuda.device(pc.device):
+            L.check(_lib.brute_b200_roll_bits(pc.data_ptr(), out.data_ptr(), rows, int(n), int(shift), _stream(pc)),
+                    "roll_packed")
+    return out
+
+
+def gather_packed(packed: torch.Tensor, idx: torch.Tensor, n_in: int) -> torch.Tensor:
+    """index_select along the packed axis: out bit j of every row = in bit idx[j]."""
+    pc, rows = _packed_rows(packed, n_in, "gather_packed")
+    _check(idx.dim() == 1 and idx.dtype == torch.int64 and idx.device == pc.device,
+           "gather_packed: idx must be a 1-D int64 tensor on the input's device")
+    ic = idx.contiguous()
+    n_out = int(ic.numel())
+    out = torch.empty(tuple(pc.shape[:-1]) + (_words(n_out),), dtype=torch.int64, device=pc.device)
+    if out.numel():
+        with torch.cuda.device(pc.device):
+            L.check(_lib.brute_b200_gather_bits(pc.data_ptr() if pc.numel() else None, ic.data_ptr(), out.data_ptr(),
+                                                rows if pc.size(-1) else out.numel() // out.size(-1), int(n_in), n_out,
+                                                _stream(pc)), "gather_packed")
+    return out
+
+
 def randomize_bits(out: torch.Tensor) -> torch.Tensor:
     out.random_()          # cbrute/cuda/ops_cuda.cu:340, a plain ATen call
     return out
@@ -399,6 +447,7 @@ _CUDA_IMPLS = {
     "row_any": row_any, "row_all": row_all, "xnor_popcount_matmul_impl": xnor_popcount_matmul_impl,
     "xnor_matmul_scale_sign_pack": xnor_matmul_scale_sign_pack, "binary_attention": binary_attention,
     "transpose_packed": transpose_packed, "reduce_rows_packed": reduce_rows_packed,
+    "flip_packed": flip_packed, "roll_packed": roll_packed, "gather_packed": gather_packed,
 }
 _IMPL = torch.library.Library("brute", "IMPL", "CUDA")
 for _name, _fn in _CUDA_IMPLS.items():
@@ -436,6 +485,10 @@ def _register_fakes() -> None:
     reg("brute::binary_attention")(lambda Qp, Kp, V, causal, scale: torch.empty_like(V))
     reg("brute::transpose_packed")(
         lambda packed, rows, cols: packed.new_empty(tuple(packed.shape[:-2]) + (cols, _words(rows)), dtype=torch.int64))
+    reg("brute::flip_packed")(lambda packed, n: torch.empty_like(packed))
+    reg("brute::roll_packed")(lambda packed, n, shift: torch.empty_like(packed))
+    reg("brute::gather_packed")(
+        lambda packed, idx, n_in: packed.new_empty(tuple(packed.shape[:-1]) + (_words(idx.shape[0]),), dtype=torch.int64))
     reg("brute::reduce_rows_packed")(
         lambda packed, dim, use_or: packed.new_empty(tuple(s for i, s in enumerate(packed.shape) if i != dim % packed.dim()),
                                                      dtype=torch.int64))

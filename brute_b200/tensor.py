@@ -1194,6 +1194,16 @@ def _h_index_select(func, args, kwargs, b1):
         if a.dim() >= 2 and dim == 0 and isinstance(idx, torch.Tensor) and idx.dim() == 1:
             return Tensor._make_bit1_from_packed(a._packed_buf.index_select(0, _plain(idx)),
                                                  [int(idx.numel())] + list(a.shape[1:]))
+        if (a.dim() >= 1 and isinstance(dim, int) and dim in (-1, a.dim() - 1) and isinstance(idx, torch.Tensor)
+                and idx.dim() == 1 and idx.dtype in (torch.int64, torch.int32) and not _is_b1(idx)):
+            # the packed axis: gather bits in the packed domain. torch raises on an index out of
+            # range; so does this (one small reduction on the index vector, no pass over the data)
+            n = int(a.shape[-1])
+            ix = _plain(idx).to(torch.int64)
+            if ix.numel() and (int(ix.min()) < 0 or int(ix.max()) >= n):
+                raise IndexError("index out of range in self")
+            out = _ops.gather_packed(a._packed_buf_contig(), ix.to(a.device), n)
+            return Tensor._make_bit1_from_packed(out, list(a.shape[:-1]) + [int(ix.numel())])
     return NotImplemented
 
 
@@ -1258,12 +1268,49 @@ def _h_flip(func, args, kwargs, b1):
     if len(b1) == 1 and b1[0].dim() >= 1:
         a = b1[0]
         dims = _arg(args, kwargs, 1, "dims")
+        if isinstance(dims, int) and all(isinstance(x, int) for x in args[1:]):
+            dims = tuple(args[1:])          # Tensor.flip(0, 2): the dims as separate arguments
         if isinstance(dims, (list, tuple)) and dims and all(isinstance(x, int) for x in dims):
             nd = a.dim()
             norm = [x if x >= 0 else nd + x for x in dims]
             if (nd - 1) not in norm:
                 return Tensor._make_bit1_from_packed(a._packed_buf.flip(norm), list(a.shape))
+            if len(set(norm)) == len(norm) and all(0 <= x < nd for x in norm):
+                # the packed axis: reverse the bits of every row in the packed domain; the other
+                # axes are word-wise flips of the packed buffer
+                others = [x for x in norm if x != nd - 1]
+                packed = a._packed_buf_contig()
+                if others:
+                    packed = packed.flip(others)
+                return Tensor._make_bit1_from_packed(_ops.flip_packed(packed, int(a.shape[-1])), list(a.shape))
     return NotImplemented
+
+
+@_fast(torch.roll, torch.Tensor.roll)
+def _h_roll(func, args, kwargs, b1):
+    if len(b1) != 1 or not _is_b1(args[0]) or args[0].dim() < 1:
+        return NotImplemented
+    a = args[0]
+    shifts = _arg(args, kwargs, 1, "shifts")
+    dims = _arg(args, kwargs, 2, "dims", None)
+    if isinstance(shifts, int) and isinstance(dims, int):
+        shifts, dims = (shifts,), (dims,)
+    if dims is None or not isinstance(shifts, (list, tuple)) or not isinstance(dims, (list, tuple)):
+        return NotImplemented          # dims=None rolls the flattened tensor: leave it to the bool path
+    if len(shifts) != len(dims) or not all(isinstance(x, int) for x in list(shifts) + list(dims)):
+        return NotImplemented
+    nd = a.dim()
+    norm = [x if x >= 0 else nd + x for x in dims]
+    if not all(0 <= x < nd for x in norm):
+        return NotImplemented
+    packed = a._packed_buf_contig()
+    lead = [(s_, d_) for s_, d_ in zip(shifts, norm) if d_ != nd - 1]
+    if lead:
+        packed = torch.roll(packed, [s_ for s_, _ in lead], [d_ for _, d_ in lead])
+    last = sum(s_ for s_, d_ in zip(shifts, norm) if d_ == nd - 1)
+    if any(d_ == nd - 1 for d_ in norm) and int(a.shape[-1]) > 0:
+        packed = _ops.roll_packed(packed.contiguous(), int(a.shape[-1]), int(last))
+    return Tensor._make_bit1_from_packed(packed, list(a.shape))
 
 
 @_fast(torch.Tensor.repeat)

@@ -191,6 +191,20 @@ int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out,
 int brute_b200_reduce_rows(int op, const uint64_t* in, uint64_t* out,
                            int64_t outer, int64_t R, int64_t inner, void* stream);
 
+/* Moves along the packed (last) axis without leaving the packed domain; rows of n bits,
+ * ceil(n/64) words each, pad bits of the result 0, in and out must not overlap:
+ *   flip:   out bit j = in bit n - 1 - j
+ *   roll:   out bit j = in bit (j - shift) mod n        (torch.roll semantics, any sign of shift)
+ *   gather: out bit j = in bit idx[j], j < n_out; idx is a device array of n_out int64, the same
+ *           for every row; an index outside [0, n_in) reads as 0.
+ * Replace the unpack -> bool flip/roll/index_select -> re-pack fallback of the reference
+ * (brute/tensor.py:699-775, 795-801). */
+int brute_b200_flip_bits(const uint64_t* in, uint64_t* out, int64_t rows, int64_t n, void* stream);
+int brute_b200_roll_bits(const uint64_t* in, uint64_t* out, int64_t rows, int64_t n, int64_t shift,
+                         void* stream);
+int brute_b200_gather_bits(const uint64_t* in, const int64_t* idx, uint64_t* out,
+                           int64_t rows, int64_t n_in, int64_t n_out, void* stream);
+
 /* ---- xnor-popcount GEMM ------------------------------------------------ */
 /* A [M, Kp] words, B [N, Kp] words (rows of B are output features), K logical
  * bits (K <= 64*Kp, pad bits 0) -> C [M, N] int32 with row pitch ldc elements,

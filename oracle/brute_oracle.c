@@ -443,3 +443,22 @@ void oracle_reduce_rows(int op, const uint64_t* in, uint64_t* out, int64_t outer
             out[o * inner + i] = acc;
         }
 }
+
+
+/* Moves along the packed axis, bit by bit. The reference unpacks, applies torch.flip / torch.roll /
+ * index_select on the bools and packs again (brute/tensor.py:699-775, 795-801); these restate that
+ * composition. mode 0: flip, 1: roll by `shift` (torch.roll), 2: gather through idx[n_out]. */
+void oracle_move_bits(int mode, const uint64_t* in, const int64_t* idx, uint64_t* out,
+                      int64_t rows, int64_t n_in, int64_t n_out, int64_t shift) {
+    const int64_t wi = (n_in + 63) / 64, wo = (n_out + 63) / 64;
+    memset(out, 0, (size_t)(rows * wo) * 8);
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t j = 0; j < n_out; ++j) {
+            int64_t s;
+            if (mode == 0) s = n_in - 1 - j;
+            else if (mode == 1) { s = (j - shift) % n_in; if (s < 0) s += n_in; }
+            else s = idx[j];
+            if (s < 0 || s >= n_in) continue;
+            if ((in[r * wi + (s >> 6)] >> (s & 63)) & 1ull) out[r * wo + (j >> 6)] |= 1ull << (j & 63);
+        }
+}

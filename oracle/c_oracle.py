@@ -56,6 +56,7 @@ def lib():
         L.oracle_binary_attention.argtypes = [p, p, p, p, i64, i64, i64, i32, f32]
         L.oracle_transpose_bits.argtypes = [p, p, i64, i64, i64]
         L.oracle_reduce_rows.argtypes = [i32, p, p, i64, i64, i64]
+        L.oracle_move_bits.argtypes = [i32, p, p, p, i64, i64, i64, i64]
         _lib = L
     return _lib
 
@@ -270,3 +271,25 @@ def reduce_rows(packed: np.ndarray, dim: int, use_or: bool) -> np.ndarray:
     if out.size:
         lib().oracle_reduce_rows(1 if use_or else 0, _ptr(p), _ptr(out), outer, int(p.shape[d]), inner)
     return out
+
+
+def _move_bits(mode: int, packed: np.ndarray, n_in: int, n_out: int, idx=None, shift: int = 0) -> np.ndarray:
+    p = _u64(packed)
+    rows = int(np.prod(p.shape[:-1], dtype=np.int64)) if p.ndim > 1 else 1
+    out = np.zeros(p.shape[:-1] + ((int(n_out) + 63) // 64,), dtype=np.uint64)
+    ix = None if idx is None else _c(idx, np.int64)
+    if out.size:
+        lib().oracle_move_bits(mode, _ptr(p), None if ix is None else _ptr(ix), _ptr(out), rows, int(n_in), int(n_out), int(shift))
+    return out
+
+
+def flip_bits(packed: np.ndarray, n: int) -> np.ndarray:
+    return _move_bits(0, packed, n, n)
+
+
+def roll_bits(packed: np.ndarray, n: int, shift: int) -> np.ndarray:
+    return _move_bits(1, packed, n, n, shift=shift)
+
+
+def gather_bits(packed: np.ndarray, idx: np.ndarray, n_in: int) -> np.ndarray:
+    return _move_bits(2, packed, n_in, int(np.asarray(idx).size), idx=idx)

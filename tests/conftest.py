@@ -151,6 +151,9 @@ def install_oracle_cpu_ops():
 
     lib.impl("signed_bundle", lambda W, V, D: n2t(co.signed_bundle(t2n(W), t2n(V), D), torch.int64))
     lib.impl("transpose_packed", lambda packed, rows, cols: n2t(co.transpose_bits(t2n(packed.contiguous()), rows, cols), torch.int64))
+    lib.impl("flip_packed", lambda packed, n: n2t(co.flip_bits(t2n(packed.contiguous()), n), torch.int64))
+    lib.impl("roll_packed", lambda packed, n, shift: n2t(co.roll_bits(t2n(packed.contiguous()), n, shift), torch.int64))
+    lib.impl("gather_packed", lambda packed, idx, n_in: n2t(co.gather_bits(t2n(packed.contiguous()), t2n(idx), n_in), torch.int64))
     lib.impl("reduce_rows_packed", lambda packed, dim, use_or: n2t(co.reduce_rows(t2n(packed.contiguous()), dim, use_or), torch.int64))
 
     def randomize(out):

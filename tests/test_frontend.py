@@ -341,3 +341,24 @@ def test_any_all_over_leading_dims(brute):
         for keepdim in (False, True):
             assert torch.equal(as_bool(b.any(dim=dim, keepdim=keepdim)), x.any(dim=dim, keepdim=keepdim).cpu())
             assert torch.equal(as_bool(b.all(dim=dim, keepdim=keepdim)), x.all(dim=dim, keepdim=keepdim).cpu())
+
+
+def test_flip_roll_index_select_on_packed_axis(brute):
+    x = rnd((3, 5, 131), 16)
+    b = b1(brute, x)
+    cases = {
+        "flip_last": (torch.flip(b, [-1]), torch.flip(x, [-1])),
+        "flip_all": (b.flip(0, 2), x.flip(0, 2)),
+        "roll_last": (torch.roll(b, 7, -1), torch.roll(x, 7, -1)),
+        "roll_neg": (b.roll(-200, 2), x.roll(-200, 2)),
+        "roll_two": (torch.roll(b, (1, 70), (0, -1)), torch.roll(x, (1, 70), (0, -1))),
+    }
+    idx = torch.tensor([130, 0, 5, 5, 64, 63], device=DEV)
+    cases["index_select"] = (torch.index_select(b, -1, idx), torch.index_select(x, -1, idx))
+    for name, (got, want) in cases.items():
+        assert got.dtype == brute.bit1 and tuple(got.shape) == tuple(want.shape), name
+        assert got.__dict__.get("_bool_dirty") is True, f"{name}: should stay in the packed domain"
+        assert same(as_bool(got), want), name
+        assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
+    with pytest.raises(IndexError):
+        torch.index_select(b, -1, torch.tensor([131], device=DEV))

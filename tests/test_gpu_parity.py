@@ -438,6 +438,24 @@ def test_reduce_rows_packed(ops, co, shape, dim):
         ops.reduce_rows_packed(p, len(shape) - 1, True)
 
 
+@pytest.mark.parametrize("shape", [(1,), (5,), (64,), (65,), (3, 130), (2, 3, 257), (4, 1003), (7, 4097), (1, 1 << 20), (300, 6400)])
+def test_flip_roll_gather_packed(ops, co, shape):
+    x = torch.rand(shape, generator=gen(sum(shape))) < 0.5
+    n = shape[-1]
+    p = ops.pack_bool(x.to(DEV))
+    assert np.array_equal(u64(ops.flip_packed(p, n)), co.pack_bool(torch.flip(x, [-1]).numpy()))
+    for shift in (0, 1, -1, 63, 64, 65, n - 1, n, 3 * n + 7, -2 * n - 5, n // 2):
+        assert np.array_equal(u64(ops.roll_packed(p, n, shift)), co.pack_bool(torch.roll(x, shift, -1).numpy())), shift
+    idx = torch.randint(0, n, (min(2 * n + 3, 100000),), generator=gen(n))
+    got = ops.gather_packed(p, idx.to(DEV), n)
+    assert np.array_equal(u64(got), co.pack_bool(x.index_select(-1, idx).numpy()))
+    assert np.array_equal(u64(got), co.gather_bits(u64(p), idx.numpy(), n))
+    # an index outside the row reads as 0 at the C ABI (the front end raises before it gets there)
+    bad = idx.clone()
+    bad[0] = n
+    assert np.array_equal(u64(ops.gather_packed(p, bad.to(DEV), n)), co.gather_bits(u64(p), bad.numpy(), n))
+
+
 # ---------------------------------------------------------------------------
 # signed_bundle
 # ---------------------------------------------------------------------------

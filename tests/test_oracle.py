@@ -179,3 +179,16 @@ def test_reduce_rows_vs_numpy():
         p = co.pack_bool(x)
         assert np.array_equal(co.reduce_rows(p, dim, True), no.pack_bool(x.any(axis=dim))), (shape, dim)
         assert np.array_equal(co.reduce_rows(p, dim, False), no.pack_bool(x.all(axis=dim))), (shape, dim)
+
+
+def test_move_bits_vs_numpy():
+    rng = np.random.default_rng(33)
+    for shape in [(1,), (5,), (64,), (65,), (3, 130), (2, 3, 257), (4, 1003)]:
+        x = rng.random(shape) < 0.5
+        n = shape[-1]
+        p = co.pack_bool(x)
+        assert np.array_equal(co.flip_bits(p, n), no.pack_bool(np.flip(x, -1))), shape
+        for shift in (0, 1, -1, 63, 64, 65, n - 1, n, 3 * n + 7, -2 * n - 5):
+            assert np.array_equal(co.roll_bits(p, n, shift), no.pack_bool(np.roll(x, shift, -1))), (shape, shift)
+        idx = rng.integers(0, n, size=2 * n + 3)
+        assert np.array_equal(co.gather_bits(p, idx, n), no.pack_bool(np.take(x, idx, axis=-1))), shape
