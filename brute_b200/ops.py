@@ -11,7 +11,9 @@ CPU kernel and no fallback, an op on a CPU tensor fails in the dispatcher.
 Ops beyond the reference's eleven carry new names and never change the eleven:
 ``pack_sign``, ``bitwise_packed``, ``select_packed``, ``row_any``, ``row_all``,
 ``xnor_popcount_matmul_impl``, ``xnor_matmul_scale_sign_pack``,
-``binary_attention``.
+``binary_attention``, ``transpose_packed``, ``reduce_rows_packed``, ``flip_packed``,
+``roll_packed``, ``gather_packed``. ``signed_bundle`` keeps the reference's schema and
+runs on the tensor cores; the scratch it needs is allocated here, never by the library.
 """
 from __future__ import annotations
 

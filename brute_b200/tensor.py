@@ -6,20 +6,23 @@ Same surface and laziness contract as the reference's ``brute/tensor.py``:
   carries an int64-packed side buffer, 64 bits per word along the last axis,
   pad bits 0 (``_packed_buf``);
 * results of packed-domain ops are built from the packed buffer only; their bool
-  storage is allocated but not filled (``_bool_dirty``) until something reads it
-  (``_ensure_bool_valid``, reference brute/tensor.py:327-352);
+  storage is a one-byte placeholder broadcast to the logical shape (``_bool_dirty``) until
+  something reads it (``_ensure_bool_valid``, reference brute/tensor.py:327-352, which
+  allocates the full bool tensor up front);
 * in-place writes to the bool storage are noticed through torch's version
   counter (``_packed_ver``) and re-pack lazily (brute/tensor.py:362-388);
-* ``b.t()`` of a 2-D bit1 tensor remembers its source (``_t_source``) so that
+* a transpose of the last two dimensions remembers its source (``_t_source``) so that
   ``a @ b.t()`` feeds the (N, K) packed buffer to the xnor GEMM
-  (brute/tensor.py:1210-1266).
+  (brute/tensor.py:1210-1266), and so that its own packed words come from a bit-matrix
+  transpose of the source's instead of a pack of the bool view.
 
 The dispatch is organised differently from the reference: ``__torch_function__``
 looks the function up in a handler table (``_FAST``) instead of walking one long
 chain of tests; a handler returns ``NotImplemented`` to fall through to the
 generic bool path. On CUDA the packed-domain handlers call this package's own
-kernels (fused xnor / masked not / select / row reductions / float->bit pack)
-where the reference composes several ATen launches.
+kernels (fused xnor / masked not / select / reductions over any axis / float->bit pack /
+flip, roll and index_select along the packed axis) where the reference composes several
+ATen launches or goes through bool.
 """
 from __future__ import annotations
 
