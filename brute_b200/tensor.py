@@ -459,7 +459,31 @@ class Tensor(torch.Tensor):
                 shape = list(self.shape[1:]) if isinstance(idx, int) else [sub.shape[0]] + list(self.shape[1:])
             if sub.numel() != 0:
                 return Tensor._make_bit1_from_packed(sub, shape)
+        sl = self._last_axis_slice(idx)
+        if sl is not None:
+            # x[..., a:b:s]: pick the bits in the packed domain
+            n = int(self.shape[-1])
+            pos = torch.arange(sl.start, sl.stop, sl.step, dtype=torch.int64, device=self.device)
+            if pos.numel() > 0:
+                out = _ops.gather_packed(self._packed_buf_contig(), pos, n)
+                return Tensor._make_bit1_from_packed(out, list(self.shape[:-1]) + [int(pos.numel())])
         return super().__getitem__(idx)
+
+    def _last_axis_slice(self, idx) -> Optional[range]:
+        """``range`` of the positions that ``idx`` keeps along the last axis when that is all it does
+        (``x[..., a:b:s]`` or ``x[:, :, a:b:s]`` with positive step), else None."""
+        if not _is_b1(self) or self.dim() < 1 or not isinstance(idx, tuple) or not idx:
+            return None
+        last = idx[-1]
+        if not isinstance(last, slice):
+            return None
+        lead = idx[:-1]
+        full = slice(None)
+        if lead == (Ellipsis,) or (len(lead) == self.dim() - 1 and all(isinstance(x, slice) and x == full for x in lead)):
+            if last == full or (last.step is not None and last.step <= 0):
+                return None
+            return range(*last.indices(int(self.shape[-1])))
+        return None
 
     def _row_pattern(self, value: bool) -> torch.Tensor:
         """One packed row of all-`value` bits with zero pad bits."""
@@ -1325,9 +1349,14 @@ def _h_repeat(func, args, kwargs, b1):
             reps = tuple(reps[0])
         if a.dim() >= 1 and len(reps) == a.dim() and all(isinstance(r, int) and r >= 0 for r in reps):
             last = int(a.shape[-1])
+            shape = [int(a.shape[i]) * int(reps[i]) for i in range(a.dim())]
             if reps[-1] == 1 or (last > 0 and last % _PACK_WIDTH == 0):
-                shape = [int(a.shape[i]) * int(reps[i]) for i in range(a.dim())]
                 return Tensor._make_bit1_from_packed(a._packed_buf.repeat(*reps), shape)
+            if last > 0 and reps[-1] > 1 and all(x > 0 for x in shape):
+                # ragged last dim: repeat the other axes word-wise, then lay the row's bits end to end
+                packed = a._packed_buf_contig().repeat(*reps[:-1], 1)
+                pos = torch.arange(last * reps[-1], dtype=torch.int64, device=a.device) % last
+                return Tensor._make_bit1_from_packed(_ops.gather_packed(packed.contiguous(), pos, last), shape)
     return NotImplemented
 
 

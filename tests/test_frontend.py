@@ -362,3 +362,14 @@ def test_flip_roll_index_select_on_packed_axis(brute):
         assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
     with pytest.raises(IndexError):
         torch.index_select(b, -1, torch.tensor([131], device=DEV))
+    more = {
+        "slice": (b[..., 3:100], x[..., 3:100]), "slice_step": (b[:, :, 1::3], x[:, :, 1::3]),
+        "slice_neg": (b[..., -70:-1:2], x[..., -70:-1:2]),
+        "repeat_ragged": (b.repeat(2, 1, 3), x.repeat(2, 1, 3)),
+    }
+    for name, (got, want) in more.items():
+        assert got.dtype == brute.bit1 and tuple(got.shape) == tuple(want.shape), name
+        assert got.__dict__.get("_bool_dirty") is True, f"{name}: should stay in the packed domain"
+        assert same(as_bool(got), want), name
+        assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
+    assert same(as_bool(b[..., 5:5]), x[..., 5:5])          # empty: the generic path
