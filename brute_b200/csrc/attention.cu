@@ -663,20 +663,11 @@ extern "C" int brute_b200_binary_attention_fwd(const uint64_t* Qp, const uint64_
             else          k_binary_attention_fwd_table<1><<<grid, AT_THREADS, 0, st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
             return launch_status();
         }
-        static bool attr_set[2] = {false, false};
         if (D == 128) {
-            if (!attr_set[1]) {
-                if (cudaFuncSetAttribute(k_binary_attention_fwd_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_mma_smem<2>()) != cudaSuccess)
-                    return BRUTE_ERR_LAUNCH;
-                attr_set[1] = true;
-            }
+            if (!kernel_smem_ready<k_binary_attention_fwd_mma<2>>(at_mma_smem<2>())) return BRUTE_ERR_LAUNCH;
             k_binary_attention_fwd_mma<2><<<grid, AT_THREADS, at_mma_smem<2>(), st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
         } else {
-            if (!attr_set[0]) {
-                if (cudaFuncSetAttribute(k_binary_attention_fwd_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_mma_smem<1>()) != cudaSuccess)
-                    return BRUTE_ERR_LAUNCH;
-                attr_set[0] = true;
-            }
+            if (!kernel_smem_ready<k_binary_attention_fwd_mma<1>>(at_mma_smem<1>())) return BRUTE_ERR_LAUNCH;
             k_binary_attention_fwd_mma<1><<<grid, AT_THREADS, at_mma_smem<1>(), st>>>(Qp, Kp_, v, o, S, causal, neg2c, bias, q_tiles);
         }
         return launch_status();

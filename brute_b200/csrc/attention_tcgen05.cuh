@@ -348,12 +348,7 @@ static int ax_run(const uint64_t* Qp, const uint64_t* Kp, const void* V, void* O
                   int causal, float neg2c_log2, float bias_log2, cudaStream_t st) {
     CUtensorMap tmV;
     BB_REQUIRE(S < (1ll << 31) - AX_BM && ax_make_v_map(&tmV, V, BH, S), BRUTE_ERR_DRIVER);
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k_binary_attention_fwd_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, AX_SMEM) != cudaSuccess)
-            return BRUTE_ERR_LAUNCH;
-        attr_set = true;
-    }
+    if (!kernel_smem_ready<k_binary_attention_fwd_tcgen05>(AX_SMEM)) return BRUTE_ERR_LAUNCH;
     const int64_t q_tiles = (S + AX_BM - 1) / AX_BM;
     const dim3 grid((unsigned)q_tiles, (unsigned)BH);
     k_binary_attention_fwd_tcgen05<<<grid, AX_THREADS, AX_SMEM, st>>>(tmV, Qp, Kp, static_cast<__nv_bfloat16*>(O), S, causal,

@@ -53,6 +53,19 @@ inline int resident_grid(Kernel kernel, int block_threads, int64_t blocks_needed
     return (int)(blocks_needed < cap ? blocks_needed : cap);
 }
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device setting of a kernel: remember per
+// device (not per process) where it has been made, so that one process may drive several GPUs.
+template <auto Kernel>
+inline bool kernel_smem_ready(int bytes) {
+    static unsigned long long done_mask = 0;       // bit d: device d is set up (devices >= 64: every call)
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess) return false;
+    if (d >= 0 && d < 64 && ((done_mask >> d) & 1ull)) return true;
+    if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    if (d >= 0 && d < 64) done_mask |= 1ull << d;
+    return true;
+}
+
 // 128-bit streaming load that does not allocate in L1.
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;

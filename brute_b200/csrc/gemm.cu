@@ -40,22 +40,15 @@ static bool mma_b1_accepts(const GemmArgs& g) {
 
 static int run_mma_b1(const GemmArgs& g, cudaStream_t st) {
     BB_REQUIRE(mma_b1_accepts(g), BRUTE_ERR_UNSUPPORTED);
-    static bool attr_set[2] = {false, false};
     const dim3 grid((unsigned)((g.N + MB_BN - 1) / MB_BN), (unsigned)((g.M + MB_BM - 1) / MB_BM));
     auto* A8 = reinterpret_cast<const uint8_t*>(g.A);
     auto* B8 = reinterpret_cast<const uint8_t*>(g.B);
     if (!g.pack) {
-        if (!attr_set[0]) {
-            cudaFuncSetAttribute(k_xnor_gemm_mma_b1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MB_SMEM);
-            attr_set[0] = true;
-        }
+        if (!kernel_smem_ready<k_xnor_gemm_mma_b1<false>>(MB_SMEM)) return BRUTE_ERR_LAUNCH;
         k_xnor_gemm_mma_b1<false><<<grid, MB_THREADS, MB_SMEM, st>>>(
             A8, B8, g.M, g.N, g.Kp * 8, (int32_t)g.K, g.C, g.ldc, nullptr, nullptr, 0, 0);
     } else {
-        if (!attr_set[1]) {
-            cudaFuncSetAttribute(k_xnor_gemm_mma_b1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MB_SMEM);
-            attr_set[1] = true;
-        }
+        if (!kernel_smem_ready<k_xnor_gemm_mma_b1<true>>(MB_SMEM)) return BRUTE_ERR_LAUNCH;
         k_xnor_gemm_mma_b1<true><<<grid, MB_THREADS, MB_SMEM, st>>>(
             A8, B8, g.M, g.N, g.Kp * 8, (int32_t)g.K, nullptr, 0, g.scale,
             reinterpret_cast<uint32_t*>(g.out), 2 * ((g.N + 63) / 64), g.mode);

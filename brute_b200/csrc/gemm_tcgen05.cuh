@@ -368,23 +368,14 @@ static int tc5_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, i
     BB_REQUIRE(tc5_accepts(A, B, M, N, Kp), BRUTE_ERR_UNSUPPORTED);
     CUtensorMap tmA, tmB;
     BB_REQUIRE(tc5_make_map(&tmA, A, M, Kp * 8, TC_BM) && tc5_make_map(&tmB, B, N, Kp * 8, TC_BN), BRUTE_ERR_DRIVER);
-    static bool attr_set[2] = {false, false};
     const dim3 grid((unsigned)((N + TC_BN - 1) / TC_BN), (unsigned)((M + TC_BM - 1) / TC_BM));
     const int32_t nkb = (int32_t)(Kp / 2);
     const int32_t klogical = (int32_t)K;
     if (!pack) {
-        if (!attr_set[0]) {
-            if (cudaFuncSetAttribute(k_xnor_gemm_tcgen05<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess)
-                return BRUTE_ERR_LAUNCH;
-            attr_set[0] = true;
-        }
+        if (!kernel_smem_ready<k_xnor_gemm_tcgen05<false>>(TC_SMEM)) return BRUTE_ERR_LAUNCH;
         k_xnor_gemm_tcgen05<false><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, klogical, C, ldc, nullptr, nullptr, 0, 0);
     } else {
-        if (!attr_set[1]) {
-            if (cudaFuncSetAttribute(k_xnor_gemm_tcgen05<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM) != cudaSuccess)
-                return BRUTE_ERR_LAUNCH;
-            attr_set[1] = true;
-        }
+        if (!kernel_smem_ready<k_xnor_gemm_tcgen05<true>>(TC_SMEM)) return BRUTE_ERR_LAUNCH;
         k_xnor_gemm_tcgen05<true><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, klogical, nullptr, 0, scale,
                                                                     reinterpret_cast<uint32_t*>(out), 2 * ((N + 63) / 64), mode);
     }

@@ -497,8 +497,11 @@ static int tc5_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const
                            int64_t M, int64_t N, int32_t nkb, int32_t klogical, int32_t tiles_m, int32_t ntiles,
                            int32_t* C, int64_t ldc, const float* scale, uint32_t* out32, int64_t halves_per_row, int mode,
                            cudaStream_t st) {
-    static int max_pairs = 0;       // pairs of SMs that can hold this kernel at once
+    static int max_pairs_dev[64] = {0};     // per device: pairs of SMs that can hold this kernel at once
     auto kern = k_xnor_gemm_tcgen05_pair<STORE>;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BRUTE_ERR_LAUNCH;
+    int& max_pairs = max_pairs_dev[dev];
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -506,9 +509,8 @@ static int tc5_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const
     cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = TP_SMEM; cfg.stream = st; cfg.attrs = attr; cfg.numAttrs = 1;
     if (max_pairs == 0) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) != cudaSuccess) return BRUTE_ERR_LAUNCH;
-        int dev = 0, sms = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            return BRUTE_ERR_LAUNCH;
+        int sms = 0, n = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return BRUTE_ERR_LAUNCH;
         cfg.gridDim = dim3((unsigned)(2 * (sms / 2)));
         if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sms / 2; }
         max_pairs = n < sms / 2 ? n : sms / 2;

@@ -320,12 +320,7 @@ extern "C" int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out,
         R < (1ll << 31) - TB_TILE && C < (1ll << 31) - TB_TILE) {
         CUtensorMap tmIn, tmOut;
         if (tb_make_map(&tmIn, in, batch, R, wpr_in) && tb_make_map(&tmOut, out, batch, C, wpr_out)) {
-            static bool attr_set = false;
-            if (!attr_set) {
-                if (cudaFuncSetAttribute(k_transpose_bits_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, TB_TMA_SMEM) != cudaSuccess)
-                    return BRUTE_ERR_LAUNCH;
-                attr_set = true;
-            }
+            if (!kernel_smem_ready<k_transpose_bits_tma>(TB_TMA_SMEM)) return BRUTE_ERR_LAUNCH;
             k_transpose_bits_tma<<<grid, TB_THREADS, TB_TMA_SMEM, as_stream(stream)>>>(tmIn, tmOut, gx, gy, sgx);
             return launch_status();
         }

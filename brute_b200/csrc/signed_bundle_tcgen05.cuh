@@ -245,12 +245,7 @@ static int st_run(const int8_t* W, const uint64_t* Vt, uint64_t* out, int64_t B,
                   int64_t Dp, int64_t D, cudaStream_t st) {
     CUtensorMap tmW;
     BB_REQUIRE(st_make_w_map(&tmW, W, B, M, N), BRUTE_ERR_DRIVER);
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k_signed_bundle_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM) != cudaSuccess)
-            return BRUTE_ERR_LAUNCH;
-        attr_set = true;
-    }
+    if (!kernel_smem_ready<k_signed_bundle_tcgen05>(ST_SMEM)) return BRUTE_ERR_LAUNCH;
     const dim3 grid((unsigned)((M + ST_BM - 1) / ST_BM), (unsigned)((D + ST_DB - 1) / ST_DB), (unsigned)B);
     k_signed_bundle_tcgen05<<<grid, ST_THREADS, ST_SMEM, st>>>(tmW, Vt, out, M, N, D, Dp, (N + 63) / 64);
     return launch_status();
