@@ -53,7 +53,7 @@ def parse_args():
     ap.add_argument("--op", default="gemm",
                     help="time ONE op alone (for profiler captures): gemm | pack_sign | pack_bool | unpack_bool | "
                          "unpack_pm1 | popcount_total | hamming_total | word_popcount | xor | not | attention | mlp | "
-                         "pack_bool_4097 | unpack_bool_4097 | memset | transpose_bits | any_dim0")
+                         "pack_bool_4097 | unpack_bool_4097 | memset | transpose_bits | any_dim0 | signed_bundle")
     ap.add_argument("--log2-bits", type=int, default=28, help="size of the bandwidth ops under --op")
     ap.add_argument("--att", default="2,8,4096,128", help="B,H,S,D of --op attention")
     return ap.parse_args()
@@ -523,6 +523,11 @@ def run_single_op(args):
         kb = brute.pack_sign(torch.randn((Bq, H, S, D), generator=g, device=dev), ge0=True)
         v = torch.randn((Bq, H, S, D), generator=g, device=dev).to(torch.bfloat16)
         fn, alg = (lambda: brute.binary_attention(qb, kb, v, causal=True)), 2 * Bq * H * S * (D // 4) + 2 * Bq * H * S * D * 2
+    elif args.op == "signed_bundle":
+        Bb, Mb, Nb, Db = 256, 1024, 1024, 128
+        wv = torch.randint(-3, 4, (Bb, Mb, Nb), generator=g, device=dev, dtype=torch.int8)
+        vv = torch.randint(-2 ** 63, 2 ** 63 - 1, (Bb, Nb, Db // 64), generator=g, dtype=torch.int64, device=dev)
+        fn, alg = (lambda: ops.signed_bundle(wv, vv, Db)), Bb * Mb * Nb + Bb * Nb * Db // 8 + Bb * Mb * Db // 8
     elif args.op == "mlp":
         xs = brute.pack_sign(torch.randn((8192, 4096), generator=g, device=dev), ge0=True)
         w1 = brute.pack_sign(torch.randn((16384, 4096), generator=g, device=dev), ge0=True)
