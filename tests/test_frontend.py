@@ -373,3 +373,37 @@ def test_flip_roll_index_select_on_packed_axis(brute):
         assert same(as_bool(got), want), name
         assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
     assert same(as_bool(b[..., 5:5]), x[..., 5:5])          # empty: the generic path
+
+
+# ---------------------------------------------------------------------------
+# concurrent host threads (the reference requires this of its drivers: tests/unit/test_multithread.py)
+# ---------------------------------------------------------------------------
+def test_threads_share_one_tensor_and_the_library(brute):
+    from concurrent.futures import ThreadPoolExecutor
+    src = rnd((64, 300), 21)
+    x = b1(brute, src)
+    w = b1(brute, rnd((40, 300), 22))
+    want_pop = int(src.sum())
+    want_mm = cpu(x @ w.t())
+
+    def reader(_):
+        # every thread walks the cached packed buffer, makes lazy results, and launches kernels
+        acc = 0
+        for _ in range(20):
+            acc += int(x.popcount())
+            y = ~(x ^ x.clone())
+            assert int(y.popcount()) == x.numel()
+            assert torch.equal(cpu(x @ w.t()), want_mm)
+        return acc
+
+    def maker(seed):
+        for i in range(20):
+            a = b1(brute, rnd((3, 70), 100 + seed * 20 + i))
+            b = b1(brute, rnd((3, 70), 500 + seed * 20 + i))
+            assert int((a & b).popcount()) + int((a ^ b).popcount()) == int((a | b).popcount())
+        return True
+
+    with ThreadPoolExecutor(max_workers=4) as ex:
+        got = list(ex.map(reader, range(4)))
+        assert all(list(ex.map(maker, range(4))))
+    assert got == [20 * want_pop] * 4
