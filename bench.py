@@ -229,7 +229,7 @@ def run_ours(args):
         pin_to_gpu_numa_node(local_rank)
         dist.init_process_group("nccl", device_id=dev)
 
-    import brute_b200  # noqa: F401  (fails loudly if the CUDA library is missing)
+    import brute_b200 as brute  # fails loudly if the CUDA library is missing
     from brute_b200 import _lib as L
     from brute_b200.kernels import shard_bounds
     ops = torch.ops.brute
@@ -341,6 +341,24 @@ def run_ours(args):
         extra["all_gather_C_ms"] = float(tg.item())
         extra["tops_with_gather"] = macs_all / ((ms_per_step + float(tg.item())) * 1e-3) / 1e12
         del gathered
+
+    if world > 1 and not args.no_extra and size == 16384:
+        # binary attention B=8 H=32 S=4096 D=128 causal, the 256 heads split across the ranks
+        # (no collective on the path); time = max over ranks, rate = all heads / that time
+        Bq, H, S, D = 8, 32, 4096, 128
+        ga = torch.Generator(device=dev).manual_seed(77)      # same operands on every rank
+        qb = brute.pack_sign(torch.randn((Bq, H, S, D), generator=ga, device=dev), ge0=True)
+        kb = brute.pack_sign(torch.randn((Bq, H, S, D), generator=ga, device=dev), ge0=True)
+        vb = torch.randn((Bq, H, S, D), generator=ga, device=dev).to(torch.bfloat16)
+        a_times = time_steps(lambda: brute.sharded_attention(qb, kb, vb, causal=True), 5, 3, flush, sync)
+        ta = torch.tensor([sum(a_times) / 5], dtype=torch.float64, device=dev)
+        dist.all_reduce(ta, op=dist.ReduceOp.MAX)
+        a_ms = float(ta.item())
+        pairs = Bq * H * S * (S + 1) / 2
+        extra["attention_8x32x4096x128_causal_sharded"] = {
+            "ms": a_ms, "heads_per_rank": Bq * H // world, "score_bitmac_tops": pairs * D / (a_ms * 1e-3) / 1e12,
+            "pv_tflops": 2 * pairs * D / (a_ms * 1e-3) / 1e12, "sharding": "batch x head, no collective"}
+        del qb, kb, vb
 
     if rank == 0 and not args.no_extra and size == 16384:
         # rank 0 alone runs these: synchronise the device only, no collective

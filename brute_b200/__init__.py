@@ -19,7 +19,8 @@ from .functional import (  # noqa: E402
 )
 from .fast import *  # noqa: E402,F401,F403
 from . import cuda_graphs, fast, streams  # noqa: E402
-from .kernels import binary_attention, binary_linear, host_matmul, pack_sign, sharded_matmul  # noqa: E402
+from .kernels import (binary_attention, binary_linear, host_matmul, pack_sign,  # noqa: E402
+                      sharded_attention, sharded_matmul)  # noqa: E402
 from .serialization import load_packed, save_packed  # noqa: E402
 
 nn = None

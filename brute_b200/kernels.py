@@ -89,6 +89,48 @@ def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group
     return torch.cat([blocks[r, :, :widths[r]] for r in range(world)], dim=1)
 
 
+def sharded_attention(q: Tensor, k: Tensor, v: torch.Tensor, causal: bool = True,
+                      scale: Optional[float] = None, group=None, gather: bool = False) -> torch.Tensor:
+    """Binary attention sharded by batch x head: the B*H heads are independent, so this
+    rank computes heads [lo, hi) of the flattened (batch, head) axis and no data crosses
+    GPUs on the path. Returns bf16 [hi - lo, S, D]; with ``gather`` the blocks are
+    all-gathered (NCCL on GPUs) and every rank returns the full [B, H, S, D]."""
+    import torch.distributed as dist
+
+    if not (_is_b1(q) and _is_b1(k)):
+        raise TypeError("sharded_attention: q and k must be bit1 tensors")
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    B, H, S, D = (int(x) for x in v.shape)
+    if scale is None:
+        scale = D ** -0.5
+    lo, hi = shard_bounds(B * H, world, rank)
+    qp = q._packed_buf_contig().reshape(1, B * H, S, -1)[:, lo:hi]
+    kp = k._packed_buf_contig().reshape(1, B * H, S, -1)[:, lo:hi]
+    vv = v.as_subclass(torch.Tensor).reshape(1, B * H, S, D)[:, lo:hi]
+    if hi > lo:
+        local = _ops.binary_attention(qp, kp, vv, bool(causal), float(scale))[0]
+    else:
+        local = torch.empty((0, S, D), dtype=v.dtype, device=v.device)
+    if not gather:
+        return local
+    if world == 1:
+        return local.reshape(B, H, S, D)
+    counts = [shard_bounds(B * H, world, r)[1] - shard_bounds(B * H, world, r)[0] for r in range(world)]
+    cmax = max(counts)
+    if cmax == min(counts):
+        full = torch.empty((B * H, S, D), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(full, local.contiguous(), group=group)
+        return full.reshape(B, H, S, D)
+    # uneven blocks: pad to the largest block, gather, drop the padding
+    padded = torch.zeros((cmax, S, D), dtype=local.dtype, device=local.device)
+    padded[:hi - lo] = local
+    stacked = torch.empty((world * cmax, S, D), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(stacked, padded, group=group)
+    blocks = stacked.view(world, cmax, S, D)
+    return torch.cat([blocks[r, :counts[r]] for r in range(world)], dim=0).reshape(B, H, S, D)
+
+
 _host_streams = {}
 
 

@@ -149,6 +149,8 @@ def install_oracle_cpu_ops():
     lib.impl("row_any", lambda A: torch.from_numpy(co.row_any(t2n(A))))
     lib.impl("row_all", lambda A, bits: torch.from_numpy(co.row_all(t2n(A), bits)))
 
+    lib.impl("binary_attention", lambda Qp, Kp, V, causal, scale: torch.from_numpy(
+        co.binary_attention(t2n(Qp), t2n(Kp), t2n(V.float()), causal, scale)).to(torch.bfloat16))
     lib.impl("signed_bundle", lambda W, V, D: n2t(co.signed_bundle(t2n(W), t2n(V), D), torch.int64))
     lib.impl("transpose_packed", lambda packed, rows, cols: n2t(co.transpose_bits(t2n(packed.contiguous()), rows, cols), torch.int64))
     lib.impl("flip_packed", lambda packed, n: n2t(co.flip_bits(t2n(packed.contiguous()), n), torch.int64))

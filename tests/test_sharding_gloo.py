@@ -1,4 +1,4 @@
-"""The multi-rank layout of the column-sharded GEMM on two CPU ranks (gloo).
+"""The multi-rank layout of the column-sharded GEMM and of the head-sharded attention on two CPU ranks (gloo).
 
 Checks the partition of B's rows, the local GEMM per rank and the layout of the
 optional all-gather against the unsharded result. The CPU ranks use the oracle
@@ -40,6 +40,41 @@ def _worker(rank, world, port, n_rows, result_dir):
     np.save(os.path.join(result_dir, f"ok{rank}.npy"), np.array([lo, hi]))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _attention_worker(rank, world, port, heads, result_dir):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import conftest
+    conftest.install_oracle_cpu_ops()
+    import brute_b200 as brute
+    from brute_b200.kernels import shard_bounds, sharded_attention
+    g = torch.Generator().manual_seed(99)                   # same operands on every rank
+    B, H, S, D = 1, heads, 40, 64
+    q = brute.pack_sign(torch.randn((B, H, S, D), generator=g), ge0=True)
+    k = brute.pack_sign(torch.randn((B, H, S, D), generator=g), ge0=True)
+    v = torch.randn((B, H, S, D), generator=g).to(torch.bfloat16)
+    full = brute.binary_attention(q, k, v, causal=True)
+    lo, hi = shard_bounds(B * H, world, rank)
+    local = sharded_attention(q, k, v, causal=True)
+    assert local.shape == (hi - lo, S, D)
+    assert torch.equal(local, full.reshape(B * H, S, D)[lo:hi])
+    gathered = sharded_attention(q, k, v, causal=True, gather=True)
+    assert torch.equal(gathered, full)
+    np.save(os.path.join(result_dir, f"att{rank}.npy"), np.array([lo, hi]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("heads", [4, 3])
+def test_two_rank_sharded_attention(tmp_path, lib_built, heads):
+    port = 30500 + (os.getpid() % 1000) + heads
+    mp.spawn(_attention_worker, args=(2, port, heads, str(tmp_path)), nprocs=2, join=True)
+    spans = [np.load(tmp_path / f"att{r}.npy") for r in range(2)]
+    assert spans[0][0] == 0 and spans[0][1] == spans[1][0] and spans[1][1] == heads
 
 
 @pytest.mark.parametrize("n_rows", [16, 13])
