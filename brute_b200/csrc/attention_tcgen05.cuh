@@ -44,8 +44,7 @@ constexpr int AX_COL_S = 0 /* two buffers of 64 */, AX_COL_O = 128, AX_TMEM_COLS
 constexpr int AX_Q_TILE = AX_BM * AX_D;                    // int8 [128 rows][128 d] = 16 KB
 constexpr int AX_OFF_KE = AX_NV * AX_V_STAGE;              // 48 KB
 constexpr int AX_OFF_Q = AX_OFF_KE + 2 * AX_KE_TILE;       // 64 KB
-constexpr int AX_OFF_T = AX_OFF_Q + AX_Q_TILE;             // 80 KB
-constexpr int AX_OFF_L = AX_OFF_T + 1024;                  // row-sum parts [2][128] floats
+constexpr int AX_OFF_L = AX_OFF_Q + AX_Q_TILE;             // 80 KB: row-sum parts [2][128] floats
 constexpr int AX_OFF_BARS = AX_OFF_L + 1024;
 constexpr int AX_SMEM = AX_OFF_BARS + 256 + 1024;          // + alignment slack
 
@@ -70,6 +69,17 @@ __device__ __forceinline__ uint64_t ax_v_desc(uint32_t saddr) {
 __device__ __forceinline__ uint32_t ax_enc_q(uint32_t h, int j) { return 0xFFFFFFFFu ^ (((h >> j) & 0x01010101u) * 0xFEu); }
 __device__ __forceinline__ uint32_t ax_enc_k(uint32_t h, int j) { return 0x02020202u ^ (((h >> j) & 0x01010101u) * 0xFCu); }
 
+// acc (two packed fp32) += {p0, p1}: one instruction on sm_100
+__device__ __forceinline__ void ax_add2(uint64_t& acc, float p0, float p1) {
+    asm("{\n\t.reg .b64 t;\n\tmov.b64 t, {%1, %2};\n\tadd.rn.f32x2 %0, %0, t;\n\t}" : "+l"(acc) : "f"(p0), "f"(p1));
+}
+__device__ __forceinline__ float ax_sum4(uint64_t a, uint64_t b) {
+    float a0, a1, b0, b1;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(a));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(b0), "=f"(b1) : "l"(b));
+    return (a0 + a1) + (b0 + b1);
+}
+
 __global__ void __launch_bounds__(AX_THREADS, 2)
 k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                                const uint64_t* __restrict__ Qp, const uint64_t* __restrict__ Kp,
@@ -88,7 +98,8 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     const uint32_t v_ring = base, ke_ring = base + AX_OFF_KE, q_tile = base + AX_OFF_Q, bars = base + AX_OFF_BARS;
     uint8_t* gke = gbase + AX_OFF_KE;
     uint8_t* gq = gbase + AX_OFF_Q;
-    float* T = reinterpret_cast<float*>(gbase + AX_OFF_T);
+    // static, so that its address is a constant that folds into the lookups' load offsets
+    __shared__ __align__(16) float T[AX_D + 4];
     float* l_part = reinterpret_cast<float*>(gbase + AX_OFF_L);
     uint8_t* gbars = gbase + AX_OFF_BARS;
     auto v_full   = [&](int s) { return bars + 8u * s; };
@@ -260,7 +271,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             if (lane == 0) mbar_arrive(q_full);
         }
         const uint32_t tc_addr = (uint32_t)__cvta_generic_to_shared(T) + 2 * AX_D;      // acc = 4*h - 2*D -> T[h]
-        float l = 0.f;
+        uint64_t l2a = 0, l2b = 0;                                  // two packed pairs of fp32 partial row sums
         bool ok = true;
         for (int32_t j = 0; j < ntiles && ok; ++j) {
             const int64_t k0 = (int64_t)j * AX_BN + 32 * grp;       // first key of this thread's 32
@@ -273,18 +284,33 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             uint32_t sc[32], pk[16];
             tc_ld32(my_cols, sc);
             tc_wait_ld();
+            if (!need_mask) {
+                // the common tile: nothing but 2 loads, 1 packed add and 1 byte permute per pair of
+                // scores, with no branch between the 32 loads
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float p0, p1;
-                asm("ld.shared.f32 %0, [%1];" : "=f"(p0) : "r"(tc_addr + sc[i]));
-                asm("ld.shared.f32 %0, [%1];" : "=f"(p1) : "r"(tc_addr + sc[i + 1]));
-                if (need_mask) {
-                    if (k0 + i >= S || (causal && k0 + i > row)) p0 = 0.f;
-                    if (k0 + i + 1 >= S || (causal && k0 + i + 1 > row)) p1 = 0.f;
+                for (int i = 0; i < 32; i += 2) {
+                    float p0, p1;
+                    asm("ld.shared.f32 %0, [%1];" : "=f"(p0) : "r"(tc_addr + sc[i]));
+                    asm("ld.shared.f32 %0, [%1];" : "=f"(p1) : "r"(tc_addr + sc[i + 1]));
+                    ax_add2(i & 2 ? l2b : l2a, p0, p1);
+                    // entries are bf16-exact: the pair is the two upper halves
+                    pk[i >> 1] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
                 }
-                l += p0 + p1;
-                // entries are bf16-exact: the pair is the two upper halves
-                pk[i >> 1] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
+            } else {
+                // keys [k0, k0 + lim) of this thread's 32 are inside the sequence and not above the diagonal
+                int64_t a = S - k0;
+                if (causal && row - k0 + 1 < a) a = row - k0 + 1;
+                const int lim = a < 0 ? 0 : (a > 32 ? 32 : (int)a);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0, p1;
+                    asm("ld.shared.f32 %0, [%1];" : "=f"(p0) : "r"(tc_addr + sc[i]));
+                    asm("ld.shared.f32 %0, [%1];" : "=f"(p1) : "r"(tc_addr + sc[i + 1]));
+                    p0 = i < lim ? p0 : 0.f;
+                    p1 = i + 1 < lim ? p1 : 0.f;
+                    ax_add2(i & 2 ? l2b : l2a, p0, p1);
+                    pk[i >> 1] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
+                }
             }
             // over the first 16 of the 32 columns this thread has just read
             tc_st16(my_cols, pk);
@@ -295,7 +321,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(o_full, 0, abort_flag, 20));
         // the two halves of a row exchange their sums; one verdict for all softmax warps first
-        l_part[grp * AX_BM + r] = l;
+        l_part[grp * AX_BM + r] = ax_sum4(l2a, l2b);
         uint32_t bad;
         asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
                      : "=r"(bad) : "r"((uint32_t)(!ok)), "n"(AX_SOFTMAX_WARPS * 32) : "memory");
