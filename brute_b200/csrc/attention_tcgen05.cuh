@@ -24,7 +24,7 @@
 // so two CTAs share an SM.
 //   warp 0      TMA producer for V (3-deep ring).
 //   warp 1      MMA issuer, TMEM owner.
-//   warps 2-3   K expanders (double-buffered int8 tile).
+//   warps 2-3   K expanders (int8 tiles, three in flight; packed words prefetched four tiles ahead).
 //   warps 4-11  softmax, then the epilogue (tcgen05.ld of O, 1/l, bf16, 16-byte stores): warps w and
 //               w + 4 share a TMEM lane quarter and split the key (then the output) columns.
 // Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag and the device
@@ -36,15 +36,16 @@ namespace bb {
 
 constexpr int AX_BM = 128, AX_BN = 64, AX_D = 128, AX_THREADS = 384;
 constexpr int AX_SOFTMAX_WARPS = 8;
-constexpr int AX_NV = 3;                                   // V stages
+constexpr int AX_NV = 4;                                   // V stages (a power of two)
 constexpr int AX_V_HALF = AX_BN * 128;                     // [64 keys][64 d] bf16 = 8 KB
 constexpr int AX_V_STAGE = 2 * AX_V_HALF;                  // 16 KB
 constexpr int AX_KE_TILE = AX_BN * AX_D;                   // int8 [64 keys][128 d] = 8 KB
+constexpr int AX_NK = 3;                                   // expanded K tiles in flight
 constexpr int AX_COL_S = 0 /* two buffers of 64 */, AX_COL_O = 128, AX_TMEM_COLS = 256;
 constexpr int AX_Q_TILE = AX_BM * AX_D;                    // int8 [128 rows][128 d] = 16 KB
-constexpr int AX_OFF_KE = AX_NV * AX_V_STAGE;              // 48 KB
-constexpr int AX_OFF_Q = AX_OFF_KE + 2 * AX_KE_TILE;       // 64 KB
-constexpr int AX_OFF_L = AX_OFF_Q + AX_Q_TILE;             // 80 KB: row-sum parts [2][128] floats
+constexpr int AX_OFF_KE = AX_NV * AX_V_STAGE;              // 64 KB
+constexpr int AX_OFF_Q = AX_OFF_KE + AX_NK * AX_KE_TILE;   // 88 KB
+constexpr int AX_OFF_L = AX_OFF_Q + AX_Q_TILE;             // 104 KB: row-sum parts [2][128] floats
 constexpr int AX_OFF_BARS = AX_OFF_L + 1024;
 constexpr int AX_SMEM = AX_OFF_BARS + 256 + 1024;          // + alignment slack
 
@@ -105,15 +106,18 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     auto v_full   = [&](int s) { return bars + 8u * s; };
     auto v_empty  = [&](int s) { return bars + 8u * (AX_NV + s); };
     auto ke_full  = [&](int s) { return bars + 8u * (2 * AX_NV + s); };
-    auto ke_empty = [&](int s) { return bars + 8u * (2 * AX_NV + 2 + s); };
-    const uint32_t s_full0 = bars + 8u * (2 * AX_NV + 4), p_full0 = s_full0 + 16u;      // [2] each, by S/P buffer
+    auto ke_empty = [&](int s) { return bars + 8u * (2 * AX_NV + AX_NK + s); };
+    const uint32_t s_full0 = bars + 8u * (2 * AX_NV + 2 * AX_NK), p_full0 = s_full0 + 16u;      // [2] each, by S/P buffer
     auto s_full = [&](int b) { return s_full0 + 8u * b; };
     auto p_full = [&](int b) { return p_full0 + 8u * b; };
     const uint32_t q_full = s_full0 + 32u, o_full = s_full0 + 40u, drain_bar = s_full0 + 48u;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (2 * AX_NV + 4 + 7));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (2 * AX_NV + 4 + 7) + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (2 * AX_NV + 2 * AX_NK + 7));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (2 * AX_NV + 2 * AX_NK + 7) + 4);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // through a shuffle so that the compiler knows the warp index, and with it every role branch
+    // below, to be the same for all lanes of a warp
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int64_t qt = q_tiles - 1 - (int64_t)blockIdx.x;          // heavy (late) causal tiles first
     const int64_t bh = blockIdx.y;
     const int64_t q0 = qt * AX_BM;
@@ -124,7 +128,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     if (tid <= AX_D) T[tid] = __bfloat162float(__float2bfloat16_rn(exp2f(neg2c_log2 * (float)tid - bias_log2)));
     if (tid == 0) {
         for (int s = 0; s < AX_NV; ++s) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(ke_full(s), 2); mbar_init(ke_empty(s), 1); }
+        for (int s = 0; s < AX_NK; ++s) { mbar_init(ke_full(s), 2); mbar_init(ke_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(s_full(b), 1); mbar_init(p_full(b), AX_SOFTMAX_WARPS); }
         mbar_init(q_full, AX_SOFTMAX_WARPS); mbar_init(o_full, 1); mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -147,7 +151,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             bool ok = true;
             int32_t issued = 0;
             for (int32_t j = 0; j < ntiles && ok; ++j) {
-                const int s = j % AX_NV;
+                const int s = j & (AX_NV - 1);
                 ok = mbar_wait_relaxed(v_empty(s), ((j / AX_NV) & 1) ^ 1, abort_flag, 11);
                 if (!ok) break;
                 mbar_expect_tx(v_full(s), AX_V_STAGE);
@@ -165,87 +169,118 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        if (lane == 0) {
-            bool ok = mbar_wait(q_full, 0, abort_flag, 12);
-            const uint64_t qdesc = tc_smem_desc(q_tile);
-            auto issue_qk = [&](int32_t j) -> bool {
-                // Writes S buffer j % 2. Its last reader is the P.V MMA of tile j - 2, issued before
-                // this one, and the tensor pipe runs in issue order.
-                const int b = j & 1;
-                if (!mbar_wait(ke_full(b), (j >> 1) & 1, abort_flag, 13)) return false;
-                tc_fence_after();
-                const uint64_t kdesc = tc_smem_desc(ke_ring + b * AX_KE_TILE);
+        // The whole warp runs this loop convergently and one elected lane issues: descriptors,
+        // addresses and loop state are then warp-uniform values, which the tcgen05 instructions take
+        // as they are. Issued from inside an `if (lane == 0)` branch every operand first has to be
+        // moved out of that one thread's registers, and each MMA took 70-100 clocks to issue - more
+        // than the 32-64 clocks it runs.
+        bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, abort_flag, 12));
+        const uint64_t qdesc = tc_smem_desc(q_tile);
+        const uint64_t kdesc0 = tc_smem_desc(ke_ring), vdesc0 = ax_v_desc(v_ring);
+        // score MMA of tile j into S buffer j % 2. The buffer's last reader is the P.V MMA of tile
+        // j - 2, issued before this one, and the tensor pipe runs in issue order.
+        int kq = 0;                                  // K buffer of the next score MMA: tile % AX_NK
+        auto issue_qk = [&](int b) {
+            if (tc_elect_one()) {
+                const uint64_t kdesc = kdesc0 + (uint64_t)(kq * (AX_KE_TILE >> 4));
 #pragma unroll
                 for (int k = 0; k < 4; ++k)      // 32 bytes of d per instruction
                     tc_mma_i8_ss(tmem + (uint32_t)(AX_COL_S + 64 * b), qdesc + 2u * k, kdesc + 2u * k, AX_IDESC_QK, k > 0 ? 1u : 0u);
                 tc_commit(s_full(b));
-                tc_commit(ke_empty(b));
-                return true;
-            };
-            auto issue_pv = [&](int32_t j) -> bool {
-                const int s = j % AX_NV, b = j & 1;
-                if (!mbar_wait(v_full(s), (j / AX_NV) & 1, abort_flag, 15)) return false;
-                if (!mbar_wait(p_full(b), (j >> 1) & 1, abort_flag, 16)) return false;
-                tc_fence_after();
-                const uint64_t vdesc = ax_v_desc(v_ring + s * AX_V_STAGE);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {    // 16 keys per instruction = two 1024-byte atoms of V
-                    // P of keys [16k, 16k+16): 8 columns, inside the S columns of the thread that wrote them
-                    const uint32_t pcol = (uint32_t)(AX_COL_S + 64 * b + 32 * (k >> 1) + 8 * (k & 1));
-                    tc_mma_f16_ts(tmem + AX_COL_O, tmem + pcol, vdesc + (uint64_t)(128u * k), AX_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
-                }
-                tc_commit(v_empty(s));
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
-            if (ok && ntiles > 1) ok = issue_qk(1);
-            for (int32_t j = 0; j < ntiles && ok; ++j) {
-                ok = issue_pv(j);
-                if (ok && j + 2 < ntiles) ok = issue_qk(j + 2);
+                tc_commit(ke_empty(kq));
             }
+            __syncwarp();
+            if (++kq == AX_NK) kq = 0;
+        };
+        // The prologue waits for the first two expanded K tiles itself. In the loop this warp waits
+        // for ONE barrier per tile, p_full: two of the softmax warps check that V tile j and K tile
+        // j + 2 have landed before they arrive on it (they have the slack; every wait, fence and
+        // commit here is on the serial path that feeds the tensor pipe).
+        for (int t = 0; t < 2 && t < ntiles && ok; ++t) {
+            ok = __all_sync(0xffffffffu, mbar_wait(ke_full(t), 0, abort_flag, 13));
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t);
+        }
+        for (int32_t j0 = 0; j0 < ntiles && ok; j0 += AX_NV) {
+#pragma unroll
+            for (int u = 0; u < AX_NV; ++u) {            // u = V stage; S/P buffer b = u % 2: both static
+                const int32_t j = j0 + u;
+                if (j >= ntiles || !ok) break;
+                const int b = u & 1;
+                ok = __all_sync(0xffffffffu, mbar_wait(p_full(b), (j >> 1) & 1, abort_flag, 16));
+                if (!ok) break;
+                tc_fence_after();
+                if (tc_elect_one()) {
+                    const uint64_t vdesc = vdesc0 + (uint64_t)(u * (AX_V_STAGE >> 4));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {    // 16 keys per instruction = two 1024-byte atoms of V
+                        // P of keys [16k, 16k+16): 8 columns, inside the S columns of the thread that wrote them
+                        const uint32_t pcol = (uint32_t)(AX_COL_S + 64 * b + 32 * (k >> 1) + 8 * (k & 1));
+                        tc_mma_f16_ts(tmem + AX_COL_O, tmem + pcol, vdesc + (uint64_t)(128u * k), AX_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(v_empty(u));
+                }
+                __syncwarp();
+                if (j + 2 < ntiles) issue_qk(b);
+            }
+        }
+        if (lane == 0) {
             if (ok) tc_commit(o_full);
             tc_commit(drain_bar);
             const uint64_t t0 = tc_globaltimer();
             while (!mbar_try(drain_bar, 0) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
         }
+        __syncwarp();
     } else if (warp < 4) {
         // ================= K expanders: packed bits -> int8 tile, K-major SWIZZLE_128B =================
         const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Kp + bh * S * 2);
         const int half = warp - 2;                        // keys [32 half, 32 half + 32) of the tile
         // lane -> (key, word): 128 words per half tile, 4 per lane, coalesced
-        uint32_t cur[4];
+        // The packed words are fetched AX_KPF tiles ahead into a ring of registers: one tile ahead left
+        // the load latency (L2, under load) on the path and made this role the slowest of the CTA.
+        constexpr int AX_KPF = 4;
+        uint32_t ring[AX_KPF][4];
         auto load_tile = [&](int32_t j, uint32_t (&w)[4]) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int idx = lane + 32 * i;            // 0..127
                 const int64_t key = (int64_t)j * AX_BN + 32 * half + (idx >> 2);
-                w[i] = key < S ? __ldg(Kw + key * 4 + (idx & 3)) : 0u;
+                w[i] = (j < ntiles && key < S) ? __ldg(Kw + key * 4 + (idx & 3)) : 0u;
             }
         };
-        load_tile(0, cur);
+#pragma unroll
+        for (int u = 0; u < AX_KPF - 1; ++u) load_tile(u, ring[u]);
         bool ok = true;
-        for (int32_t j = 0; j < ntiles && ok; ++j) {
-            const int b = j & 1;
-            uint32_t nxt[4] = {0u, 0u, 0u, 0u};
-            if (j + 1 < ntiles) load_tile(j + 1, nxt);
-            ok = __all_sync(0xffffffffu, mbar_wait_relaxed(ke_empty(b), ((j >> 1) & 1) ^ 1, abort_flag, 17));
-            if (!ok) break;
+        int kb = 0;                                       // K buffer of tile j, j % AX_NK, and its phase
+        uint32_t kbp = 0;
+        for (int32_t j0 = 0; j0 < ntiles && ok; j0 += AX_KPF) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int idx = lane + 32 * i;
-                const int key = 32 * half + (idx >> 2), w = idx & 3;
-                uint8_t* row = gke + b * AX_KE_TILE + key * 128;
-                const int sw = key & 7;
-                *reinterpret_cast<uint4*>(row + (((2 * w) ^ sw) << 4)) =
-                    make_uint4(ax_enc_k(cur[i], 0), ax_enc_k(cur[i], 1), ax_enc_k(cur[i], 2), ax_enc_k(cur[i], 3));
-                *reinterpret_cast<uint4*>(row + (((2 * w + 1) ^ sw) << 4)) =
-                    make_uint4(ax_enc_k(cur[i], 4), ax_enc_k(cur[i], 5), ax_enc_k(cur[i], 6), ax_enc_k(cur[i], 7));
+            for (int u = 0; u < AX_KPF; ++u) {            // ring slots are static register names
+                const int32_t j = j0 + u;
+                if (j >= ntiles || !ok) break;
+                load_tile(j + AX_KPF - 1, ring[(u + AX_KPF - 1) % AX_KPF]);
+                // K buffer kb is free once the score MMA of tile j - AX_NK has completed. (A barrier of its
+                // own: s_full of that tile may already be a phase further, which a parity wait cannot tell.)
+                ok = __all_sync(0xffffffffu, mbar_wait_relaxed(ke_empty(kb), kbp ^ 1u, abort_flag, 17));
+                if (!ok) break;
+                const uint32_t (&cur)[4] = ring[u];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int idx = lane + 32 * i;
+                    const int key = 32 * half + (idx >> 2), w = idx & 3;
+                    uint8_t* row = gke + kb * AX_KE_TILE + key * 128;
+                    const int sw = key & 7;
+                    *reinterpret_cast<uint4*>(row + (((2 * w) ^ sw) << 4)) =
+                        make_uint4(ax_enc_k(cur[i], 0), ax_enc_k(cur[i], 1), ax_enc_k(cur[i], 2), ax_enc_k(cur[i], 3));
+                    *reinterpret_cast<uint4*>(row + (((2 * w + 1) ^ sw) << 4)) =
+                        make_uint4(ax_enc_k(cur[i], 4), ax_enc_k(cur[i], 5), ax_enc_k(cur[i], 6), ax_enc_k(cur[i], 7));
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(ke_full(kb));
+                if (++kb == AX_NK) { kb = 0; kbp ^= 1u; }
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(ke_full(b));
-#pragma unroll
-            for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
         }
     } else {
         // ================= softmax (two threads per query row = TMEM lane), then epilogue =================
@@ -271,6 +306,8 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             if (lane == 0) mbar_arrive(q_full);
         }
         const uint32_t tc_addr = (uint32_t)__cvta_generic_to_shared(T) + 2 * AX_D;      // acc = 4*h - 2*D -> T[h]
+        int kx = 2 % AX_NK;                                        // K buffer and phase of tile j + 2
+        uint32_t kxp = 2 / AX_NK;
         uint64_t l2a = 0, l2b = 0;                                  // two packed pairs of fp32 partial row sums
         bool ok = true;
         for (int32_t j = 0; j < ntiles && ok; ++j) {
@@ -316,6 +353,12 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             tc_st16(my_cols, pk);
             tc_wait_st();
             tc_fence_before();
+            // on behalf of the MMA warp, which waits for p_full alone: V tile j and the expanded K
+            // tile j + 2 (the operands of the two MMA groups it issues next) have landed
+            if (warp == 4) ok = __all_sync(0xffffffffu, mbar_wait(v_full(j & (AX_NV - 1)), (j / AX_NV) & 1, abort_flag, 15));
+            if (warp == 5 && j + 2 < ntiles) ok = __all_sync(0xffffffffu, mbar_wait(ke_full(kx), kxp, abort_flag, 13));
+            if (++kx == AX_NK) { kx = 0; kxp ^= 1u; }
+            if (!ok) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full(b));
         }
