@@ -242,7 +242,8 @@ k_xnor_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int* pb_pair = pb_part + 2 * 4 * TP_BNH;                         // [2][256]
     const uint32_t pb_pair_addr = bars + 256u + 4u * (2 * 4 * TP_BM + 2 * 4 * TP_BNH);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // a shuffle result: known to the compiler as the same in all lanes
     const uint32_t rank = cluster_ctarank(), peer = rank ^ 1u;
     const int32_t pair_id = (int32_t)cluster_id_x(), npairs = (int32_t)cluster_count_x();
     const int32_t nst = (nkb + TC_KB_PER_STAGE - 1) / TC_KB_PER_STAGE;     // packed stages per tile; K tails are zero filled

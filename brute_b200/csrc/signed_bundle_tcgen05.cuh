@@ -76,7 +76,8 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (NB + 2));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (NB + 2) + 4);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // a shuffle result: known to the compiler as the same in all lanes
     const int64_t m0 = (int64_t)blockIdx.x * ST_BM;
     const int64_t d0 = (int64_t)blockIdx.y * ST_DB;
     const int64_t b = blockIdx.z;
