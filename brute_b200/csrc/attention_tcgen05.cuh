@@ -22,8 +22,9 @@
 //
 // CTA = 128 query rows of one (batch, head); 384 threads; 256 TMEM columns (S/P 2 x 64, O 128),
 // so two CTAs share an SM.
-//   warp 0      TMA producer for V (3-deep ring).
-//   warp 1      MMA issuer, TMEM owner.
+//   warp 0      TMA producer for V (4-deep ring).
+//   warp 1      MMA issuer (convergent, one elected lane), TMEM owner; waits on p_full only: softmax
+//               warps 4 and 5 check v_full / ke_full on its behalf before they arrive.
 //   warps 2-3   K expanders (int8 tiles, three in flight; packed words prefetched four tiles ahead).
 //   warps 4-11  softmax, then the epilogue (tcgen05.ld of O, 1/l, bf16, 16-byte stores): warps w and
 //               w + 4 share a TMEM lane quarter and split the key (then the output) columns.
