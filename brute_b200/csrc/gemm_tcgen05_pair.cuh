@@ -51,7 +51,7 @@ constexpr int TP_E_TILE = TP_BNH * 128;                  // expanded half of B o
 constexpr int TP_E_SLOT = 2 * TP_E_TILE;                 // 32 KB
 constexpr int TP_A_SLOT_COLS = 2 * TC_A_COLS;            // 64 TMEM columns per slot
 constexpr int TP_NBARS = 2 * TP_PSTAGES + 2 * TP_ESLOTS + 4;   // + acc_full, acc_empty, pb, drain
-constexpr int TP_ROWPOP_INTS = 2 * 4 * TP_BM + 2 * 4 * TP_BNH + 2 * TP_BN;   // pa parts, pb parts, pb of the pair
+constexpr int TP_ROWPOP_INTS = 2 * 4 * TP_BM + 2 * 4 * TP_BNH + 4 * TP_BN;   // pa parts, pb parts, pb of the pair, column signs
 constexpr int TP_SMEM = TP_ESLOTS * TP_E_SLOT + TP_PSTAGES * TP_P_STAGE + 256 + 4 * TP_ROWPOP_INTS + 1024;
 static_assert(TC_ACC_COLS + TP_ESLOTS * TP_A_SLOT_COLS <= TC_TMEM_COLS, "A ring must fit beside the accumulator");
 static_assert(TP_ESLOTS * TP_E_SLOT == TP_BM * TP_BN * 4, "the expanded ring doubles as the staging area of one C tile");
@@ -240,6 +240,7 @@ k_xnor_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int* pa_part = reinterpret_cast<int*>(gbars + 256);              // [2][4][128]
     int* pb_part = pa_part + 2 * 4 * TP_BM;                          // [2][4][128] (this CTA's half of B)
     int* pb_pair = pb_part + 2 * 4 * TP_BNH;                         // [2][256]
+    int* col_s = pb_pair + 2 * TP_BN;                                // [2][256] (fused epilogue only)
     const uint32_t pb_pair_addr = bars + 256u + 4u * (2 * 4 * TP_BM + 2 * 4 * TP_BNH);
 
     const int tid = threadIdx.x, lane = tid & 31;
@@ -376,8 +377,30 @@ k_xnor_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_c
             asm volatile("bar.sync 1, %0;" :: "n"(TC_EXP_WARPS * 32) : "memory");
             if (tid < TP_BNH) {
                 const int* pp = pb_part + par * 4 * TP_BNH + tid;
-                const int v = pp[0] + pp[TP_BNH] + pp[2 * TP_BNH] + pp[3 * TP_BNH];
                 const uint32_t idx = par * TP_BN + rank * TP_BNH + (uint32_t)tid;
+                int v = pp[0] + pp[TP_BNH] + pp[2 * TP_BNH] + pp[3 * TP_BNH];
+                if (STORE == 2) {
+                    // sign(scale * C) without a float per element: bit = (s * C + off >= 0), with
+                    //   finite scale > 0: s = 1,  off = 0 (>= 0) or -1 (> 0);   scale < 0: s = -1, same off
+                    //   scale = +-0: the product is +-0: s = 0, off = 0 (>= 0 holds) or -1 (> 0 does not)
+                    //   scale = +-inf: 0 * inf is NaN, which compares false: s = +-1, off = -1 in both modes
+                    //   NaN, and columns past N: s = 0, off = -1 (bit 0)
+                    // The column's popcount goes into the offset: u = off - 2 * s * pb.
+                    const int64_t n = n0 + (int64_t)rank * TP_BNH + tid;
+                    int sg = 0, off = -1;
+                    if (n < N) {
+                        const float sc = __ldg(scale + n);
+                        const bool ge0 = mode == BRUTE_SIGN_GE0;
+                        if (sc == 0.0f) off = ge0 ? 0 : -1;
+                        else if (sc > 0.0f || sc < 0.0f) {
+                            sg = sc > 0.0f ? 1 : -1;
+                            off = (ge0 && fabsf(sc) <= 3.402823466e38f) ? 0 : -1;
+                        }
+                    }
+                    asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(mapa_shared(pb_pair_addr + 4u * (2 * TP_BN + idx), peer)), "r"(sg) : "memory");
+                    col_s[idx] = sg;
+                    v = off - 2 * sg * v;
+                }
                 pb_pair[idx] = v;
                 asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(mapa_shared(pb_pair_addr + 4u * idx, peer)), "r"(v) : "memory");
             }
@@ -403,9 +426,11 @@ k_xnor_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(acc_empty_leader);
                 }
+                if (STORE != 2) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    v[j] = (uint32_t)(row_term - 2 * pbp[col + j] + 4 * (int32_t)(v[j] >> 7));
+                    for (int j = 0; j < 32; ++j)
+                        v[j] = (uint32_t)(row_term - 2 * pbp[col + j] + 4 * (int32_t)(v[j] >> 7));
+                }
                 const int64_t n = n0 + col;
                 if (STORE == 0) {
                     // box (2*cblock + cc): [128 rows][32 ints], 128-byte rows, 16-byte chunks XOR (row & 7)
@@ -426,18 +451,36 @@ k_xnor_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_c
                         }
                     }
                 } else {
+                    // bit j = (s_j * C + off_j >= 0), C = row_term - 2 pb_j + 4 a: integer only
+                    const int* csp = col_s + par * TP_BN + col;
                     uint32_t bits = 0;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        if (n + j < N) {
-                            const float y = __ldg(scale + n + j) * (float)(int32_t)v[j];
-                            const bool b = mode == BRUTE_SIGN_GE0 ? (y >= 0.0f) : (y > 0.0f);
-                            bits |= (b ? 1u : 0u) << j;
+                        const int32_t t = csp[j] * (row_term + 4 * (int32_t)(v[j] >> 7)) + pbp[col + j];
+                        bits = (bits >> 1) | (~(uint32_t)t & 0x80000000u);
+                    }
+                    // [128 rows][8 words] of this CTA's 256 columns: a row is one 32-byte sector
+                    reinterpret_cast<uint32_t*>(gbase)[prow * 8 + 2 * cblock + cc] = bits;
+                }
+            }
+            if (STORE == 2) {
+                asm volatile("bar.sync 1, %0;" :: "n"(TC_EXP_WARPS * 32) : "memory");
+                if (tid < 2 * TP_BM) {
+                    const int r = tid >> 1, h = tid & 1;
+                    const int64_t mr = m0 + r, w0 = (n0 >> 5) + 4 * h;        // first of this thread's 4 words
+                    if (mr < M && w0 < halves_per_row) {
+                        const uint4 q = reinterpret_cast<const uint4*>(gbase)[tid];
+                        uint32_t* dst = out32 + mr * halves_per_row + w0;
+                        if (w0 + 4 <= halves_per_row && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                            *reinterpret_cast<uint4*>(dst) = q;
+                        } else {
+                            const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+                            for (int i = 0; i < 4 && w0 + i < halves_per_row; ++i) dst[i] = qq[i];
                         }
                     }
-                    const int64_t hidx = n >> 5;
-                    if (m < M && hidx < halves_per_row) out32[m * halves_per_row + hidx] = bits;
                 }
+                // the staging words are rewritten by the next tile's epilogue, after its own barriers
+                asm volatile("bar.sync 1, %0;" :: "n"(TC_EXP_WARPS * 32) : "memory");
             }
             if (STORE == 0) {
                 // staged tile -> global: one box per warp 0..7, issued once every warp has written

@@ -379,6 +379,36 @@ def test_mlp_layer(ops, co, impl_name, mode):
     assert np.array_equal(u64(ops.xnor_matmul_scale_sign_pack(ap, wp, scale.to(DEV), K, mode)), want)
 
 
+@pytest.mark.parametrize("impl_name", ["popc", "tcgen05", "tcgen05_pair"])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_mlp_layer_special_scales(ops, co, impl_name, mode):
+    # sign(scale * C) for every kind of scale: the pair kernel decides it in integers (a sign and an
+    # offset per column), the others multiply; both must give what the float product gives, also where
+    # C = 0 (0 * inf is NaN and compares false) and for zero, negative, denormal and NaN scales
+    from brute_b200 import _lib as L
+    M, K, N = 300, 256, 520
+    a = torch.randint(0, 2, (M, K), generator=gen(21)).bool()
+    w = torch.randint(0, 2, (N, K), generator=gen(22)).bool()
+    w[:16] = a[:16]
+    w[:16, : K // 2] ^= True                       # rows 0..15 of A against columns 0..15: C = 0
+    specials = torch.tensor([0.0, -0.0, float("inf"), float("-inf"), float("nan"), 1e-42, -1e-42, -2.5,
+                             3.0e38, -3.0e38, 1.0, -1.0], dtype=torch.float32)
+    scale = torch.rand(N, generator=gen(23)) - 0.5
+    for i in range(N):
+        if i % 3 != 2:
+            scale[i] = specials[(i // 3 + i) % len(specials)]
+    ap, wp = ops.pack_bool(a.to(DEV)), ops.pack_bool(w.to(DEV))
+    c = co.xnor_gemm(u64(ap), u64(wp), K)
+    assert (c[:16, :16].diagonal() == 0).all()
+    want = co.xnor_gemm_scale_sign_pack(u64(ap), u64(wp), scale.numpy(), K, mode)
+    out = torch.empty((M, (N + 63) // 64), dtype=torch.int64, device=DEV)
+    rc = L.load().brute_b200_xnor_gemm_scale_sign_pack(
+        ap.data_ptr(), wp.data_ptr(), scale.to(DEV).data_ptr(), out.data_ptr(), M, N, K // 64, K, mode,
+        {**impls(), "tcgen05_pair": L.GEMM_TCGEN05_PAIR}[impl_name], torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert np.array_equal(u64(out), want)
+
+
 def test_mlp_config4_chain(ops, co):
     # BASELINE config 4 at reduced batch against the oracle: 4096 -> 16384 -> 4096
     import brute_b200 as brute
