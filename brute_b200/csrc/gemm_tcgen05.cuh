@@ -53,7 +53,7 @@ constexpr int TC_THREADS = (TC_EXP_WARPS + 2) * 32;     // 576
 constexpr int TC_A_COLS = 32;                           // A of one k-block: 128 int8 of K per row = 32 columns of 32 bits
 constexpr int TC_ACC_COLS = 256;
 constexpr int TC_TMEM_COLS = 512;                       // power of two >= 256 + 3 * 32
-constexpr int TC_ROWPOP_BYTES = (TC_BM + TC_BN) * 4;      // pa[128], pb[256] of the tile
+constexpr int TC_ROWPOP_BYTES = (TC_BM + 2 * TC_BN) * 4;  // pa[128], pb[256], column signs[256] of the tile
 constexpr int TC_SMEM = TC_ESTAGES * TC_E_STAGE + TC_PSTAGES * TC_P_STAGE + 256 + TC_ROWPOP_BYTES + 1024;
 // kind::i8, D = s32, A = B = unsigned int8 (format 0), both K-major, M = 128, N = 256
 constexpr uint32_t TC_IDESC = (2u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(TC_BN >> 3) << 17) |
@@ -188,6 +188,7 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     int* pa_s = reinterpret_cast<int*>(gbars + 256);      // set bits per A row of the tile
     int* pb_s = pa_s + TC_BM;                             // set bits per B row of the tile
+    int* cs_s = pb_s + TC_BN;                             // fused epilogue: sign of the column's scale
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // a shuffle result: known to the compiler as the same in all lanes
@@ -289,6 +290,28 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         atomicAdd(pb_s + erow, cx.pc_b0);
         atomicAdd(pb_s + erow + 128, cx.pc_b1);
         asm volatile("bar.sync 1, %0;" :: "n"(TC_EXP_WARPS * 32) : "memory");     // all expander warps, whatever `ok` is
+        if (PACK) {
+            // sign(scale * C) in integers: bit = (s * C + off >= 0). Finite scale > 0: s = 1, off = 0
+            // for ">= 0" or -1 for "> 0"; scale < 0: s = -1; scale = +-0: s = 0, off = 0 / -1 (the
+            // product is +-0); +-inf: off = -1 in both modes (0 * inf is NaN, which compares false);
+            // NaN and columns past N: s = 0, off = -1. pb_s becomes u = off - 2 * s * pb.
+            if (tid < TC_BN) {
+                const int64_t n = n0 + tid;
+                int sg = 0, off = -1;
+                if (n < N) {
+                    const float sc = __ldg(scale + n);
+                    const bool ge0 = mode == BRUTE_SIGN_GE0;
+                    if (sc == 0.0f) off = ge0 ? 0 : -1;
+                    else if (sc > 0.0f || sc < 0.0f) {
+                        sg = sc > 0.0f ? 1 : -1;
+                        off = (ge0 && fabsf(sc) <= 3.402823466e38f) ? 0 : -1;
+                    }
+                }
+                cs_s[tid] = sg;
+                pb_s[tid] = off - 2 * sg * pb_s[tid];
+            }
+            asm volatile("bar.sync 1, %0;" :: "n"(TC_EXP_WARPS * 32) : "memory");
+        }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, 5));
         if (ok) {
             tc_fence_after();
@@ -302,9 +325,11 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 uint32_t v[32];
                 tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col, v);
                 tc_wait_ld();
+                if (!PACK) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    v[j] = (uint32_t)(row_term - 2 * pb_s[col + j] + 4 * (int32_t)(v[j] >> 7));
+                    for (int j = 0; j < 32; ++j)
+                        v[j] = (uint32_t)(row_term - 2 * pb_s[col + j] + 4 * (int32_t)(v[j] >> 7));
+                }
                 const int64_t n = n0 + col;
                 if (!PACK) {
                     if (m < M) {
@@ -322,11 +347,8 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     uint32_t bits = 0;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        if (n + j < N) {
-                            const float y = __ldg(scale + n + j) * (float)(int32_t)v[j];
-                            const bool b = mode == BRUTE_SIGN_GE0 ? (y >= 0.0f) : (y > 0.0f);
-                            bits |= (b ? 1u : 0u) << j;
-                        }
+                        const int32_t t = cs_s[col + j] * (row_term + 4 * (int32_t)(v[j] >> 7)) + pb_s[col + j];
+                        bits = (bits >> 1) | (~(uint32_t)t & 0x80000000u);
                     }
                     const int64_t hidx = n >> 5;
                     if (m < M && hidx < halves_per_row) out32[m * halves_per_row + hidx] = bits;
