@@ -650,12 +650,13 @@ extern "C" int brute_b200_binary_attention_fwd(const uint64_t* Qp, const uint64_
     if (span_log2 <= 100.0f) {
         const float neg2c = -2.0f * scale_log2;
         const float bias = scale_log2 < 0.f ? neg2c * (float)D : 0.f;      // keeps max(T) == 1
-        // BRUTE_ATTENTION_IMPL = tcgen05 (default for D = 128) | mma (mma.sync scores) | popc (CUDA-core scores)
+        // BRUTE_ATTENTION_IMPL = tcgen05 (default) | mma (mma.sync scores) | popc (CUDA-core scores)
         const char* env_impl = std::getenv("BRUTE_ATTENTION_IMPL");     // read per call: tests switch it
         const bool want_popc = env_impl && !std::strcmp(env_impl, "popc");
         const bool want_mma = env_impl && !std::strcmp(env_impl, "mma");
-        if (D == 128 && !want_popc && !want_mma) {
-            const int rc = ax_run(Qp, Kp_, V, O, B * H, S, causal, neg2c, bias, st);
+        if (!want_popc && !want_mma) {
+            const int rc = D == 128 ? ax_run<128>(Qp, Kp_, V, O, B * H, S, causal, neg2c, bias, st)
+                                    : ax_run<64>(Qp, Kp_, V, O, B * H, S, causal, neg2c, bias, st);
             if (rc != BRUTE_ERR_DRIVER) return rc;      // no tensor-map encoder: fall through to mma.sync
         }
         if (want_popc) {

@@ -1,4 +1,5 @@
-// Fused binary attention forward on the 5th-generation tensor cores (D = 128).
+// Fused binary attention forward on the 5th-generation tensor cores (D = 128 or 64; the text
+// below gives the figures for 128).
 //
 // Both contractions run on tcgen05.mma with accumulators in tensor memory:
 //   S = Q.K^T   kind::i8, M128 N64 K32 x 4. Q (+1/-1) is expanded once per CTA and the K tile
@@ -35,15 +36,15 @@
 
 namespace bb {
 
-constexpr int AX_BM = 128, AX_BN = 64, AX_D = 128, AX_THREADS = 384;
+constexpr int AX_BM = 128, AX_BN = 64, AX_DMAX = 128, AX_THREADS = 384;
 constexpr int AX_SOFTMAX_WARPS = 8;
 constexpr int AX_NV = 4;                                   // V stages (a power of two)
 constexpr int AX_V_HALF = AX_BN * 128;                     // [64 keys][64 d] bf16 = 8 KB
 constexpr int AX_V_STAGE = 2 * AX_V_HALF;                  // 16 KB
-constexpr int AX_KE_TILE = AX_BN * AX_D;                   // int8 [64 keys][128 d] = 8 KB
+constexpr int AX_KE_TILE = AX_BN * AX_DMAX;                // int8 [64 keys][128-byte rows] = 8 KB
 constexpr int AX_NK = 3;                                   // expanded K tiles in flight
 constexpr int AX_COL_S = 0 /* two buffers of 64 */, AX_COL_O = 128, AX_TMEM_COLS = 256;
-constexpr int AX_Q_TILE = AX_BM * AX_D;                    // int8 [128 rows][128 d] = 16 KB
+constexpr int AX_Q_TILE = AX_BM * AX_DMAX;                 // int8 [128 rows][128-byte rows] = 16 KB
 constexpr int AX_OFF_KE = AX_NV * AX_V_STAGE;              // 64 KB
 constexpr int AX_OFF_Q = AX_OFF_KE + AX_NK * AX_KE_TILE;   // 88 KB
 constexpr int AX_OFF_L = AX_OFF_Q + AX_Q_TILE;             // 104 KB: row-sum parts [2][128] floats
@@ -52,8 +53,9 @@ constexpr int AX_SMEM = AX_OFF_BARS + 256 + 1024;          // + alignment slack
 
 // kind::i8: D s32, A and B signed int8, K-major both, M 128, N 64
 constexpr uint32_t AX_IDESC_QK = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AX_BN >> 3) << 17) | ((uint32_t)(AX_BM >> 4) << 24);
-// kind::f16: D f32, A and B bf16, A K-major (TMEM), B MN-major, M 128, N 128
-constexpr uint32_t AX_IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AX_D >> 3) << 17) | ((uint32_t)(AX_BM >> 4) << 24);
+// kind::f16: D f32, A and B bf16, A K-major (TMEM), B MN-major, M 128, N = head dim
+template <int D>
+constexpr uint32_t AX_IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(AX_BM >> 4) << 24);
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -82,6 +84,7 @@ __device__ __forceinline__ float ax_sum4(uint64_t a, uint64_t b) {
     return (a0 + a1) + (b0 + b1);
 }
 
+template <int AX_D>      // head dim, 64 or 128. With 64 every operand row keeps its 128-byte pitch and half of it is used.
 __global__ void __launch_bounds__(AX_THREADS, 2)
 k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                                const uint64_t* __restrict__ Qp, const uint64_t* __restrict__ Kp,
@@ -101,7 +104,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     uint8_t* gke = gbase + AX_OFF_KE;
     uint8_t* gq = gbase + AX_OFF_Q;
     // static, so that its address is a constant that folds into the lookups' load offsets
-    __shared__ __align__(16) float T[AX_D + 4];
+    __shared__ __align__(16) float T[AX_DMAX + 4];
     float* l_part = reinterpret_cast<float*>(gbase + AX_OFF_L);
     uint8_t* gbars = gbase + AX_OFF_BARS;
     auto v_full   = [&](int s) { return bars + 8u * s; };
@@ -155,9 +158,9 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                 const int s = j & (AX_NV - 1);
                 ok = mbar_wait_relaxed(v_empty(s), ((j / AX_NV) & 1) ^ 1, abort_flag, 11);
                 if (!ok) break;
-                mbar_expect_tx(v_full(s), AX_V_STAGE);
+                mbar_expect_tx(v_full(s), AX_V_HALF * (AX_D / 64));
                 tma_load_3d(v_ring + s * AX_V_STAGE, &tmV, 0, j * AX_BN, (int32_t)bh, v_full(s));
-                tma_load_3d(v_ring + s * AX_V_STAGE + AX_V_HALF, &tmV, 64, j * AX_BN, (int32_t)bh, v_full(s));
+                if (AX_D == 128) tma_load_3d(v_ring + s * AX_V_STAGE + AX_V_HALF, &tmV, 64, j * AX_BN, (int32_t)bh, v_full(s));
                 issued = j + 1;
             }
             if (!ok) {
@@ -185,7 +188,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             if (tc_elect_one()) {
                 const uint64_t kdesc = kdesc0 + (uint64_t)(kq * (AX_KE_TILE >> 4));
 #pragma unroll
-                for (int k = 0; k < 4; ++k)      // 32 bytes of d per instruction
+                for (int k = 0; k < AX_D / 32; ++k)      // 32 bytes of d per instruction
                     tc_mma_i8_ss(tmem + (uint32_t)(AX_COL_S + 64 * b), qdesc + 2u * k, kdesc + 2u * k, AX_IDESC_QK, k > 0 ? 1u : 0u);
                 tc_commit(s_full(b));
                 tc_commit(ke_empty(kq));
@@ -218,7 +221,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                     for (int k = 0; k < 4; ++k) {    // 16 keys per instruction = two 1024-byte atoms of V
                         // P of keys [16k, 16k+16): 8 columns, inside the S columns of the thread that wrote them
                         const uint32_t pcol = (uint32_t)(AX_COL_S + 64 * b + 32 * (k >> 1) + 8 * (k & 1));
-                        tc_mma_f16_ts(tmem + AX_COL_O, tmem + pcol, vdesc + (uint64_t)(128u * k), AX_IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+                        tc_mma_f16_ts(tmem + AX_COL_O, tmem + pcol, vdesc + (uint64_t)(128u * k), AX_IDESC_PV<AX_D>, (j > 0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(v_empty(u));
                 }
@@ -235,19 +238,20 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         __syncwarp();
     } else if (warp < 4) {
         // ================= K expanders: packed bits -> int8 tile, K-major SWIZZLE_128B =================
-        const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Kp + bh * S * 2);
+        constexpr int WPK = AX_D / 32;                    // 32-bit words per key: 4 or 2
+        const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Kp + bh * S * (AX_D / 64));
         const int half = warp - 2;                        // keys [32 half, 32 half + 32) of the tile
-        // lane -> (key, word): 128 words per half tile, 4 per lane, coalesced
+        // lane -> (key, word): 32 * WPK words per half tile, WPK per lane, coalesced
         // The packed words are fetched AX_KPF tiles ahead into a ring of registers: one tile ahead left
         // the load latency (L2, under load) on the path and made this role the slowest of the CTA.
         constexpr int AX_KPF = 4;
-        uint32_t ring[AX_KPF][4];
-        auto load_tile = [&](int32_t j, uint32_t (&w)[4]) {
+        uint32_t ring[AX_KPF][WPK];
+        auto load_tile = [&](int32_t j, uint32_t (&w)[WPK]) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int idx = lane + 32 * i;            // 0..127
-                const int64_t key = (int64_t)j * AX_BN + 32 * half + (idx >> 2);
-                w[i] = (j < ntiles && key < S) ? __ldg(Kw + key * 4 + (idx & 3)) : 0u;
+            for (int i = 0; i < WPK; ++i) {
+                const int idx = lane + 32 * i;            // 0 .. 32 * WPK - 1
+                const int64_t key = (int64_t)j * AX_BN + 32 * half + idx / WPK;
+                w[i] = (j < ntiles && key < S) ? __ldg(Kw + key * WPK + idx % WPK) : 0u;
             }
         };
 #pragma unroll
@@ -265,11 +269,11 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                 // own: s_full of that tile may already be a phase further, which a parity wait cannot tell.)
                 ok = __all_sync(0xffffffffu, mbar_wait_relaxed(ke_empty(kb), kbp ^ 1u, abort_flag, 17));
                 if (!ok) break;
-                const uint32_t (&cur)[4] = ring[u];
+                const uint32_t (&cur)[WPK] = ring[u];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < WPK; ++i) {
                     const int idx = lane + 32 * i;
-                    const int key = 32 * half + (idx >> 2), w = idx & 3;
+                    const int key = 32 * half + idx / WPK, w = idx % WPK;
                     uint8_t* row = gke + kb * AX_KE_TILE + key * 128;
                     const int sw = key & 7;
                     *reinterpret_cast<uint4*>(row + (((2 * w) ^ sw) << 4)) =
@@ -290,13 +294,15 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         const int64_t row = q0 + r;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         {
-            // Q row: this thread's 64 bits -> 64 int8 = chunks 4 grp .. 4 grp + 3 of the 128-byte operand row
-            const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * 2);
+            // Q row: this thread's half of the bits -> int8 chunks of the 128-byte operand row
+            // (D = 128: 64 bits -> chunks 4 grp .. 4 grp + 3; D = 64: 32 bits -> chunks 2 grp, 2 grp + 1)
+            constexpr int QW = AX_D / 64;                 // 32-bit words per thread
+            const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * (AX_D / 64));
             uint8_t* qrow = gq + r * 128;
 #pragma unroll
-            for (int w = 0; w < 2; ++w) {
-                const uint32_t h = row < S ? __ldg(Qw + row * 4 + 2 * grp + w) : 0u;
-                const int ch = 4 * grp + 2 * w;
+            for (int w = 0; w < QW; ++w) {
+                const uint32_t h = row < S ? __ldg(Qw + row * (2 * QW) + QW * grp + w) : 0u;
+                const int ch = 2 * QW * grp + 2 * w;
                 *reinterpret_cast<uint4*>(qrow + ((ch ^ (r & 7)) << 4)) =
                     make_uint4(ax_enc_q(h, 0), ax_enc_q(h, 1), ax_enc_q(h, 2), ax_enc_q(h, 3));
                 *reinterpret_cast<uint4*>(qrow + (((ch + 1) ^ (r & 7)) << 4)) =
@@ -373,11 +379,11 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
             tc_fence_after();
             const float lsum = l_part[r] + l_part[AX_BM + r];
             const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-            __nv_bfloat16* orow = O + (bh * S + row) * AX_D + 64 * grp;      // this thread's 64 of the 128 columns
+            __nv_bfloat16* orow = O + (bh * S + row) * AX_D + (AX_D / 2) * grp;      // this thread's half of the columns
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < AX_D / 64; ++c) {
                 uint32_t v[32];
-                tc_ld32(lane_base + AX_COL_O + 64 * grp + 32 * c, v);
+                tc_ld32(lane_base + AX_COL_O + (AX_D / 2) * grp + 32 * c, v);
                 tc_wait_ld();
                 if (row < S) {
 #pragma unroll
@@ -401,8 +407,8 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     }
 }
 
-// V [BH, S, 128] bf16 as a 3-D tensor, box = [64 d, 64 keys, 1], SWIZZLE_128B: keys past S read as zero
-static bool ax_make_v_map(CUtensorMap* tm, const void* V, int64_t BH, int64_t S) {
+// V [BH, S, D] bf16 as a 3-D tensor, box = [64 d, 64 keys, 1], SWIZZLE_128B: keys past S read as zero
+static bool ax_make_v_map(CUtensorMap* tm, const void* V, int64_t BH, int64_t S, int AX_D) {
     PFN_tmapEncodeTiled enc = tc5_encode_fn();
     if (!enc) return false;
     const cuuint64_t dims[3] = {(cuuint64_t)AX_D, (cuuint64_t)S, (cuuint64_t)BH};
@@ -414,15 +420,16 @@ static bool ax_make_v_map(CUtensorMap* tm, const void* V, int64_t BH, int64_t S)
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <int D>
 static int ax_run(const uint64_t* Qp, const uint64_t* Kp, const void* V, void* O, int64_t BH, int64_t S,
                   int causal, float neg2c_log2, float bias_log2, cudaStream_t st) {
     CUtensorMap tmV;
-    BB_REQUIRE(S < (1ll << 31) - AX_BM && ax_make_v_map(&tmV, V, BH, S), BRUTE_ERR_DRIVER);
-    if (!kernel_smem_ready<k_binary_attention_fwd_tcgen05>(AX_SMEM)) return BRUTE_ERR_LAUNCH;
+    BB_REQUIRE(S < (1ll << 31) - AX_BM && ax_make_v_map(&tmV, V, BH, S, D), BRUTE_ERR_DRIVER);
+    if (!kernel_smem_ready<k_binary_attention_fwd_tcgen05<D>>(AX_SMEM)) return BRUTE_ERR_LAUNCH;
     const int64_t q_tiles = (S + AX_BM - 1) / AX_BM;
     const dim3 grid((unsigned)q_tiles, (unsigned)BH);
-    k_binary_attention_fwd_tcgen05<<<grid, AX_THREADS, AX_SMEM, st>>>(tmV, Qp, Kp, static_cast<__nv_bfloat16*>(O), S, causal,
-                                                                    neg2c_log2, bias_log2, q_tiles);
+    k_binary_attention_fwd_tcgen05<D><<<grid, AX_THREADS, AX_SMEM, st>>>(tmV, Qp, Kp, static_cast<__nv_bfloat16*>(O), S, causal,
+                                                                       neg2c_log2, bias_log2, q_tiles);
     return launch_status();
 }
 

@@ -36,6 +36,7 @@ constexpr int ST_OFF_B = ST_ASTAGES * ST_A_TILE;
 constexpr int ST_OFF_BARS = ST_OFF_B + ST_BSTAGES * ST_B_TILE;
 constexpr int ST_SMEM = ST_OFF_BARS + 256 + 1024;
 static_assert(ST_B_TILE % 1024 == 0, "operand tiles are 1024-byte aligned");
+static_assert(ST_ASTAGES % ST_BSTAGES == 0, "the B ring position is static inside the unrolled A ring");
 
 // kind::i8: D s32, A signed int8, B unsigned int8, K-major both, M 128, N 144
 constexpr uint32_t ST_IDESC = (2u << 4) | (1u << 7) | (0u << 10) | ((uint32_t)(ST_NMMA >> 3) << 17) | ((uint32_t)(ST_BM >> 4) << 24);
@@ -131,27 +132,40 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        if (lane == 0) {
-            bool ok = true;
-            for (int32_t kb = 0; kb < nkb && ok; ++kb) {
-                const int sa = kb % ST_ASTAGES, sb = kb % ST_BSTAGES;
-                ok = mbar_wait(a_full(sa), (kb / ST_ASTAGES) & 1, abort_flag, 22);
-                if (ok) ok = mbar_wait(b_full(sb), (kb / ST_BSTAGES) & 1, abort_flag, 23);
+        // The whole warp runs the loop and one elected lane issues, with the ring positions static
+        // (unrolled over the A ring): next to busy warps a one-thread role pays 10+ clocks per
+        // instruction, and this one sits between the TMA data and the tensor pipe.
+        bool ok = true;
+        const uint64_t adesc0 = tc_smem_desc(a_ring), bdesc0 = tc_smem_desc(b_ring);
+        for (int32_t kb0 = 0; kb0 < nkb && ok; kb0 += ST_ASTAGES) {
+#pragma unroll
+            for (int u = 0; u < ST_ASTAGES; ++u) {
+                const int32_t kb = kb0 + u;
+                if (kb >= nkb || !ok) break;
+                const int sb = u % ST_BSTAGES;
+                const uint32_t pa = (uint32_t)(kb0 / ST_ASTAGES) & 1u, pb = (uint32_t)(kb / ST_BSTAGES) & 1u;
+                ok = __all_sync(0xffffffffu, mbar_wait(a_full(u), pa, abort_flag, 22) && mbar_wait(b_full(sb), pb, abort_flag, 23));
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t adesc = tc_smem_desc(a_ring + sa * ST_A_TILE);
-                const uint64_t bdesc = tc_smem_desc(b_ring + sb * ST_B_TILE);
+                if (tc_elect_one()) {
+                    const uint64_t adesc = adesc0 + (uint64_t)(u * (ST_A_TILE >> 4));
+                    const uint64_t bdesc = bdesc0 + (uint64_t)(sb * (ST_B_TILE >> 4));
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    tc_mma_i8_ss(tmem, adesc + 2u * k, bdesc + 2u * k, ST_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-                tc_commit(a_empty(sa));
-                tc_commit(b_empty(sb));
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma_i8_ss(tmem, adesc + 2u * k, bdesc + 2u * k, ST_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(a_empty(u));
+                    tc_commit(b_empty(sb));
+                }
+                __syncwarp();
             }
+        }
+        if (lane == 0) {
             if (ok) tc_commit(acc_full);
             tc_commit(drain_bar);
             const uint64_t t0 = tc_globaltimer();
             while (!mbar_try(drain_bar, 0) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
         }
+        __syncwarp();
     } else {
         // ================= B expanders (thread = one d row), then the epilogue (thread = one row of W) =================
         const int t = tid - 64;                              // 0..127
@@ -162,26 +176,39 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
             w[0] = (d < D && w0 < wpn) ? __ldg(vrow + w0) : 0ull;
             w[1] = (d < D && w0 + 1 < wpn) ? __ldg(vrow + w0 + 1) : 0ull;
         };
-        uint64_t cur[2], nxt[2];
-        load_bits(0, cur);
-        bool ok = true;
-        for (int32_t kb = 0; kb < nkb && ok; ++kb) {
-            const int sb = kb % ST_BSTAGES;
-            nxt[0] = nxt[1] = 0ull;
-            if (kb + 1 < nkb) load_bits(kb + 1, nxt);
-            ok = __all_sync(0xffffffffu, mbar_wait(b_empty(sb), ((kb / ST_BSTAGES) & 1) ^ 1, abort_flag, 24));
-            if (!ok) break;
-            uint8_t* row = gb + sb * ST_B_TILE + t * 128;
+        // the packed words are fetched ST_VPF k-blocks ahead (a ring of registers): one ahead leaves
+        // the load latency on the path of every k-block
+        constexpr int ST_VPF = 4;
+        uint64_t ring[ST_VPF][2];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {                     // chunk c: bytes 16c .. 16c+15 = bits 16c .. 16c+15
-                const uint32_t w32 = (uint32_t)(cur[c >> 2] >> (16 * (c & 3)));
-                *reinterpret_cast<uint4*>(row + ((c ^ (t & 7)) << 4)) =
-                    make_uint4(st_bits4_to_bytes(w32, 0), st_bits4_to_bytes(w32, 4), st_bits4_to_bytes(w32, 8), st_bits4_to_bytes(w32, 12));
+        for (int u = 0; u < ST_VPF - 1; ++u) {
+            ring[u][0] = ring[u][1] = 0ull;
+            if (u < nkb) load_bits(u, ring[u]);
+        }
+        bool ok = true;
+        for (int32_t kb0 = 0; kb0 < nkb && ok; kb0 += ST_VPF) {
+#pragma unroll
+            for (int u = 0; u < ST_VPF; ++u) {                // ring slots are static register names
+                const int32_t kb = kb0 + u;
+                if (kb >= nkb || !ok) break;
+                const int sb = u % ST_BSTAGES;
+                uint64_t (&nx)[2] = ring[(u + ST_VPF - 1) % ST_VPF];
+                nx[0] = nx[1] = 0ull;
+                if (kb + ST_VPF - 1 < nkb) load_bits(kb + ST_VPF - 1, nx);
+                ok = __all_sync(0xffffffffu, mbar_wait(b_empty(sb), ((kb / ST_BSTAGES) & 1) ^ 1, abort_flag, 24));
+                if (!ok) break;
+                const uint64_t (&cur)[2] = ring[u];
+                uint8_t* row = gb + sb * ST_B_TILE + t * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {                 // chunk c: bytes 16c .. 16c+15 = bits 16c .. 16c+15
+                    const uint32_t w32 = (uint32_t)(cur[c >> 2] >> (16 * (c & 3)));
+                    *reinterpret_cast<uint4*>(row + ((c ^ (t & 7)) << 4)) =
+                        make_uint4(st_bits4_to_bytes(w32, 0), st_bits4_to_bytes(w32, 4), st_bits4_to_bytes(w32, 8), st_bits4_to_bytes(w32, 12));
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_full(sb));
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(b_full(sb));
-            cur[0] = nxt[0]; cur[1] = nxt[1];
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, 25));
         if (ok) {

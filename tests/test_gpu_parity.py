@@ -548,7 +548,7 @@ ATT_TOL = 2e-2      # relative to the largest |output|, the tolerance the task s
 
 @pytest.mark.parametrize("B,H,S,D,causal", [(1, 2, 256, 128, True), (1, 1, 200, 128, True), (2, 2, 128, 64, True),
                                             (1, 2, 333, 128, False), (1, 1, 64, 64, False), (1, 1, 1, 128, True),
-                                            (1, 3, 1000, 128, True)])
+                                            (1, 3, 1000, 128, True), (1, 2, 1000, 64, True), (1, 2, 777, 64, False)])
 def test_attention_vs_oracle(ops, co, B, H, S, D, causal):
     import brute_b200 as brute
     g = gen(S + D)
@@ -565,16 +565,17 @@ def test_attention_vs_oracle(ops, co, B, H, S, D, causal):
     assert np.abs(got - want).max() <= ATT_TOL * max(np.abs(want).max(), 1e-6)
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("S,causal,scale", [(2048, True, None), (1111, False, None), (640, True, -0.05), (512, True, 0.5)])
-def test_attention_kernels_agree(ops, co, monkeypatch, S, causal, scale):
-    # D = 128 has three kernels (tcgen05, mma.sync scores, CUDA-core scores) that round the weights
+def test_attention_kernels_agree(ops, co, monkeypatch, S, causal, scale, D):
+    # each head dim has three kernels (tcgen05, mma.sync scores, CUDA-core scores) that round the weights
     # to bf16 the same way and differ only in the order of fp32 sums; scale 0.5 is too steep for the
     # table and takes the online-softmax kernel whatever the setting
     import brute_b200 as brute
     g = gen(S)
-    q = torch.randn((1, 4, S, 128), generator=g)
-    k = torch.randn((1, 4, S, 128), generator=g)
-    v = torch.randn((1, 4, S, 128), generator=g).to(torch.bfloat16).to(DEV)
+    q = torch.randn((1, 4, S, D), generator=g)
+    k = torch.randn((1, 4, S, D), generator=g)
+    v = torch.randn((1, 4, S, D), generator=g).to(torch.bfloat16).to(DEV)
     qb, kb = brute.pack_sign(q.to(DEV), ge0=True), brute.pack_sign(k.to(DEV), ge0=True)
     outs = {}
     for impl in ("tcgen05", "mma", "popc"):
@@ -585,7 +586,7 @@ def test_attention_kernels_agree(ops, co, monkeypatch, S, causal, scale):
     for impl in ("tcgen05", "mma"):
         assert float((outs[impl] - ref).abs().max()) <= 1e-2 * float(ref.abs().max()), impl
     want = co.binary_attention(co.pack_sign_f32(q.numpy(), 1), co.pack_sign_f32(k.numpy(), 1),
-                               v.float().cpu().numpy(), causal, 128 ** -0.5 if scale is None else scale)
+                               v.float().cpu().numpy(), causal, D ** -0.5 if scale is None else scale)
     assert np.abs(outs["tcgen05"].cpu().numpy() - want).max() <= ATT_TOL * np.abs(want).max()
     assert status_ok()
 
