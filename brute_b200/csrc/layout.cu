@@ -58,7 +58,9 @@ k_transpose_bits(const uint64_t* __restrict__ in, uint64_t* __restrict__ out,
     // 64-byte run per DRAM page.
     const int64_t grp = (int64_t)blockIdx.x >> 6;
     const int in_grp = (int)(blockIdx.x & 63);
-    const int64_t tx = (grp % sgx) * 8 + (in_grp & 7), ty = (grp / sgx) * 8 + (in_grp >> 3);
+    // sgx = 0: a matrix with fewer than 8 tiles along a side gets one CTA per tile, in row-major order
+    const int64_t tx = sgx ? (grp % sgx) * 8 + (in_grp & 7) : (int64_t)blockIdx.x % gx;
+    const int64_t ty = sgx ? (grp / sgx) * 8 + (in_grp >> 3) : (int64_t)blockIdx.x / gx;
     if (tx >= gx || ty >= gy) return;
     const int64_t r0 = ty * TB_TILE;                               // first input row of the tile
     const int64_t cw0 = tx * TB_BLOCKS;                            // first input word (column block) of the tile
@@ -139,7 +141,9 @@ k_transpose_bits_tma(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
     const int64_t b = blockIdx.y;
     const int64_t grp = (int64_t)blockIdx.x >> 6;
     const int in_grp = (int)(blockIdx.x & 63);
-    const int64_t tx = (grp % sgx) * 8 + (in_grp & 7), ty = (grp / sgx) * 8 + (in_grp >> 3);
+    // sgx = 0: a matrix with fewer than 8 tiles along a side gets one CTA per tile, in row-major order
+    const int64_t tx = sgx ? (grp % sgx) * 8 + (in_grp & 7) : (int64_t)blockIdx.x % gx;
+    const int64_t ty = sgx ? (grp / sgx) * 8 + (in_grp >> 3) : (int64_t)blockIdx.x / gx;
     if (tx >= gx || ty >= gy) return;
 
     if (tid == 0) {
@@ -312,9 +316,13 @@ extern "C" int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out,
     BB_REQUIRE(in != nullptr && out != nullptr && in != out, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(aligned8(in) && aligned8(out), BRUTE_ERR_MISALIGNED);
     const int64_t gx = (wpr_in + TB_BLOCKS - 1) / TB_BLOCKS, gy = (R + TB_TILE - 1) / TB_TILE;
-    const int64_t sgx = (gx + 7) / 8, sgy = (gy + 7) / 8;
-    BB_REQUIRE(sgx * sgy * 64 <= 0x7fffffffll && batch <= 65535, BRUTE_ERR_UNSUPPORTED);
-    const dim3 grid((unsigned)(sgx * sgy * 64), (unsigned)batch);
+    // 8 x 8 groups of tiles for DRAM locality; a narrow or short matrix (many small ones in a batch,
+    // as signed_bundle's V) would launch mostly empty groups, so it gets exactly its tiles
+    const bool grouped = gx >= 8 && gy >= 8;
+    const int64_t sgx = grouped ? (gx + 7) / 8 : 0, sgy = (gy + 7) / 8;
+    const int64_t ctas = grouped ? sgx * sgy * 64 : gx * gy;
+    BB_REQUIRE(ctas <= 0x7fffffffll && batch <= 65535, BRUTE_ERR_UNSUPPORTED);
+    const dim3 grid((unsigned)ctas, (unsigned)batch);
     // TMA wants 16-byte aligned bases and row (and batch) pitches, and 32-bit coordinates
     if ((wpr_in & 1) == 0 && (wpr_out & 1) == 0 && aligned16(in) && aligned16(out) &&
         R < (1ll << 31) - TB_TILE && C < (1ll << 31) - TB_TILE) {

@@ -12,7 +12,8 @@
 // The kernel streams W once: B*M*N bytes against B*M*N*D MACs, i.e. it is HBM bound once the
 // tensor cores do the MACs (the dp4a kernel in signed_bundle.cu is 30x away from that bound).
 //
-// CTA = 128 rows of W of one batch x one block of 128 d; 192 threads:
+// Work item = 128 rows of W of one batch x one block of 128 d; persistent CTAs of 192 threads
+// (two per SM) walk over the items:
 //   warp 0      TMA producer for W tiles (4-deep ring of 16 KB)
 //   warp 1      MMA issuer, TMEM owner (256 columns; two CTAs per SM)
 //   warps 2-5   expand Vt bits into the B tile (2-deep ring of 144 x 128 bytes), then the epilogue:
@@ -55,7 +56,8 @@ __global__ void __launch_bounds__(ST_THREADS, 2)
 k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
                         const uint64_t* __restrict__ Vt /* [B, D, wpn] words, bit n of row d */,
                         uint64_t* __restrict__ out /* [B, M, Dp] */,
-                        int64_t M, int64_t N, int64_t D, int64_t Dp, int64_t wpn) {
+                        int64_t M, int64_t N, int64_t D, int64_t Dp, int64_t wpn,
+                        int32_t m_tiles, int32_t d_blocks, int64_t items) {
     extern __shared__ uint8_t st_smem_raw[];
     __shared__ int s_skip;
     if (threadIdx.x == 0) s_skip = *(volatile int*)&g_tc_status;
@@ -73,16 +75,19 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
     auto b_full  = [&](int s) { return bars + 8u * (2 * ST_ASTAGES + s); };
     auto b_empty = [&](int s) { return bars + 8u * (2 * ST_ASTAGES + ST_BSTAGES + s); };
     constexpr int NB = 2 * ST_ASTAGES + 2 * ST_BSTAGES;
-    const uint32_t acc_full = bars + 8u * NB, drain_bar = acc_full + 8u;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (NB + 2));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (NB + 2) + 4);
+    const uint32_t acc_full = bars + 8u * NB, acc_empty = acc_full + 8u, drain_bar = acc_full + 16u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbars + 8 * (NB + 3));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbars + 8 * (NB + 3) + 4);
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // a shuffle result: known to the compiler as the same in all lanes
-    const int64_t m0 = (int64_t)blockIdx.x * ST_BM;
-    const int64_t d0 = (int64_t)blockIdx.y * ST_DB;
-    const int64_t b = blockIdx.z;
     const int32_t nkb = (int32_t)((N + ST_KB - 1) / ST_KB);
+    // work item -> (row tile, d block, batch); consecutive items share the batch and the d block
+    auto item_coords = [&](int64_t it, int64_t& m0, int64_t& dblk, int64_t& b) {
+        m0 = (it % m_tiles) * ST_BM;
+        dblk = (it / m_tiles) % d_blocks;
+        b = it / ((int64_t)m_tiles * d_blocks);
+    };
 
     // the constant rows of both B tiles: row 128 = ones (gives S), rows 129..143 = zeros
     for (int i = tid; i < ST_BSTAGES * 16 * 8; i += ST_THREADS) {
@@ -94,6 +99,7 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
         for (int s = 0; s < ST_ASTAGES; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
         for (int s = 0; s < ST_BSTAGES; ++s) { mbar_init(b_full(s), 4); mbar_init(b_empty(s), 1); }
         mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 4);
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -109,58 +115,68 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
+    // Persistent: the CTA walks over work items, and every role keeps ONE running count of the
+    // k-blocks it has handled, so the TMA ring never drains between items (a CTA per item paid its
+    // set-up, its first TMA latency and its epilogue once per 128 KB of W).
     if (warp == 0) {
         // ================= TMA producer: W tiles [128 rows x 128 bytes of n] =================
         if (lane == 0) {
             bool ok = true;
-            int32_t issued = 0;
-            for (int32_t kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % ST_ASTAGES;
-                ok = mbar_wait(a_empty(s), ((kb / ST_ASTAGES) & 1) ^ 1, abort_flag, 21);
-                if (!ok) break;
-                mbar_expect_tx(a_full(s), ST_A_TILE);
-                tma_load_3d(a_ring + s * ST_A_TILE, &tmW, kb * ST_KB, (int32_t)m0, (int32_t)b, a_full(s));
-                issued = kb + 1;
+            uint32_t g = 0;                                   // k-blocks issued so far
+            for (int64_t it = blockIdx.x; it < items && ok; it += gridDim.x) {
+                int64_t m0, dblk, b;
+                item_coords(it, m0, dblk, b);
+                for (int32_t kb = 0; kb < nkb; ++kb, ++g) {
+                    const int s = (int)(g % ST_ASTAGES);
+                    ok = mbar_wait(a_empty(s), ((g / ST_ASTAGES) & 1u) ^ 1u, abort_flag, 21);
+                    if (!ok) break;
+                    mbar_expect_tx(a_full(s), ST_A_TILE);
+                    tma_load_3d(a_ring + s * ST_A_TILE, &tmW, kb * ST_KB, (int32_t)m0, (int32_t)b, a_full(s));
+                }
             }
             if (!ok) {
-                const int32_t first = issued > ST_ASTAGES ? issued - ST_ASTAGES : 0;
-                for (int32_t kb = first; kb < issued; ++kb) {
+                // g loads were issued; let the last ring's worth land before the shared memory goes away
+                const uint32_t first = g > (uint32_t)ST_ASTAGES ? g - ST_ASTAGES : 0u;
+                for (uint32_t k = first; k < g; ++k) {
                     const uint64_t t0 = tc_globaltimer();
-                    while (!mbar_try(a_full(kb % ST_ASTAGES), (kb / ST_ASTAGES) & 1) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
+                    while (!mbar_try(a_full((int)(k % ST_ASTAGES)), (k / ST_ASTAGES) & 1u) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
                 }
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        // The whole warp runs the loop and one elected lane issues, with the ring positions static
-        // (unrolled over the A ring): next to busy warps a one-thread role pays 10+ clocks per
-        // instruction, and this one sits between the TMA data and the tensor pipe.
+        // The whole warp runs the loop and one elected lane issues: next to busy warps a one-thread
+        // role pays 10+ clocks per instruction, and this one sits between the TMA data and the
+        // tensor pipe.
         bool ok = true;
         const uint64_t adesc0 = tc_smem_desc(a_ring), bdesc0 = tc_smem_desc(b_ring);
-        for (int32_t kb0 = 0; kb0 < nkb && ok; kb0 += ST_ASTAGES) {
-#pragma unroll
-            for (int u = 0; u < ST_ASTAGES; ++u) {
-                const int32_t kb = kb0 + u;
-                if (kb >= nkb || !ok) break;
-                const int sb = u % ST_BSTAGES;
-                const uint32_t pa = (uint32_t)(kb0 / ST_ASTAGES) & 1u, pb = (uint32_t)(kb / ST_BSTAGES) & 1u;
-                ok = __all_sync(0xffffffffu, mbar_wait(a_full(u), pa, abort_flag, 22) && mbar_wait(b_full(sb), pb, abort_flag, 23));
+        uint32_t g = 0, n_items = 0;
+        for (int64_t it = blockIdx.x; it < items && ok; it += gridDim.x, ++n_items) {
+            // the accumulator of the previous item has been read by the four epilogue warps
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_empty, (n_items & 1u) ^ 1u, abort_flag, 26));
+            if (!ok) break;
+            tc_fence_after();
+            for (int32_t kb = 0; kb < nkb && ok; ++kb, ++g) {
+                const int sa = (int)(g % ST_ASTAGES), sb = (int)(g % ST_BSTAGES);
+                ok = __all_sync(0xffffffffu, mbar_wait(a_full(sa), (g / ST_ASTAGES) & 1u, abort_flag, 22) &&
+                                             mbar_wait(b_full(sb), (g / ST_BSTAGES) & 1u, abort_flag, 23));
                 if (!ok) break;
                 tc_fence_after();
                 if (tc_elect_one()) {
-                    const uint64_t adesc = adesc0 + (uint64_t)(u * (ST_A_TILE >> 4));
+                    const uint64_t adesc = adesc0 + (uint64_t)(sa * (ST_A_TILE >> 4));
                     const uint64_t bdesc = bdesc0 + (uint64_t)(sb * (ST_B_TILE >> 4));
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         tc_mma_i8_ss(tmem, adesc + 2u * k, bdesc + 2u * k, ST_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(a_empty(u));
+                    tc_commit(a_empty(sa));
                     tc_commit(b_empty(sb));
                 }
                 __syncwarp();
             }
+            if (ok && tc_elect_one()) tc_commit(acc_full);
+            __syncwarp();
         }
         if (lane == 0) {
-            if (ok) tc_commit(acc_full);
             tc_commit(drain_bar);
             const uint64_t t0 = tc_globaltimer();
             while (!mbar_try(drain_bar, 0) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
@@ -169,53 +185,53 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
     } else {
         // ================= B expanders (thread = one d row), then the epilogue (thread = one row of W) =================
         const int t = tid - 64;                              // 0..127
-        const int64_t d = d0 + t;
-        const uint64_t* vrow = Vt + (b * D + (d < D ? d : 0)) * wpn;
-        auto load_bits = [&](int32_t kb, uint64_t (&w)[2]) {
-            const int64_t w0 = 2 * (int64_t)kb;
-            w[0] = (d < D && w0 < wpn) ? __ldg(vrow + w0) : 0ull;
-            w[1] = (d < D && w0 + 1 < wpn) ? __ldg(vrow + w0 + 1) : 0ull;
-        };
-        // the packed words are fetched ST_VPF k-blocks ahead (a ring of registers): one ahead leaves
-        // the load latency on the path of every k-block
-        constexpr int ST_VPF = 4;
-        uint64_t ring[ST_VPF][2];
-#pragma unroll
-        for (int u = 0; u < ST_VPF - 1; ++u) {
-            ring[u][0] = ring[u][1] = 0ull;
-            if (u < nkb) load_bits(u, ring[u]);
-        }
+        const int quarter = warp & 3;
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
-        for (int32_t kb0 = 0; kb0 < nkb && ok; kb0 += ST_VPF) {
+        uint32_t g = 0, n_items = 0;
+        for (int64_t it = blockIdx.x; it < items && ok; it += gridDim.x, ++n_items) {
+            int64_t m0, dblk, b;
+            item_coords(it, m0, dblk, b);
+            const int64_t d = dblk * ST_DB + t;
+            const uint64_t* vrow = Vt + (b * D + (d < D ? d : 0)) * wpn;
+            auto load_bits = [&](int32_t kb, uint64_t (&w)[2]) {
+                const int64_t w0 = 2 * (int64_t)kb;
+                w[0] = (kb < nkb && d < D && w0 < wpn) ? __ldg(vrow + w0) : 0ull;
+                w[1] = (kb < nkb && d < D && w0 + 1 < wpn) ? __ldg(vrow + w0 + 1) : 0ull;
+            };
+            // the packed words are fetched ST_VPF k-blocks ahead (a ring of registers): one ahead
+            // leaves the load latency on the path of every k-block
+            constexpr int ST_VPF = 4;
+            uint64_t ring[ST_VPF][2];
 #pragma unroll
-            for (int u = 0; u < ST_VPF; ++u) {                // ring slots are static register names
-                const int32_t kb = kb0 + u;
-                if (kb >= nkb || !ok) break;
-                const int sb = u % ST_BSTAGES;
-                uint64_t (&nx)[2] = ring[(u + ST_VPF - 1) % ST_VPF];
-                nx[0] = nx[1] = 0ull;
-                if (kb + ST_VPF - 1 < nkb) load_bits(kb + ST_VPF - 1, nx);
-                ok = __all_sync(0xffffffffu, mbar_wait(b_empty(sb), ((kb / ST_BSTAGES) & 1) ^ 1, abort_flag, 24));
-                if (!ok) break;
-                const uint64_t (&cur)[2] = ring[u];
-                uint8_t* row = gb + sb * ST_B_TILE + t * 128;
+            for (int u = 0; u < ST_VPF - 1; ++u) load_bits(u, ring[u]);
+            for (int32_t kb0 = 0; kb0 < nkb && ok; kb0 += ST_VPF) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {                 // chunk c: bytes 16c .. 16c+15 = bits 16c .. 16c+15
-                    const uint32_t w32 = (uint32_t)(cur[c >> 2] >> (16 * (c & 3)));
-                    *reinterpret_cast<uint4*>(row + ((c ^ (t & 7)) << 4)) =
-                        make_uint4(st_bits4_to_bytes(w32, 0), st_bits4_to_bytes(w32, 4), st_bits4_to_bytes(w32, 8), st_bits4_to_bytes(w32, 12));
+                for (int u = 0; u < ST_VPF; ++u) {            // ring slots are static register names
+                    const int32_t kb = kb0 + u;
+                    if (kb >= nkb || !ok) break;
+                    load_bits(kb + ST_VPF - 1, ring[(u + ST_VPF - 1) % ST_VPF]);
+                    const int sb = (int)(g % ST_BSTAGES);
+                    ok = __all_sync(0xffffffffu, mbar_wait(b_empty(sb), ((g / ST_BSTAGES) & 1u) ^ 1u, abort_flag, 24));
+                    if (!ok) break;
+                    ++g;
+                    const uint64_t (&cur)[2] = ring[u];
+                    uint8_t* row = gb + sb * ST_B_TILE + t * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {             // chunk c: bytes 16c .. 16c+15 = bits 16c .. 16c+15
+                        const uint32_t w32 = (uint32_t)(cur[c >> 2] >> (16 * (c & 3)));
+                        *reinterpret_cast<uint4*>(row + ((c ^ (t & 7)) << 4)) =
+                            make_uint4(st_bits4_to_bytes(w32, 0), st_bits4_to_bytes(w32, 4), st_bits4_to_bytes(w32, 8), st_bits4_to_bytes(w32, 12));
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(b_full(sb));
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(b_full(sb));
             }
-        }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, 25));
-        if (ok) {
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, n_items & 1u, abort_flag, 25));
+            if (!ok) break;
             tc_fence_after();
-            const int quarter = warp & 3;
             const int64_t m = m0 + quarter * 32 + lane;
-            const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
             const int32_t S = (int32_t)tc_ld1(lane_base + ST_DB);
             uint32_t bits[4];
 #pragma unroll 1
@@ -223,6 +239,11 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
                 uint32_t v[32];
                 tc_ld32(lane_base + 32 * c, v);
                 tc_wait_ld();
+                if (c == 3) {                                 // the accumulator is in registers: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty);
+                }
                 uint32_t w = 0;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) w |= (2 * (int32_t)v[j] - S >= 0 ? 1u : 0u) << j;
@@ -231,7 +252,7 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
             if (m < M) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int64_t word = 2 * (int64_t)blockIdx.y + h;
+                    const int64_t word = 2 * dblk + h;
                     if (word >= Dp) continue;
                     uint64_t w = (uint64_t)bits[2 * h] | ((uint64_t)bits[2 * h + 1] << 32);
                     const int64_t valid = D - word * 64;                 // pad bits stay 0
@@ -274,8 +295,12 @@ static int st_run(const int8_t* W, const uint64_t* Vt, uint64_t* out, int64_t B,
     CUtensorMap tmW;
     BB_REQUIRE(st_make_w_map(&tmW, W, B, M, N), BRUTE_ERR_DRIVER);
     if (!kernel_smem_ready<k_signed_bundle_tcgen05>(ST_SMEM)) return BRUTE_ERR_LAUNCH;
-    const dim3 grid((unsigned)((M + ST_BM - 1) / ST_BM), (unsigned)((D + ST_DB - 1) / ST_DB), (unsigned)B);
-    k_signed_bundle_tcgen05<<<grid, ST_THREADS, ST_SMEM, st>>>(tmW, Vt, out, M, N, D, Dp, (N + 63) / 64);
+    const int64_t m_tiles = (M + ST_BM - 1) / ST_BM, d_blocks = (D + ST_DB - 1) / ST_DB;
+    const int64_t items = m_tiles * d_blocks * B;
+    const int64_t resident = 2 * (int64_t)kNumSMs;                     // two CTAs per SM (shared memory)
+    const unsigned grid = (unsigned)(items < resident ? items : resident);
+    k_signed_bundle_tcgen05<<<grid, ST_THREADS, ST_SMEM, st>>>(tmW, Vt, out, M, N, D, Dp, (N + 63) / 64,
+                                                              (int32_t)m_tiles, (int32_t)d_blocks, items);
     return launch_status();
 }
 
