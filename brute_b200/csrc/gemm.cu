@@ -82,9 +82,12 @@ static int dispatch(const GemmArgs& g, int impl, cudaStream_t st) {
         else if (e == BRUTE_GEMM_TCGEN05_PAIR && tc5_accepts(g.A, g.B, g.M, g.N, g.Kp) && tc5_pair_accepts(g.M, g.N)) impl = e;
     }
     if (impl == BRUTE_GEMM_AUTO) {
-        // Small problems do not fill the tensor-core tiles; the CUDA-core path
-        // has no shape rules at all.
-        if (tc5_accepts(g.A, g.B, g.M, g.N, g.Kp) && g.M * g.N >= 128 * 256)
+        // The tcgen05 kernels take every shape their TMA maps can describe, down to one row: even
+        // a single mostly empty tile (28 us for 1 x 4096 x 4096 from an eager call, of which
+        // about 25 are the call itself) beats the serial K loops of the other two paths
+        // (84 us CUDA cores, 190 us mma.sync b1 at K = 4096). The CUDA-core path has no shape
+        // rules at all and takes the rest (odd word counts, unaligned operands).
+        if (tc5_accepts(g.A, g.B, g.M, g.N, g.Kp))
             impl = tc5_pair_prefers(g.M, g.N) ? BRUTE_GEMM_TCGEN05_PAIR : BRUTE_GEMM_TCGEN05;
         else if (mma_b1_accepts(g) && g.M * g.N >= 64 * 64) impl = BRUTE_GEMM_MMA_B1;
         else impl = BRUTE_GEMM_POPC;
