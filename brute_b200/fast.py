@@ -14,51 +14,63 @@ from .tensor import Tensor, _OP_AND, _OP_OR, _OP_XOR, _OP_XNOR, _packed_bin
 _ops = torch.ops.brute
 
 
-def _wrap(packed: torch.Tensor, like: Tensor) -> Tensor:
-    return Tensor._make_bit1_from_packed(packed, list(like.shape))
+# Shapes and packed buffers are read through the plain alias of a tensor (one as_subclass): every
+# attribute read on the subclass itself is a __torch_function__ round trip.
+def _pk(t: Tensor):
+    """(packed buffer, logical shape) of a bit1 tensor."""
+    plain = t.as_subclass(torch.Tensor)
+    return t._packed_fast(plain), plain.shape
+
+
+def _bin(code: int, a: Tensor, b: Tensor) -> Tensor:
+    pa, shape = _pk(a)
+    pb, _ = _pk(b)
+    return Tensor._make_bit1_from_packed(_packed_bin(code, pa, pb, shape[-1]), shape)
 
 
 def bitwise_xor(a: Tensor, b: Tensor) -> Tensor:
     """``a ^ b`` on two same-shape bit1 tensors; the result's bool view is lazy."""
-    return _wrap(_packed_bin(_OP_XOR, a._packed_buf, b._packed_buf, int(a.shape[-1])), a)
+    return _bin(_OP_XOR, a, b)
 
 
 def bitwise_and(a: Tensor, b: Tensor) -> Tensor:
-    return _wrap(_packed_bin(_OP_AND, a._packed_buf, b._packed_buf, int(a.shape[-1])), a)
+    return _bin(_OP_AND, a, b)
 
 
 def bitwise_or(a: Tensor, b: Tensor) -> Tensor:
-    return _wrap(_packed_bin(_OP_OR, a._packed_buf, b._packed_buf, int(a.shape[-1])), a)
+    return _bin(_OP_OR, a, b)
 
 
 def bitwise_not(a: Tensor) -> Tensor:
     """``~a`` with the pad bits of each row's last word kept 0."""
-    return _wrap(_ops.bit1_not_packed(a._packed_buf, int(a.shape[-1])), a)
+    pa, shape = _pk(a)
+    return Tensor._make_bit1_from_packed(_ops.bit1_not_packed(pa, shape[-1]), shape)
 
 
 def eq(a: Tensor, b: Tensor) -> Tensor:
     """``a == b``: pad-safe XNOR."""
-    return _wrap(_packed_bin(_OP_XNOR, a._packed_buf, b._packed_buf, int(a.shape[-1])), a)
+    return _bin(_OP_XNOR, a, b)
 
 
 def ne(a: Tensor, b: Tensor) -> Tensor:
     """``a != b``: XOR."""
-    return _wrap(_packed_bin(_OP_XOR, a._packed_buf, b._packed_buf, int(a.shape[-1])), a)
+    return _bin(_OP_XOR, a, b)
 
 
 def popcount(a: Tensor) -> Tensor:
     """Total number of set bits, 0-dim int64."""
-    return Tensor._make_plain(_ops.packed_popcount(a._packed_buf))
+    return Tensor._make_plain(_ops.packed_popcount(_pk(a)[0]))
 
 
 def hamming(a: Tensor, b: Tensor) -> Tensor:
     """Total Hamming distance, 0-dim int64."""
-    return Tensor._make_plain(_ops.bit1_hamming_total(a._packed_buf, b._packed_buf))
+    return Tensor._make_plain(_ops.bit1_hamming_total(_pk(a)[0], _pk(b)[0]))
 
 
 def matmul(a: Tensor, b_t: Tensor) -> torch.Tensor:
     """A (M, K) times B given as (N, K) rows of output features -> int32 ``K - 2H``."""
-    return _ops.xnor_popcount_matmul(a._packed_buf, b_t._packed_buf, int(a.shape[-1]))
+    pa, shape = _pk(a)
+    return _ops.xnor_popcount_matmul(pa, _pk(b_t)[0], shape[-1])
 
 
 def signed_bundle(W: torch.Tensor, V: Tensor) -> Tensor:

@@ -63,8 +63,43 @@ def _check(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
+_TORCH_CURRENT_STREAM = torch.cuda.current_stream
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_GET_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream(t: torch.Tensor) -> int:
+    """The caller's current stream on the tensor's device, as the raw handle the C ABI takes.
+    ``torch.cuda.current_stream`` builds a Stream object per call (a few microseconds, on an op
+    whose kernel may take as long); the raw handle comes straight from the runtime. While
+    ``parallel_streams`` has the public function replaced by its rotating one, that one is asked."""
+    if _RAW_STREAM is not None and torch.cuda.current_stream is _TORCH_CURRENT_STREAM:
+        return _RAW_STREAM(t.device.index)
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _device_guard:
+    """``with torch.cuda.device(dev)`` costs two runtime round trips per op; nearly every call
+    is for the device that is current already, where nothing has to be done."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index
+        self.prev = -1
+
+    def __enter__(self):
+        if self.idx is None:
+            return self
+        cur = _GET_DEVICE() if _GET_DEVICE is not None else torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def _words(n_bits: int) -> int:
@@ -85,7 +120,7 @@ def pack_bool(input: torch.Tensor) -> torch.Tensor:
     out = torch.empty(shape, dtype=torch.int64, device=inp.device)
     if out.numel() == 0:
         return out
-    with torch.cuda.device(inp.device):
+    with _device_guard(inp.device):
         L.check(_lib.brute_b200_pack_bool(inp.data_ptr(), out.data_ptr(), inp.numel() // ld, ld,
                                           _stream(inp)), "pack_bool")
     return out
@@ -101,7 +136,7 @@ def pack_sign(input: torch.Tensor, mode: int) -> torch.Tensor:
     out = torch.empty(shape, dtype=torch.int64, device=inp.device)
     if out.numel() == 0:
         return out
-    with torch.cuda.device(inp.device):
+    with _device_guard(inp.device):
         L.check(_lib.brute_b200_pack_sign(inp.data_ptr(), _SIGN_DTYPES[inp.dtype], out.data_ptr(),
                                           inp.numel() // ld, ld, int(mode), _stream(inp)), "pack_sign")
     return out
@@ -128,7 +163,7 @@ def unpack_bool(packed: torch.Tensor, logical_shape) -> torch.Tensor:
         return out
     _check(p.dtype == torch.int64, "unpack_bool: packed must be torch.int64")
     _check(_unpack_geometry_ok(p, shape, ll), "unpack_bool: packed shape does not match logical_shape")
-    with torch.cuda.device(p.device):
+    with _device_guard(p.device):
         L.check(_lib.brute_b200_unpack_bool(p.data_ptr(), out.data_ptr(), p.numel() // p.size(-1), ll,
                                             _stream(p)), "unpack_bool")
     return out
@@ -141,7 +176,7 @@ def unpack_bits(packed: torch.Tensor, logical_shape) -> torch.Tensor:
         return out
     _check(p.dtype == torch.int64, "unpack_bits: packed must be torch.int64")
     _check(_unpack_geometry_ok(p, shape, ll), "unpack_bits: packed shape does not match logical_shape")
-    with torch.cuda.device(p.device):
+    with _device_guard(p.device):
         L.check(_lib.brute_b200_unpack_pm1_f32(p.data_ptr(), out.data_ptr(), p.numel() // p.size(-1), ll,
                                                _stream(p)), "unpack_bits")
     return out
@@ -165,7 +200,7 @@ def xnor_popcount_matmul_impl(A: torch.Tensor, B: torch.Tensor, K: int, impl: in
     C = torch.empty((M, N), dtype=torch.int32, device=Ac.device)
     if M == 0 or N == 0:
         return C
-    with torch.cuda.device(Ac.device):
+    with _device_guard(Ac.device):
         L.check(_lib.brute_b200_xnor_gemm(Ac.data_ptr(), Bc.data_ptr(), C.data_ptr(), M, N, Kp, int(K), N,
                                           int(impl), _stream(Ac)), "xnor_popcount_matmul")
     return C
@@ -184,7 +219,7 @@ def xnor_matmul_scale_sign_pack(A, B, scale, K: int, mode: int) -> torch.Tensor:
     out = torch.empty((M, _words(N)), dtype=torch.int64, device=Ac.device)
     if out.numel() == 0:
         return out
-    with torch.cuda.device(Ac.device):
+    with _device_guard(Ac.device):
         L.check(_lib.brute_b200_xnor_gemm_scale_sign_pack(
             Ac.data_ptr(), Bc.data_ptr(), sc.data_ptr(), out.data_ptr(), M, N, Kp, int(K), int(mode),
             L.GEMM_AUTO, _stream(Ac)), "xnor_matmul_scale_sign_pack")
@@ -201,7 +236,7 @@ def signed_bundle(W: torch.Tensor, V: torch.Tensor, D: int) -> torch.Tensor:
     Wc, Vc = W.contiguous(), V.contiguous()
     out = torch.empty((B, M, Dp), dtype=torch.int64, device=V.device)
     if out.numel():
-        with torch.cuda.device(V.device):
+        with _device_guard(V.device):
             # the library allocates nothing: the scratch for the bit-transposed V comes from here
             ws_bytes = int(_lib.brute_b200_signed_bundle_workspace_bytes(B, N, int(D)))
             ws = torch.empty(max(ws_bytes, 8) // 8, dtype=torch.int64, device=V.device)
@@ -221,7 +256,7 @@ def popcount(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty(p.shape, dtype=torch.int32, device=p.device)
     if p.numel() == 0:
         return out
-    with torch.cuda.device(p.device):
+    with _device_guard(p.device):
         L.check(_lib.brute_b200_popcount_elems(p.data_ptr(), out.data_ptr(), p.numel(),
                                                _POPCOUNT_BYTES[p.dtype], _stream(p)), "popcount")
     return out
@@ -230,7 +265,7 @@ def popcount(x: torch.Tensor) -> torch.Tensor:
 def packed_popcount(x: torch.Tensor) -> torch.Tensor:
     p = x.contiguous()
     out = torch.empty((), dtype=torch.int64, device=p.device)      # zeroed by the call itself
-    with torch.cuda.device(p.device):
+    with _device_guard(p.device):
         L.check(_lib.brute_b200_popcount_total(p.data_ptr() if p.numel() else None,
                                                p.numel() * p.element_size(), out.data_ptr(), _stream(p)),
                 "packed_popcount")
@@ -242,7 +277,7 @@ def bit1_hamming_total(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
     _check(A.dtype == B.dtype, "bit1_hamming_total: dtype mismatch")
     Ac, Bc = A.contiguous(), B.contiguous()
     out = torch.empty((), dtype=torch.int64, device=Ac.device)
-    with torch.cuda.device(Ac.device):
+    with _device_guard(Ac.device):
         L.check(_lib.brute_b200_hamming_total(Ac.data_ptr() if Ac.numel() else None,
                                               Bc.data_ptr() if Bc.numel() else None,
                                               Ac.numel() * Ac.element_size(), out.data_ptr(), _stream(Ac)),
@@ -255,7 +290,7 @@ def hamming_distance(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
         Ac, Bc = A.contiguous(), B.contiguous()
         out = torch.empty(Ac.shape, dtype=torch.int32, device=Ac.device)
         if Ac.numel():
-            with torch.cuda.device(Ac.device):
+            with _device_guard(Ac.device):
                 L.check(_lib.brute_b200_hamming_words(Ac.data_ptr(), Bc.data_ptr(), out.data_ptr(),
                                                       Ac.numel(), _stream(Ac)), "hamming_distance")
         return out
@@ -273,7 +308,7 @@ def bit1_not_packed(A: torch.Tensor, last_dim_bits: int) -> torch.Tensor:
         return out
     wpr = Ac.size(-1) if Ac.dim() else 1
     # the reference leaves the tail alone when last_dim_bits == 0 or a multiple of 64
-    with torch.cuda.device(Ac.device):
+    with _device_guard(Ac.device):
         L.check(_lib.brute_b200_not_masked(Ac.data_ptr(), out.data_ptr(), Ac.numel() // wpr, wpr,
                                            int(last_dim_bits), _stream(Ac)), "bit1_not_packed")
     return out
@@ -287,7 +322,7 @@ def bitwise_packed(A: torch.Tensor, B: torch.Tensor, op: int, last_dim_bits: int
     if Ac.numel() == 0:
         return out
     wpr = Ac.size(-1) if Ac.dim() else 1
-    with torch.cuda.device(Ac.device):
+    with _device_guard(Ac.device):
         L.check(_lib.brute_b200_bitwise(int(op), Ac.data_ptr(), Bc.data_ptr(), out.data_ptr(),
                                         Ac.numel() // wpr, wpr, int(last_dim_bits), _stream(Ac)),
                 "bitwise_packed")
@@ -299,7 +334,7 @@ def select_packed(cond: torch.Tensor, A: torch.Tensor, B: torch.Tensor) -> torch
     c, a, b = cond.contiguous(), A.contiguous(), B.contiguous()
     out = torch.empty_like(a)
     if a.numel():
-        with torch.cuda.device(a.device):
+        with _device_guard(a.device):
             L.check(_lib.brute_b200_select(c.data_ptr(), a.data_ptr(), b.data_ptr(), out.data_ptr(),
                                            a.numel(), _stream(a)), "select_packed")
     return out
@@ -310,7 +345,7 @@ def row_any(A: torch.Tensor) -> torch.Tensor:
     Ac = A.contiguous()
     out = torch.empty(Ac.shape[:-1], dtype=torch.bool, device=Ac.device)
     if out.numel():
-        with torch.cuda.device(Ac.device):
+        with _device_guard(Ac.device):
             L.check(_lib.brute_b200_row_any(Ac.data_ptr() if Ac.numel() else None, out.data_ptr(),
                                             out.numel(), Ac.size(-1), _stream(Ac)), "row_any")
     return out
@@ -321,7 +356,7 @@ def row_all(A: torch.Tensor, last_dim_bits: int) -> torch.Tensor:
     Ac = A.contiguous()
     out = torch.empty(Ac.shape[:-1], dtype=torch.bool, device=Ac.device)
     if out.numel():
-        with torch.cuda.device(Ac.device):
+        with _device_guard(Ac.device):
             L.check(_lib.brute_b200_row_all(Ac.data_ptr() if Ac.numel() else None, out.data_ptr(),
                                             out.numel(), Ac.size(-1), int(last_dim_bits), _stream(Ac)),
                     "row_all")
@@ -340,7 +375,7 @@ def transpose_packed(packed: torch.Tensor, rows: int, cols: int) -> torch.Tensor
         batch *= int(d)
     out = torch.empty(tuple(pc.shape[:-2]) + (cols, _words(rows)), dtype=torch.int64, device=pc.device)
     if out.numel():
-        with torch.cuda.device(pc.device):
+        with _device_guard(pc.device):
             L.check(_lib.brute_b200_transpose_bits(pc.data_ptr(), out.data_ptr(), batch, rows, cols, _stream(pc)),
                     "transpose_packed")
     return out
@@ -361,7 +396,7 @@ def reduce_rows_packed(packed: torch.Tensor, dim: int, use_or: bool) -> torch.Te
         inner *= int(s_)
     out = torch.empty(tuple(pc.shape[:d]) + tuple(pc.shape[d + 1:]), dtype=torch.int64, device=pc.device)
     if out.numel():
-        with torch.cuda.device(pc.device):
+        with _device_guard(pc.device):
             L.check(_lib.brute_b200_reduce_rows(L.OP_OR if use_or else L.OP_AND, pc.data_ptr() if pc.numel() else None,
                                                 out.data_ptr(), outer, int(pc.size(d)), inner, _stream(pc)),
                     "reduce_rows_packed")
@@ -381,7 +416,7 @@ def flip_packed(packed: torch.Tensor, n: int) -> torch.Tensor:
     pc, rows = _packed_rows(packed, n, "flip_packed")
     out = torch.empty_like(pc)
     if out.numel():
-        with torch.cuda.device(pc.device):
+        with _device_guard(pc.device):
             L.check(_lib.brute_b200_flip_bits(pc.data_ptr(), out.data_ptr(), rows, int(n), _stream(pc)), "flip_packed")
     return out
 
@@ -391,7 +426,7 @@ def roll_packed(packed: torch.Tensor, n: int, shift: int) -> torch.Tensor:
     pc, rows = _packed_rows(packed, n, "roll_packed")
     out = torch.empty_like(pc)
     if out.numel():
-        with torch.cuda.device(pc.device):
+        with _device_guard(pc.device):
             L.check(_lib.brute_b200_roll_bits(pc.data_ptr(), out.data_ptr(), rows, int(n), int(shift), _stream(pc)),
                     "roll_packed")
     return out
@@ -406,7 +441,7 @@ def gather_packed(packed: torch.Tensor, idx: torch.Tensor, n_in: int) -> torch.T
     n_out = int(ic.numel())
     out = torch.empty(tuple(pc.shape[:-1]) + (_words(n_out),), dtype=torch.int64, device=pc.device)
     if out.numel():
-        with torch.cuda.device(pc.device):
+        with _device_guard(pc.device):
             L.check(_lib.brute_b200_gather_bits(pc.data_ptr() if pc.numel() else None, ic.data_ptr(), out.data_ptr(),
                                                 rows if pc.size(-1) else out.numel() // out.size(-1), int(n_in), n_out,
                                                 _stream(pc)), "gather_packed")
@@ -432,7 +467,7 @@ def binary_attention(Qp: torch.Tensor, Kp: torch.Tensor, V: torch.Tensor, causal
     q, k, v = Qp.contiguous(), Kp.contiguous(), V.contiguous()
     out = torch.empty_like(v)
     if out.numel():
-        with torch.cuda.device(v.device):
+        with _device_guard(v.device):
             L.check(_lib.brute_b200_binary_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                                          B, H, S, D, int(bool(causal)), float(scale), _stream(v)),
                     "binary_attention")

@@ -87,6 +87,25 @@ def _packed_bin(code: int, pa: torch.Tensor, pb: torch.Tensor, last_bits: int) -
     return _ops.bit1_not_packed(torch.bitwise_xor(pa, pb), last_bits)
 
 
+def _arg_leaves(args, kwargs) -> list:
+    """Leaves of a call's arguments. Nearly every call has tensors and scalars at the top level or
+    one list deep; walking those by hand costs a microsecond where the general tree flattener
+    costs twenty. Anything nested deeper (or a dict) goes to the general one."""
+    out = []
+    for a in args if not kwargs else (*args, *kwargs.values()):
+        if isinstance(a, (list, tuple)):
+            for b in a:
+                if isinstance(b, (list, tuple, dict)):
+                    out.extend(torch.utils._pytree.tree_leaves(b))
+                else:
+                    out.append(b)
+        elif isinstance(a, dict):
+            out.extend(torch.utils._pytree.tree_leaves(a))
+        else:
+            out.append(a)
+    return out
+
+
 def _rebuild_brute_tensor(plain_tensor: torch.Tensor, is_bit1: bool = False):
     """Pickle hook: rebuild from the (bool or plain) base tensor."""
     t = plain_tensor.as_subclass(Tensor)
@@ -162,7 +181,8 @@ class Tensor(torch.Tensor):
             # One byte of storage broadcast to the logical shape: a lazy result that is never read
             # as bool costs no memory (the reference allocates a full bool tensor here,
             # brute/tensor.py:316, 1 GiB at 2^30 bits). _ensure_bool_valid swaps real storage in.
-            bool_t = torch.empty((), dtype=torch.bool, device=packed.device).expand(list(logical_shape))
+            shape = tuple(logical_shape)
+            bool_t = torch.empty_strided(shape, (0,) * len(shape), dtype=torch.bool, device=packed.device)
         else:
             assert bool_view.dtype == torch.bool, "bool_view must be torch.bool"
             bool_t = _plain(bool_view)
@@ -354,25 +374,71 @@ class Tensor(torch.Tensor):
         return _unpack_pm1(self._packed_buf_contig(), list(self.shape))
 
     # ----------------------------------------------- packed binary operators
+    # The operators are the per-op hot path of the front end (a few microseconds of kernel): they
+    # read shapes and versions from the plain alias (one as_subclass) instead of through
+    # __torch_function__, which costs a round trip per attribute.
+    def _packed_fast(self, plain: torch.Tensor) -> torch.Tensor:
+        """``self._packed_buf`` given the plain alias of ``self``."""
+        d = self.__dict__
+        cache = d.get("_packed_buf_cache")
+        if cache is not None and (d.get("_bool_dirty", False) or d.get("_packed_ver") == plain._version):
+            return cache
+        return self._packed_buf
+
+    def _bin_operands(self, other):
+        """(packed self, packed other, shape) when both are bit1 of one shape with >= 1 dim, else None."""
+        if not (self.__dict__.get("_is_bit1", False) and isinstance(other, Tensor)
+                and other.__dict__.get("_is_bit1", False)):
+            return None
+        ps, po = self.as_subclass(torch.Tensor), other.as_subclass(torch.Tensor)
+        shape = ps.shape
+        if len(shape) == 0 or shape != po.shape:
+            return None
+        return self._packed_fast(ps), other._packed_fast(po), shape
+
     def _same_shape_b1(self, other) -> bool:
-        return (_is_b1(self) and _is_b1(other) and self.shape == other.shape and self.dim() >= 1)
+        return self._bin_operands(other) is not None
 
     def _bin_new(self, other, code: int) -> "Tensor":
-        return Tensor._make_bit1_from_packed(
-            _packed_bin(code, self._packed_buf, other._packed_buf, int(self.shape[-1])), list(self.shape))
+        pa, pb, shape = self._bin_operands(other)
+        return Tensor._make_bit1_from_packed(_packed_bin(code, pa, pb, shape[-1]), shape)
 
     def _bin_inplace(self, other, code: int) -> "Tensor":
-        self._mark_packed_only(_packed_bin(code, self._packed_buf, other._packed_buf, int(self.shape[-1])))
+        pa, pb, shape = self._bin_operands(other)
+        self._mark_packed_only(_packed_bin(code, pa, pb, shape[-1]))
         return self
 
     def __and__(self, other):
-        return self._bin_new(other, _OP_AND) if self._same_shape_b1(other) else super().__and__(other)
+        ops = self._bin_operands(other)
+        if ops is None:
+            return super().__and__(other)
+        return Tensor._make_bit1_from_packed(_packed_bin(_OP_AND, ops[0], ops[1], ops[2][-1]), ops[2])
 
     def __or__(self, other):
-        return self._bin_new(other, _OP_OR) if self._same_shape_b1(other) else super().__or__(other)
+        ops = self._bin_operands(other)
+        if ops is None:
+            return super().__or__(other)
+        return Tensor._make_bit1_from_packed(_packed_bin(_OP_OR, ops[0], ops[1], ops[2][-1]), ops[2])
 
     def __xor__(self, other):
-        return self._bin_new(other, _OP_XOR) if self._same_shape_b1(other) else super().__xor__(other)
+        ops = self._bin_operands(other)
+        if ops is None:
+            return super().__xor__(other)
+        return Tensor._make_bit1_from_packed(_packed_bin(_OP_XOR, ops[0], ops[1], ops[2][-1]), ops[2])
+
+    def __eq__(self, other):
+        ops = self._bin_operands(other) if isinstance(other, Tensor) else None
+        if ops is None:
+            return super().__eq__(other)
+        return Tensor._make_bit1_from_packed(_packed_bin(_OP_XNOR, ops[0], ops[1], ops[2][-1]), ops[2])
+
+    def __ne__(self, other):
+        ops = self._bin_operands(other) if isinstance(other, Tensor) else None
+        if ops is None:
+            return super().__ne__(other)
+        return Tensor._make_bit1_from_packed(_packed_bin(_OP_XOR, ops[0], ops[1], ops[2][-1]), ops[2])
+
+    __hash__ = torch.Tensor.__hash__
 
     def __iand__(self, other):
         return self._bin_inplace(other, _OP_AND) if self._same_shape_b1(other) else super().__iand__(other)
@@ -384,9 +450,12 @@ class Tensor(torch.Tensor):
         return self._bin_inplace(other, _OP_XOR) if self._same_shape_b1(other) else super().__ixor__(other)
 
     def __invert__(self):
-        if _is_b1(self) and self.dim() >= 1:
-            return Tensor._make_bit1_from_packed(
-                _ops.bit1_not_packed(self._packed_buf, int(self.shape[-1])), list(self.shape))
+        if self.__dict__.get("_is_bit1", False):
+            plain = self.as_subclass(torch.Tensor)
+            shape = plain.shape
+            if len(shape) >= 1:
+                return Tensor._make_bit1_from_packed(
+                    _ops.bit1_not_packed(self._packed_fast(plain), shape[-1]), shape)
         return super().__invert__()
 
     # -------------------------------------------------------------- indexing
@@ -528,8 +597,9 @@ class Tensor(torch.Tensor):
         """Number of positions where self and other differ, 0-dim int64."""
         if not (_is_b1(self) and _is_b1(other)):
             raise TypeError("hamming() is only defined for bit1 tensors")
-        if self.shape != other.shape:
-            raise ValueError(f"hamming() requires matching shapes; got {tuple(self.shape)} vs {tuple(other.shape)}")
+        sa, sb = self.as_subclass(torch.Tensor).shape, other.as_subclass(torch.Tensor).shape
+        if sa != sb:
+            raise ValueError(f"hamming() requires matching shapes; got {tuple(sa)} vs {tuple(sb)}")
         return Tensor._make_plain(_ops.bit1_hamming_total(self._packed_buf_contig(), other._packed_buf_contig()))
 
     def word_popcount(self) -> "Tensor":
@@ -696,8 +766,9 @@ class Tensor(torch.Tensor):
         """Transpose that moves the packed axis: a bool view, packed lazily; a 2-D
         one remembers its source for the matmul fast path."""
         self._ensure_bool_valid()
-        inst = Tensor._make_bit1(_plain(self).transpose(d0, d1), lazy_pack=True)
-        nd = self.dim()
+        plain = self.as_subclass(torch.Tensor)
+        inst = Tensor._make_bit1(plain.transpose(d0, d1), lazy_pack=True)
+        nd = plain.dim()
         if {d0, d1} == {nd - 2, nd - 1}:
             inst.__dict__["_t_source"] = self
         return inst
@@ -719,9 +790,10 @@ class Tensor(torch.Tensor):
         return super().transpose(dim0, dim1)
 
     def t(self) -> "Tensor":
-        if not _is_b1(self):
-            return Tensor._make_plain(_plain(self).t())
-        if self.dim() < 2:
+        plain = self.as_subclass(torch.Tensor)
+        if not self.__dict__.get("_is_bit1", False):
+            return Tensor._make_plain(plain.t())
+        if plain.dim() < 2:
             return self
         return self._transposed_with_source(0, 1)
 
@@ -785,15 +857,16 @@ class Tensor(torch.Tensor):
     @staticmethod
     def _matmul_bit1(a: "Tensor", b: "Tensor"):
         """A (M,K) @ B with B stored (N,K), or B = src.t() with src stored (N,K)."""
-        if not (a.dim() == 2 and b.dim() == 2):
+        sa, sb = a.as_subclass(torch.Tensor).shape, b.as_subclass(torch.Tensor).shape
+        if not (len(sa) == 2 and len(sb) == 2):
             return NotImplemented
-        K = int(a.shape[-1])
-        if int(b.shape[-1]) == K:
+        K = sa[-1]
+        if sb[-1] == K:
             pa, pb = a._packed_buf_contig(), b._packed_buf_contig()
             if pa.shape[-1] == pb.shape[-1]:
                 return _ops.xnor_popcount_matmul(pa, pb, K)
         src = b.__dict__.get("_t_source")
-        if _is_b1(src) and int(src.shape[-1]) == K:
+        if _is_b1(src) and src.as_subclass(torch.Tensor).shape[-1] == K:
             pa, ps = a._packed_buf_contig(), src._packed_buf_contig()
             if pa.shape[-1] == ps.shape[-1]:
                 return _ops.xnor_popcount_matmul(pa, ps, K)
@@ -819,7 +892,7 @@ class Tensor(torch.Tensor):
             with torch._C.DisableTorchFunctionSubclass():
                 return args[0]._base
 
-        flat = torch.utils._pytree.tree_leaves((list(args), list(kwargs.values())))
+        flat = _arg_leaves(args, kwargs)
         bit1_ins = [x for x in flat if _is_b1(x)]
         if not bit1_ins:
             with torch._C.DisableTorchFunctionSubclass():
@@ -1053,17 +1126,17 @@ _BIN_CODES = {
 
 @_fast(*_BIN_CODES.keys())
 def _h_binary(func, args, kwargs, b1):
-    if len(b1) >= 2 and len(args) >= 2 and _is_b1(args[0]) and _is_b1(args[1]) and not kwargs:
-        a, b = args[0], args[1]
-        if a.shape == b.shape and a.dim() >= 1:
-            return a._bin_new(b, _BIN_CODES[func])
+    if len(b1) >= 2 and len(args) >= 2 and not kwargs and isinstance(args[0], Tensor):
+        ops = args[0]._bin_operands(args[1])
+        if ops is not None:
+            return Tensor._make_bit1_from_packed(_packed_bin(_BIN_CODES[func], ops[0], ops[1], ops[2][-1]), ops[2])
     return NotImplemented
 
 
 @_fast(torch.bitwise_not, torch.logical_not, torch.Tensor.bitwise_not, torch.Tensor.logical_not,
        torch.Tensor.__invert__)
 def _h_not(func, args, kwargs, b1):
-    if len(b1) == 1 and b1[0].dim() >= 1 and not kwargs:
+    if len(b1) == 1 and not kwargs and b1[0].as_subclass(torch.Tensor).dim() >= 1:
         return b1[0].__invert__()
     return NotImplemented
 
