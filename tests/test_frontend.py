@@ -128,6 +128,30 @@ def test_bitwise_parity_with_bool(brute, shape):
     assert torch.equal(a, a.clone()) and (not torch.equal(a, ~a) or a.numel() == 0)
 
 
+def test_operator_fast_paths_fall_back(brute):
+    # ==, !=, ^, &, | skip __torch_function__ for two bit1 tensors of one shape; everything else
+    # (scalars, plain bool tensors, broadcasting, 0-dim) must take the general path and agree with torch
+    sa, sb = rnd((3, 70), 5), rnd((3, 70), 6)
+    a, b = b1(brute, sa), b1(brute, sb)
+    assert (a != b).dtype == brute.bit1 and same(as_bool(a != b), sa != sb)
+    assert same(as_bool(a == b), sa == sb)
+    row = b1(brute, sb[0])                                  # broadcast: general path
+    assert same(as_bool(a ^ row), sa ^ sb[0]) and same(as_bool(a == row), sa == sb[0])
+    plain = sb.clone()                                      # a plain bool operand does not promote
+    assert same(cpu(a == plain), sa == sb) and same(cpu(a & plain), sa & sb)
+    assert same(cpu(a == True), sa == True)                 # noqa: E712  (scalar comparison)
+    z0, z1 = b1(brute, sa[0, 0]), b1(brute, sb[0, 0])       # 0-dim
+    assert bool(cpu(z0 == z1)) == bool(sa[0, 0] == sb[0, 0])
+    assert hash(a) == hash(a) and a in [a] and len({a: 1, b: 2}) == 2   # defining __eq__ kept the hash
+    # nested and keyword arguments reach the handlers through the hand-rolled flattener
+    assert same(as_bool(torch.cat([a, b], dim=0)), torch.cat([sa, sb], dim=0))
+    assert same(as_bool(torch.stack((a, b))), torch.stack((sa, sb)))
+    assert same(as_bool(torch.where(condition=a, input=b, other=a)), torch.where(sa, sb, sa))
+    assert same(as_bool(torch.cat(tensors=[a, b], dim=1)), torch.cat([sa, sb], dim=1))
+    parts = torch.split(a, [1, 2], dim=0)
+    assert same(as_bool(parts[1]), sa[1:])
+
+
 def test_invert_pad_safe_sizes(brute):
     for n in [1, 7, 8, 9, 31, 32, 33, 63, 64, 65, 1003, 4096]:
         src = rnd((n,), n)
