@@ -260,33 +260,23 @@ __device__ __forceinline__ uint32_t row_bits16_short(const uint64_t* rowp, int64
 
 // ELEM = bytes per output element (1: bool byte, 4: float +-1). A lane owns one
 // 16-byte ALIGNED group of the output, i.e. EPG = 16/ELEM elements.
-// groups a lane writes per task
-#ifndef BRUTE_UNPACK_GPL
-#define BRUTE_UNPACK_GPL 2
-#endif
-template <int ELEM> constexpr int UNPACK_GPL = ELEM == 1 ? BRUTE_UNPACK_GPL : 1;
-
 template <int ELEM, bool FLAT>
 // 8 blocks per SM (32 registers): this kernel mostly writes, and measured 17 % faster at full
 // occupancy than with the deeper unrolling the compiler picks when given more registers
-__global__ void __launch_bounds__(256, (ELEM == 1 && BRUTE_UNPACK_GPL > 1) ? 6 : 8)
+__global__ void __launch_bounds__(256, 8)
 k_unpack(const uint64_t* __restrict__ in, uint8_t* __restrict__ out,
          int64_t ll, int64_t wpr, TaskMap tm, int64_t tasks) {
     constexpr int EPG = 16 / ELEM;
-    constexpr int GPL = UNPACK_GPL<ELEM>;            // 16-byte groups per lane and task, GPL * 32 apart... see below
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t task = warp; task < tasks; task += nwarps) {
         int64_t r, c;
         split_task<FLAT>(task, tm, r, c);
+        const int64_t g = c * 32 + lane;
         const uint64_t* rowp = in + r * wpr;
         uint8_t* orow = out + r * ll * ELEM;
         const int m = (int)(reinterpret_cast<uintptr_t>(orow) & 15u) / ELEM;   // elements
-#pragma unroll
-      for (int k = 0; k < GPL; ++k) {
-        // the task's k-th run of 32 groups: a warp store still covers 512 contiguous bytes
-        const int64_t g = (c * GPL + k) * 32 + lane;
         const int64_t col0 = g * EPG - m;            // first element of this lane's group
         if (col0 >= ll || col0 + EPG <= 0) continue;
         if (col0 >= 0 && col0 + EPG <= ll) {
@@ -317,7 +307,6 @@ k_unpack(const uint64_t* __restrict__ in, uint8_t* __restrict__ out,
                 else reinterpret_cast<float*>(orow)[col] = bit ? 1.0f : -1.0f;
             }
         }
-      }
     }
 }
 
@@ -421,7 +410,7 @@ static int launch_unpack(const uint64_t* in, void* out, int64_t rows, int64_t ll
     constexpr int EPG = 16 / ELEM;
     // groups per row: the row may start up to EPG-1 elements into its first group
     const int64_t gpr = (fll + 2 * EPG - 2) / EPG;
-    const int64_t cpr = (gpr + 32 * UNPACK_GPL<ELEM> - 1) / (32 * UNPACK_GPL<ELEM>);
+    const int64_t cpr = (gpr + 31) / 32;
     const int64_t tasks = frows * cpr;
     const TaskMap tm = make_task_map(cpr, tasks);
     const int grid = stream_grid(tasks, 8, 8);
