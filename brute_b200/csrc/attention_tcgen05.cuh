@@ -90,7 +90,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                                const uint64_t* __restrict__ Qp, const uint64_t* __restrict__ Kp,
                                __nv_bfloat16* __restrict__ O,
                                int64_t S, int causal, float neg2c_log2 /* -2*scale*log2(e) */, float bias_log2,
-                               int64_t q_tiles) {
+                               int64_t q_tiles, int qt_major_flag) {
     extern __shared__ uint8_t ax_smem_raw[];
     __shared__ int s_skip;
     if (threadIdx.x == 0) s_skip = *(volatile int*)&g_tc_status;
@@ -122,8 +122,13 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     // through a shuffle so that the compiler knows the warp index, and with it every role branch
     // below, to be the same for all lanes of a warp
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const int64_t qt = q_tiles - 1 - (int64_t)blockIdx.x;          // heavy (late) causal tiles first
-    const int64_t bh = blockIdx.y;
+    // Heavy (late) causal tiles first. grid = (q_tiles, heads): head by head, so that the CTAs in
+    // flight share few heads' K and V in L2. grid = (heads, q_tiles) is the launcher's choice when
+    // all heads' K and V fit in L2 together: then the heavy tiles of ALL heads go first and the light
+    // ones fill the tail (few heads per GPU: 3.5 waves otherwise end half empty).
+    const bool head_major = qt_major_flag == 0;
+    const int64_t qt = q_tiles - 1 - (int64_t)(head_major ? blockIdx.x : blockIdx.y);
+    const int64_t bh = head_major ? blockIdx.y : blockIdx.x;
     const int64_t q0 = qt * AX_BM;
     const int64_t kend = causal ? (q0 + AX_BM < S ? q0 + AX_BM : S) : S;
     const int32_t ntiles = (int32_t)((kend + AX_BN - 1) / AX_BN);  // >= 1 because q0 < S
@@ -427,9 +432,11 @@ static int ax_run(const uint64_t* Qp, const uint64_t* Kp, const void* V, void* O
     BB_REQUIRE(S < (1ll << 31) - AX_BM && ax_make_v_map(&tmV, V, BH, S, D), BRUTE_ERR_DRIVER);
     if (!kernel_smem_ready<k_binary_attention_fwd_tcgen05<D>>(AX_SMEM)) return BRUTE_ERR_LAUNCH;
     const int64_t q_tiles = (S + AX_BM - 1) / AX_BM;
-    const dim3 grid((unsigned)q_tiles, (unsigned)BH);
+    // K + V of all heads against a third of the L2 (126 MB): see the kernel's tile order
+    const bool qt_major = causal && q_tiles <= 65535 && BH * S * (int64_t)(2 * D + D / 4) <= (80ll << 20);
+    const dim3 grid = qt_major ? dim3((unsigned)BH, (unsigned)q_tiles) : dim3((unsigned)q_tiles, (unsigned)BH);
     k_binary_attention_fwd_tcgen05<D><<<grid, AX_THREADS, AX_SMEM, st>>>(tmV, Qp, Kp, static_cast<__nv_bfloat16*>(O), S, causal,
-                                                                       neg2c_log2, bias_log2, q_tiles);
+                                                                       neg2c_log2, bias_log2, q_tiles, qt_major ? 1 : 0);
     return launch_status();
 }
 
