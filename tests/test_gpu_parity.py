@@ -591,14 +591,17 @@ def test_attention_kernels_agree(ops, co, monkeypatch, S, causal, scale, D):
     assert status_ok()
 
 
-def test_attention_repeatable_under_load(ops):
+@pytest.mark.parametrize("B,D", [(8, 128), (1, 128), (2, 64)])
+def test_attention_repeatable_under_load(ops, B, D):
     # no atomics anywhere in the kernel: 30 launches of BASELINE config 5 must agree bit for bit
-    # (a buffer handed over too early in the TMEM / shared-memory pipeline would show up here)
+    # (a buffer handed over too early in the TMEM / shared-memory pipeline would show up here).
+    # B = 8: tiles ordered head by head; B = 1 (one rank's share on 8 GPUs): all heads' K and V
+    # fit in L2 and the tiles are ordered heavy-first across the heads; D = 64: the other instance.
     import brute_b200 as brute
     g = gen(8)
-    q = brute.pack_sign(torch.randn((8, 32, 4096, 128), generator=g).to(DEV), ge0=True)
-    k = brute.pack_sign(torch.randn((8, 32, 4096, 128), generator=g).to(DEV), ge0=True)
-    v = torch.randn((8, 32, 4096, 128), generator=g).to(torch.bfloat16).to(DEV)
+    q = brute.pack_sign(torch.randn((B, 32, 4096, D), generator=g).to(DEV), ge0=True)
+    k = brute.pack_sign(torch.randn((B, 32, 4096, D), generator=g).to(DEV), ge0=True)
+    v = torch.randn((B, 32, 4096, D), generator=g).to(torch.bfloat16).to(DEV)
     ref = brute.binary_attention(q, k, v, causal=True)
     for it in range(30):
         assert torch.equal(brute.binary_attention(q, k, v, causal=True), ref), f"launch {it}"
