@@ -159,9 +159,10 @@ __device__ __forceinline__ bool tc_expander_steps(ExpanderCtx& cx, int32_t i0, i
 template <bool PACK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    int64_t M, int64_t N, int32_t nkb /* 128-bit k-blocks */, int32_t klogical /* K */,
+                    int64_t M, int64_t N, int32_t nkb_all /* 128-bit k-blocks */, int32_t klogical /* K */,
                     int32_t* __restrict__ C, int64_t ldc,
-                    const float* __restrict__ scale, uint32_t* __restrict__ out32, int64_t halves_per_row, int mode) {
+                    const float* __restrict__ scale, uint32_t* __restrict__ out32, int64_t halves_per_row, int mode,
+                    int32_t nkb_split /* k-blocks per blockIdx.z (a multiple of 4), or nkb_all */) {
     extern __shared__ uint8_t tc_smem_raw[];
     __shared__ int s_skip;
     if (threadIdx.x == 0) s_skip = *(volatile int*)&g_tc_status;
@@ -193,6 +194,10 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // a shuffle result: known to the compiler as the same in all lanes
     const int64_t m0 = (int64_t)blockIdx.y * TC_BM, n0 = (int64_t)blockIdx.x * TC_BN;
+    // split K (gridDim.z > 1, int32 output only): this CTA contracts k-blocks [kb0, kb0 + nkb) and ADDS its
+    // part of C to memory that the launcher has zeroed; integer sums do not depend on the order
+    const int32_t kb0 = (int32_t)blockIdx.z * nkb_split;
+    const int32_t nkb = nkb_all - kb0 < nkb_split ? nkb_all - kb0 : nkb_split;
     const int32_t nstages = (nkb + TC_KB_PER_STAGE - 1) / TC_KB_PER_STAGE;
 
     if (tid < TC_BM + TC_BN) pa_s[tid] = 0;
@@ -225,8 +230,8 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 ok = mbar_wait(p_empty(s), ((st / TC_PSTAGES) & 1) ^ 1, abort_flag, 1);
                 if (!ok) break;
                 mbar_expect_tx(p_full(s), TC_P_STAGE);
-                tma_load_2d(p_ring + s * TC_P_STAGE, &tmA, st * TC_PK, (int32_t)m0, p_full(s));
-                tma_load_2d(p_ring + s * TC_P_STAGE + TC_P_A, &tmB, st * TC_PK, (int32_t)n0, p_full(s));
+                tma_load_2d(p_ring + s * TC_P_STAGE, &tmA, kb0 * 16 + st * TC_PK, (int32_t)m0, p_full(s));
+                tma_load_2d(p_ring + s * TC_P_STAGE + TC_P_A, &tmB, kb0 * 16 + st * TC_PK, (int32_t)n0, p_full(s));
                 issued = st + 1;
             }
             if (!ok) {
@@ -318,7 +323,7 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int quarter = warp & 3, cblock = warp >> 2;     // 16 warps: 4 lane quarters x 4 blocks of 64 columns
             const int64_t m = m0 + quarter * 32 + lane;
             // C = K - 2*(pa + pb) + 4*popcount(a & b), popcount(a & b) = acc >> 7
-            const int32_t row_term = klogical - 2 * pa_s[quarter * 32 + lane];
+            const int32_t row_term = (blockIdx.z == 0 ? klogical : 0) - 2 * pa_s[quarter * 32 + lane];
 #pragma unroll 1
             for (int cc = 0; cc < 2; ++cc) {
                 const int col = cblock * 64 + cc * 32;
@@ -332,7 +337,11 @@ k_xnor_gemm_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 const int64_t n = n0 + col;
                 if (!PACK) {
-                    if (m < M) {
+                    if (m < M && gridDim.z > 1) {
+                        int32_t* dst = C + m * ldc + n;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (n + j < N) atomicAdd(dst + j, (int32_t)v[j]);
+                    } else if (m < M) {
                         int32_t* dst = C + m * ldc + n;
                         if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
@@ -396,11 +405,32 @@ static int tc5_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, i
     const int32_t klogical = (int32_t)K;
     if (!pack) {
         if (!kernel_smem_ready<k_xnor_gemm_tcgen05<false>>(TC_SMEM)) return BRUTE_ERR_LAUNCH;
-        k_xnor_gemm_tcgen05<false><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, klogical, C, ldc, nullptr, nullptr, 0, 0);
+        // A handful of tiles with a long K (small batch against a wide layer) would leave most SMs
+        // idle behind one serial k loop per tile: split K over blockIdx.z until the CTAs about fill
+        // the GPU, at least 16 k-blocks each, and let the parts add up in the zeroed output. The
+        // zeroing and the atomic adds cost about as much as a two-way split saves, so only four-way
+        // and wider splits are taken (CUDA-graph replays: 128 x 4096 x 16384 50 -> 30 us,
+        // 64 x 1024 x 16384 48 -> 20 us; 1024 x 1024 x 4096 would go from 20 to 29 us two-way).
+        const int64_t tiles = (int64_t)grid.x * grid.y;
+        int64_t splits = tiles > 0 ? kNumSMs / tiles : 1;
+        if (splits > nkb / 16) splits = nkb / 16;
+        if (splits > 64) splits = 64;
+        if (splits >= 4) {
+            int32_t per = (int32_t)((nkb + splits - 1) / splits);
+            per = (per + TC_KB_PER_STAGE - 1) / TC_KB_PER_STAGE * TC_KB_PER_STAGE;
+            const unsigned gz = (unsigned)((nkb + per - 1) / per);
+            if (gz >= 2) {
+                if (cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, st) != cudaSuccess) return BRUTE_ERR_LAUNCH;
+                k_xnor_gemm_tcgen05<false><<<dim3(grid.x, grid.y, gz), TC_THREADS, TC_SMEM, st>>>(
+                    tmA, tmB, M, N, nkb, klogical, C, ldc, nullptr, nullptr, 0, 0, per);
+                return launch_status();
+            }
+        }
+        k_xnor_gemm_tcgen05<false><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, klogical, C, ldc, nullptr, nullptr, 0, 0, nkb);
     } else {
         if (!kernel_smem_ready<k_xnor_gemm_tcgen05<true>>(TC_SMEM)) return BRUTE_ERR_LAUNCH;
         k_xnor_gemm_tcgen05<true><<<grid, TC_THREADS, TC_SMEM, st>>>(tmA, tmB, M, N, nkb, klogical, nullptr, 0, scale,
-                                                                    reinterpret_cast<uint32_t*>(out), 2 * ((N + 63) / 64), mode);
+                                                                    reinterpret_cast<uint32_t*>(out), 2 * ((N + 63) / 64), mode, nkb);
     }
     return launch_status();
 }

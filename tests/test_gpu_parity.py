@@ -200,6 +200,31 @@ def status_ok():
     return L.load().brute_b200_device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 512, 4096), (128, 4096, 16384), (1, 256, 8192), (200, 300, 6400), (130, 700, 2048 + 128)])
+def test_gemm_split_k(ops, co, M, N, K):
+    # few tiles, long K: the one-CTA kernel splits K over blockIdx.z and the parts add up in the
+    # zeroed output (integer adds: still bit-exact). Through the C ABI with ldc > N, so that the
+    # columns past N must keep their sentinel (only the [M, N] block may be zeroed and written).
+    from brute_b200 import _lib as L
+    g = gen(M + N)
+    a = torch.randint(-2 ** 63, 2 ** 63 - 1, (M, K // 64), generator=g, dtype=torch.int64)
+    b = torch.randint(-2 ** 63, 2 ** 63 - 1, (N, K // 64), generator=g, dtype=torch.int64)
+    want = co.xnor_gemm(u64(a), u64(b), K)
+    ad, bd = a.to(DEV), b.to(DEV)
+    assert np.array_equal(ops.xnor_popcount_matmul(ad, bd, K).cpu().numpy(), want)
+    ldc = N + 12
+    c = torch.full((M, ldc), 7777, dtype=torch.int32, device=DEV)
+    rc = L.load().brute_b200_xnor_gemm(ad.data_ptr(), bd.data_ptr(), c.data_ptr(), M, N, K // 64, K, ldc,
+                                       L.GEMM_TCGEN05, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    got = c.cpu().numpy()
+    assert np.array_equal(got[:, :N], want) and (got[:, N:] == 7777).all()
+    for _ in range(20):                       # repeated launches into the same buffer
+        ops.xnor_popcount_matmul(ad, bd, K)
+    assert np.array_equal(ops.xnor_popcount_matmul(ad, bd, K).cpu().numpy(), want)
+    assert status_ok()
+
+
 def test_gemm_golden(ops, golden):
     for idx, (M, K, N) in enumerate(golden["gemm_cases"]):
         ap = torch.from_numpy(golden[f"gemm{idx}_ap"]).to(DEV)
