@@ -310,6 +310,35 @@ k_unpack(const uint64_t* __restrict__ in, uint8_t* __restrict__ out,
     }
 }
 
+// The flat, 32-byte aligned case of the two unpacks with 256-bit stores (sm_100): a lane turns 32 bits
+// into 32 bool bytes, or 8 bits into 8 floats, and a warp store covers 1 KB of contiguous output,
+// half the store instructions of the 16-byte form for this write-bound kernel. n32 = number of
+// 32-byte output groups.
+__device__ __forceinline__ void stg_stream_256(void* p, const uint32_t (&r)[8]) {
+    asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" :: "l"(p),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+
+template <int ELEM>
+__global__ void __launch_bounds__(256, 8)
+k_unpack_flat256(const uint32_t* __restrict__ in32, uint8_t* __restrict__ out, int64_t n32) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < n32; g += stride) {
+        uint32_t r[8];
+        if (ELEM == 1) {
+            const uint32_t bits = __ldg(in32 + g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = bits4_to_bytes01(bits >> (4 * i));
+        } else {
+            // 8 bits of the packed stream per lane: byte g of it
+            const uint32_t bits = __ldg(reinterpret_cast<const uint8_t*>(in32) + g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[i] = 0xBF800000u ^ (((bits >> i) & 1u) << 31);
+        }
+        stg_stream_256(out + g * 32, r);
+    }
+}
+
 // ---------------------------------------------------------------------------
 static inline void flatten_rows(int64_t& rows, int64_t& len) {
     // rows of a multiple of 64 bits pack back to back: treat as one long row
@@ -407,6 +436,12 @@ static int launch_unpack(const uint64_t* in, void* out, int64_t rows, int64_t ll
     int64_t frows = rows, fll = ll;
     int64_t fwpr = wpr;
     if (ll % 64 == 0 || rows == 1) { fll = ll * rows; frows = 1; fwpr = wpr * rows; }
+    if (frows == 1 && (reinterpret_cast<uintptr_t>(out) & 31u) == 0 && (fll * ELEM) % 32 == 0) {
+        const int64_t n32 = fll * ELEM / 32;
+        k_unpack_flat256<ELEM><<<stream_grid(n32, 256, 8), 256, 0, st>>>(reinterpret_cast<const uint32_t*>(in),
+                                                                      static_cast<uint8_t*>(out), n32);
+        return launch_status();
+    }
     constexpr int EPG = 16 / ELEM;
     // groups per row: the row may start up to EPG-1 elements into its first group
     const int64_t gpr = (fll + 2 * EPG - 2) / EPG;
