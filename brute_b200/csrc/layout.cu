@@ -127,7 +127,7 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, uint32_t src
                  :: "l"(tm), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
-constexpr int TB_TMA_SMEM = 2 * TB_TILE * 64 + 64 + 1024;
+constexpr int TB_TMA_SMEM = TB_TILE * 64 + 64 + 1024;     // ONE tile buffer: the transposed tile is staged over the input
 
 __global__ void __launch_bounds__(TB_THREADS)
 k_transpose_bits_tma(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmOut,
@@ -135,8 +135,11 @@ k_transpose_bits_tma(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
     extern __shared__ uint8_t tb_smem_raw[];
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(tb_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    const uint32_t in_s = base, out_s = base + TB_TILE * 64, bar = out_s + TB_TILE * 64;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tb_smem_raw + (base - raw) + 2 * TB_TILE * 64 + 8);
+    // The whole tile is in registers before anything is staged, so the output reuses the input's
+    // 32 KB (one barrier in between): half the shared memory, twice the CTAs per SM to overlap the
+    // load, butterfly and store phases of different tiles.
+    const uint32_t in_s = base, out_s = base, bar = base + TB_TILE * 64;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tb_smem_raw + (base - raw) + TB_TILE * 64 + 8);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t b = blockIdx.y;
     const int64_t grp = (int64_t)blockIdx.x >> 6;
@@ -172,6 +175,7 @@ k_transpose_bits_tma(const __grid_constant__ CUtensorMap tmIn, const __grid_cons
             hi[2 * c] = (uint64_t)vb.x | ((uint64_t)vb.y << 32); hi[2 * c + 1] = (uint64_t)vb.z | ((uint64_t)vb.w << 32);
         }
     }
+    __syncthreads();                 // every warp has read its rows: the buffer may be overwritten
 #pragma unroll
     for (int cb = 0; cb < TB_BLOCKS; ++cb) {
         transpose64x64(lo[cb], hi[cb], lane);
