@@ -1,9 +1,11 @@
-"""Build the CUDA library in-tree: ``python -m brute_b200.build``.
+"""Build the native parts in-tree: ``python -m brute_b200.build``.
 
-Compiles every ``csrc/*.cu`` for sm_100a only and links them into
-``brute_b200/libbrute_b200.so`` (a plain C-ABI shared library, no torch or
-Python types in it). nvcc cross-compiles without a GPU; objects are rebuilt only
-when a source or header is newer.
+* ``csrc/*.cu`` are compiled for sm_100a only and linked into ``brute_b200/libbrute_b200.so``
+  (a plain C-ABI shared library, no torch or Python types in it). nvcc cross-compiles without a
+  GPU; objects are rebuilt only when a source or header is newer.
+* ``csrc_host/cbrute.cpp`` becomes the Python extension module ``brute_b200/_cbrute.so`` (g++
+  against the installed torch): the front end's tensor-implementation helpers and the compiled
+  ``torch.ops.brute`` binding, which calls the C ABI of the library above.
 """
 from __future__ import annotations
 
@@ -19,6 +21,8 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 OBJ_DIR = PKG / "build"
 LIB = PKG / "libbrute_b200.so"
+HOST_SRC = PKG / "csrc_host" / "cbrute.cpp"
+HOST_MOD = PKG / "_cbrute.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -71,7 +75,33 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    build_host_module(force)
     return LIB
+
+
+def build_host_module(force: bool = False) -> Path:
+    """Compile ``_cbrute`` (pybind11 + torch headers, host code only) and link it to the library."""
+    deps = [HOST_SRC, *INCLUDE.glob("*.h")]
+    if not force and HOST_MOD.exists() and HOST_MOD.stat().st_mtime > max(d.stat().st_mtime for d in deps):
+        return HOST_MOD
+    import sysconfig
+    import torch
+    tdir = Path(torch.__file__).resolve().parent
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cuda_home = Path(_nvcc()).resolve().parent.parent
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-attributes",
+           "-DTORCH_EXTENSION_NAME=_cbrute", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           f"-I{tdir / 'include'}", f"-I{tdir / 'include' / 'torch' / 'csrc' / 'api' / 'include'}",
+           f"-I{sysconfig.get_paths()['include']}", f"-I{INCLUDE}", f"-I{cuda_home / 'include'}",
+           str(HOST_SRC), "-o", str(HOST_MOD),
+           f"-L{tdir / 'lib'}", "-lc10", "-lc10_cuda", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-ltorch_python",
+           f"-L{PKG}", "-l:libbrute_b200.so",
+           f"-Wl,-rpath,{tdir / 'lib'}", "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building _cbrute failed:\n{res.stdout}\n{res.stderr}")
+    return HOST_MOD
 
 
 if __name__ == "__main__":

@@ -94,7 +94,10 @@ extern "C" int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, u
                                            void* workspace, int64_t workspace_bytes, void* stream) {
     BB_REQUIRE(B >= 0 && M >= 0 && N >= 0 && Dp >= 0 && D >= 0 && D <= 64 * Dp, BRUTE_ERR_INVALID_ARG);
     if (B * M * Dp == 0) return BRUTE_OK;
-    if (!st_accepts(W, B, M, N, D))              // shapes outside the TMA rules: the CUDA-core kernel, no workspace
+    // Shapes outside the TMA rules take the CUDA-core kernel, no workspace. So do rows that are padded
+    // beyond ceil(D/64) words: the bit transpose reads V with a pitch of ceil(D/64) words per row, and
+    // the tensor path writes only that many words of every output row.
+    if (!st_accepts(W, B, M, N, D) || Dp != (D + 63) / 64)
         return brute_b200_signed_bundle(W, V, out, B, M, N, Dp, D, stream);
     BB_REQUIRE(out != nullptr && W != nullptr && V != nullptr, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(aligned8(V) && aligned8(out), BRUTE_ERR_MISALIGNED);
@@ -125,7 +128,7 @@ extern "C" int brute_b200_signed_bundle_static(const int8_t* W, const uint64_t* 
                                                void* stream) {
     BB_REQUIRE(B >= 0 && M >= 0 && N >= 0 && Dp >= 0 && D >= 0 && D <= 64 * Dp, BRUTE_ERR_INVALID_ARG);
     if (B * M * Dp == 0) return BRUTE_OK;
-    if (!st_accepts(W, B, M, N, D))              // the CUDA-core kernel uses no scratch, whatever the size
+    if (!st_accepts(W, B, M, N, D) || Dp != (D + 63) / 64)     // the CUDA-core kernel uses no scratch, whatever the size
         return brute_b200_signed_bundle(W, V, out, B, M, N, Dp, D, stream);
     const int64_t need = brute_b200_signed_bundle_workspace_bytes(B, N, D);
     BB_REQUIRE(need <= SB_STATIC_SCRATCH_BYTES, BRUTE_ERR_WORKSPACE);

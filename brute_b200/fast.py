@@ -18,7 +18,7 @@ _ops = torch.ops.brute
 # attribute read on the subclass itself is a __torch_function__ round trip.
 def _pk(t: Tensor):
     """(packed buffer, logical shape) of a bit1 tensor."""
-    plain = t.as_subclass(torch.Tensor)
+    plain = torch.Tensor.as_subclass(t, torch.Tensor)     # the raw one: no materialisation
     return t._packed_fast(plain), plain.shape
 
 

@@ -71,11 +71,42 @@ _GET_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
 def _stream(t: torch.Tensor) -> int:
     """The caller's current stream on the tensor's device, as the raw handle the C ABI takes.
     ``torch.cuda.current_stream`` builds a Stream object per call (a few microseconds, on an op
-    whose kernel may take as long); the raw handle comes straight from the runtime. While
-    ``parallel_streams`` has the public function replaced by its rotating one, that one is asked."""
-    if _RAW_STREAM is not None and torch.cuda.current_stream is _TORCH_CURRENT_STREAM:
+    whose kernel may take as long); the raw handle comes straight from the runtime. Inside a
+    ``parallel_streams`` block the op layer has already made the pool stream the real current
+    stream (``_rotated``), so the runtime's answer is the right one there too."""
+    if _RAW_STREAM is not None:
         return _RAW_STREAM(t.device.index)
-    return torch.cuda.current_stream(t.device).cuda_stream
+    return _TORCH_CURRENT_STREAM(t.device).cuda_stream
+
+
+def _guarded(name: str, fn):
+    """What every CUDA implementation gets before its body runs.
+
+    * Every tensor argument must be a CUDA tensor on the first one's device. The dispatcher picks the
+      CUDA key as soon as ONE argument is a CUDA tensor and the kernels take raw pointers: a host
+      pointer, or another GPU's, would fault the device where ATen and the reference raise.
+    * Inside a ``parallel_streams`` block the op runs on the block's next stream (streams.py).
+    """
+    from . import streams as _streams
+
+    def call(*args):
+        dev = None
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                if dev is None:
+                    dev = a.device
+                    if dev.type != "cuda":
+                        raise RuntimeError(f"{name}: expected CUDA tensors, got a tensor on {dev}")
+                elif a.device != dev:
+                    raise RuntimeError(f"{name}: expected all tensors to be on the same device, "
+                                       f"but found at least two devices, {dev} and {a.device}")
+        rot = _streams._ACTIVE
+        if rot is None:
+            return fn(*args)
+        return rot.run(fn, args)
+    call.__name__ = fn.__name__
+    call.__wrapped__ = fn
+    return call
 
 
 class _device_guard:
@@ -488,7 +519,7 @@ _CUDA_IMPLS = {
 }
 _IMPL = torch.library.Library("brute", "IMPL", "CUDA")
 for _name, _fn in _CUDA_IMPLS.items():
-    _IMPL.impl(_name, _fn)
+    _IMPL.impl(_name, _guarded(_name, _fn))
 
 
 # Shape-only kernels so that FakeTensor / torch.compile tracing sees the ops

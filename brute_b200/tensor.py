@@ -5,10 +5,11 @@ Same surface and laziness contract as the reference's ``brute/tensor.py``:
 * a bit1 tensor IS a ``torch.bool`` tensor (so every torch op has a meaning) that
   carries an int64-packed side buffer, 64 bits per word along the last axis,
   pad bits 0 (``_packed_buf``);
-* results of packed-domain ops are built from the packed buffer only; their bool
-  storage is a one-byte placeholder broadcast to the logical shape (``_bool_dirty``) until
-  something reads it (``_ensure_bool_valid``, reference brute/tensor.py:327-352, which
-  allocates the full bool tensor up front);
+* results of packed-domain ops are built from the packed buffer only (``_bool_dirty``); their
+  bool tensor has the logical sizes and contiguous strides over an EMPTY storage until something
+  reads it (``_ensure_bool_valid``; the reference, brute/tensor.py:288-352, allocates the full
+  bool tensor up front). Reading fills that same storage object, so views and plain aliases
+  taken before or after share it, as they do in the reference;
 * in-place writes to the bool storage are noticed through torch's version
   counter (``_packed_ver``) and re-pack lazily (brute/tensor.py:362-388);
 * a transpose of the last two dimensions remembers its source (``_t_source``) so that
@@ -30,6 +31,8 @@ from typing import Callable, Dict, List, Optional
 
 import torch
 
+from . import _cbrute
+from . import streams as _streams
 from .dtype import _PACK_STORAGE_DTYPE, _PACK_WIDTH, _Bit1DType, bit1
 
 _ops = torch.ops.brute
@@ -39,8 +42,23 @@ _OP_AND, _OP_OR, _OP_XOR, _OP_XNOR = 0, 1, 2, 3
 _SIGN_GT0, _SIGN_GE0 = 0, 1
 
 
+# The base class's as_subclass, which Tensor overrides (a dirty lazy tensor is materialised before a
+# caller gets a plain alias of it). Internal code reads shapes and versions through this one.
+_AS = torch.Tensor.as_subclass
+
+
 def _plain(t: torch.Tensor) -> torch.Tensor:
-    return t.as_subclass(torch.Tensor) if isinstance(t, Tensor) else t
+    return _AS(t, torch.Tensor) if isinstance(t, Tensor) else t
+
+
+def _join_streams() -> None:
+    """Inside a ``parallel_streams`` block the package's ops run on pool streams while plain torch ops
+    run on the caller's stream. Every front-end entry point that is about to hand packed or bool data
+    to a plain torch op calls this first: the caller's stream then waits for the pool work queued so
+    far. Entry points that only launch this package's kernels skip it (those are ordered by the
+    block's own events), which is what lets independent ops overlap."""
+    if _streams._ACTIVE is not None:
+        _streams._ACTIVE.join()
 
 
 def _is_b1(x) -> bool:
@@ -76,7 +94,7 @@ def _unpack_pm1(packed: torch.Tensor, logical_shape: list) -> torch.Tensor:
 
 def _packed_bin(code: int, pa: torch.Tensor, pb: torch.Tensor, last_bits: int) -> torch.Tensor:
     """Word-wise op on two packed buffers: one fused kernel on CUDA, ATen elsewhere."""
-    if pa.is_cuda and pa.shape == pb.shape:
+    if pa.is_cuda and pa.shape == pb.shape and pb.device == pa.device:
         return _ops.bitwise_packed(pa, pb, code, last_bits)
     if code == _OP_AND:
         return torch.bitwise_and(pa, pb)
@@ -178,11 +196,10 @@ class Tensor(torch.Tensor):
         bool storage is allocated uninitialised and marked dirty."""
         dirty = bool_view is None
         if dirty:
-            # One byte of storage broadcast to the logical shape: a lazy result that is never read
-            # as bool costs no memory (the reference allocates a full bool tensor here,
-            # brute/tensor.py:316, 1 GiB at 2^30 bits). _ensure_bool_valid swaps real storage in.
-            shape = tuple(logical_shape)
-            bool_t = torch.empty_strided(shape, (0,) * len(shape), dtype=torch.bool, device=packed.device)
+            # Logical sizes, contiguous strides, 0 bytes of storage: a lazy result that is never
+            # read as bool costs no memory (the reference allocates a full bool tensor here,
+            # brute/tensor.py:316, 1 GiB at 2^30 bits). _ensure_bool_valid fills the storage in place.
+            bool_t = _cbrute.lazy_bool(tuple(logical_shape), packed.device)
         else:
             assert bool_view.dtype == torch.bool, "bool_view must be torch.bool"
             bool_t = _plain(bool_view)
@@ -211,11 +228,15 @@ class Tensor(torch.Tensor):
                 unpacked = _ops.unpack_bool(src, [1]).reshape(())
             else:
                 unpacked = _ops.unpack_bool(src, shape)
-            if base.numel() > 1 and 0 in base.stride():
-                # the placeholder was a broadcast byte: adopt the real storage (on the tensor itself,
-                # not on the plain alias, which has its own sizes and strides)
-                torch.Tensor.set_(self, unpacked)
-                base = _plain(self)
+            _join_streams()          # bool storage is read by plain torch ops on the caller's stream
+            if base.numel() and base.untyped_storage().nbytes() == 0:
+                # still the empty placeholder: move the unpacked allocation into ITS storage object
+                # (no copy), so that every alias of this tensor sees the data
+                if len(shape) == 0:
+                    base.untyped_storage().resize_(1)
+                    base.copy_(unpacked)
+                else:
+                    _cbrute.adopt_storage(base, unpacked)
             else:
                 base.copy_(unpacked)
             ver = base._version
@@ -228,6 +249,13 @@ class Tensor(torch.Tensor):
         d["_packed_buf_cache"] = packed
         d["_bool_dirty"] = True
         d["_packed_ver"] = _plain(self)._version
+
+    def as_subclass(self, cls):
+        """A plain alias exposes the bool storage to the caller: fill it first if it is stale (the
+        reference hands out uninitialised memory here; an unread lazy result here owns none)."""
+        if self.__dict__.get("_bool_dirty", False):
+            self._ensure_bool_valid()
+        return _AS(self, cls)
 
     # ------------------------------------------------------------- properties
     @property
@@ -277,6 +305,7 @@ class Tensor(torch.Tensor):
         pb = self._packed_buf
         if pb is None or pb.is_contiguous():
             return pb
+        _join_streams()
         return pb.contiguous()
 
     def element_size(self) -> int:
@@ -360,6 +389,23 @@ class Tensor(torch.Tensor):
             explicit = kwargs.get("dtype")
             if explicit is None:
                 explicit = next((a for a in args if isinstance(a, torch.dtype)), None)
+            if explicit is None:
+                # a move between devices: carry the packed words (1/8 of the bytes) when they are
+                # current, and leave the bool view of the result lazy
+                d = self.__dict__
+                pb = d.get("_packed_buf_cache")
+                plain = _plain(self)
+                if (pb is not None and plain.dim() >= 1
+                        and (d.get("_bool_dirty", False) or d.get("_packed_ver") == plain._version)):
+                    try:
+                        probe = torch.empty(0, dtype=torch.bool, device=pb.device).to(*args, **kwargs)
+                    except Exception:                    # not a device-only request: the bool path decides
+                        probe = None
+                    if probe is not None and probe.dtype == torch.bool and probe.device != pb.device:
+                        _join_streams()
+                        return Tensor._make_bit1_from_packed(pb.contiguous().to(probe.device), list(plain.shape))
+                    # same device: the reference's path below (it also validates the bool view,
+                    # which its tests rely on: tests/unit/test_lazy_bool.py:85-90)
             self._ensure_bool_valid()
             moved = _plain(self).to(*args, **kwargs)
             if explicit is None and moved.dtype == torch.bool:
@@ -390,7 +436,7 @@ class Tensor(torch.Tensor):
         if not (self.__dict__.get("_is_bit1", False) and isinstance(other, Tensor)
                 and other.__dict__.get("_is_bit1", False)):
             return None
-        ps, po = self.as_subclass(torch.Tensor), other.as_subclass(torch.Tensor)
+        ps, po = _AS(self, torch.Tensor), _AS(other, torch.Tensor)
         shape = ps.shape
         if len(shape) == 0 or shape != po.shape:
             return None
@@ -451,7 +497,7 @@ class Tensor(torch.Tensor):
 
     def __invert__(self):
         if self.__dict__.get("_is_bit1", False):
-            plain = self.as_subclass(torch.Tensor)
+            plain = _AS(self, torch.Tensor)
             shape = plain.shape
             if len(shape) >= 1:
                 return Tensor._make_bit1_from_packed(
@@ -518,6 +564,7 @@ class Tensor(torch.Tensor):
         d["_packed_ver"] = _plain(self)._version
 
     def __getitem__(self, idx):
+        _join_streams()
         if self._leading_axis_fast(idx):
             packed = self._packed_buf
             if isinstance(idx, torch.Tensor):
@@ -528,31 +575,9 @@ class Tensor(torch.Tensor):
                 shape = list(self.shape[1:]) if isinstance(idx, int) else [sub.shape[0]] + list(self.shape[1:])
             if sub.numel() != 0:
                 return Tensor._make_bit1_from_packed(sub, shape)
-        sl = self._last_axis_slice(idx)
-        if sl is not None:
-            # x[..., a:b:s]: pick the bits in the packed domain
-            n = int(self.shape[-1])
-            pos = torch.arange(sl.start, sl.stop, sl.step, dtype=torch.int64, device=self.device)
-            if pos.numel() > 0:
-                out = _ops.gather_packed(self._packed_buf_contig(), pos, n)
-                return Tensor._make_bit1_from_packed(out, list(self.shape[:-1]) + [int(pos.numel())])
+        # x[..., a:b:s] is a view in torch (writes through it reach the base), so it takes the bool
+        # path like in the reference; index_select along the packed axis, which copies, stays packed
         return super().__getitem__(idx)
-
-    def _last_axis_slice(self, idx) -> Optional[range]:
-        """``range`` of the positions that ``idx`` keeps along the last axis when that is all it does
-        (``x[..., a:b:s]`` or ``x[:, :, a:b:s]`` with positive step), else None."""
-        if not _is_b1(self) or self.dim() < 1 or not isinstance(idx, tuple) or not idx:
-            return None
-        last = idx[-1]
-        if not isinstance(last, slice):
-            return None
-        lead = idx[:-1]
-        full = slice(None)
-        if lead == (Ellipsis,) or (len(lead) == self.dim() - 1 and all(isinstance(x, slice) and x == full for x in lead)):
-            if last == full or (last.step is not None and last.step <= 0):
-                return None
-            return range(*last.indices(int(self.shape[-1])))
-        return None
 
     def _row_pattern(self, value: bool) -> torch.Tensor:
         """One packed row of all-`value` bits with zero pad bits."""
@@ -566,6 +591,7 @@ class Tensor(torch.Tensor):
         return row
 
     def __setitem__(self, idx, value):
+        _join_streams()
         scalar = isinstance(value, (bool, int))
         if scalar and self._leading_axis_fast(idx) and not isinstance(idx, torch.Tensor):
             pb = self._packed_buf
@@ -597,7 +623,7 @@ class Tensor(torch.Tensor):
         """Number of positions where self and other differ, 0-dim int64."""
         if not (_is_b1(self) and _is_b1(other)):
             raise TypeError("hamming() is only defined for bit1 tensors")
-        sa, sb = self.as_subclass(torch.Tensor).shape, other.as_subclass(torch.Tensor).shape
+        sa, sb = _AS(self, torch.Tensor).shape, _AS(other, torch.Tensor).shape
         if sa != sb:
             raise ValueError(f"hamming() requires matching shapes; got {tuple(sa)} vs {tuple(sb)}")
         return Tensor._make_plain(_ops.bit1_hamming_total(self._packed_buf_contig(), other._packed_buf_contig()))
@@ -612,6 +638,7 @@ class Tensor(torch.Tensor):
         """Uniformly random bits in place; pad bits of every row stay 0."""
         if not _is_b1(self):
             raise TypeError("randomize_() is only defined for bit1 tensors")
+        _join_streams()
         pb = self._packed_buf.clone()
         _ops.randomize_bits(pb)
         K = int(self.shape[-1]) if self.dim() >= 1 else 0
@@ -624,6 +651,7 @@ class Tensor(torch.Tensor):
     # ------------------------------------------------- shape ops (methods)
     def _reshape_packed(self, new_shape: list) -> Optional["Tensor"]:
         """Reshape through the packed buffer when the last axis allows it."""
+        _join_streams()              # reshape of a strided packed view copies with a plain torch op
         total = self.numel()
         new_shape = [int(d) for d in new_shape]
         if new_shape.count(-1) == 1:
@@ -766,7 +794,7 @@ class Tensor(torch.Tensor):
         """Transpose that moves the packed axis: a bool view, packed lazily; a 2-D
         one remembers its source for the matmul fast path."""
         self._ensure_bool_valid()
-        plain = self.as_subclass(torch.Tensor)
+        plain = _AS(self, torch.Tensor)
         inst = Tensor._make_bit1(plain.transpose(d0, d1), lazy_pack=True)
         nd = plain.dim()
         if {d0, d1} == {nd - 2, nd - 1}:
@@ -790,7 +818,7 @@ class Tensor(torch.Tensor):
         return super().transpose(dim0, dim1)
 
     def t(self) -> "Tensor":
-        plain = self.as_subclass(torch.Tensor)
+        plain = _AS(self, torch.Tensor)
         if not self.__dict__.get("_is_bit1", False):
             return Tensor._make_plain(plain.t())
         if plain.dim() < 2:
@@ -841,6 +869,7 @@ class Tensor(torch.Tensor):
         return super().squeeze(*args, **kwargs)
 
     def clone(self, *, memory_format=torch.preserve_format):
+        _join_streams()
         if _is_b1(self) and self.dim() >= 1:
             return Tensor._make_bit1_from_packed(self._packed_buf.clone(), list(self.shape))
         return super().clone(memory_format=memory_format)
@@ -857,7 +886,7 @@ class Tensor(torch.Tensor):
     @staticmethod
     def _matmul_bit1(a: "Tensor", b: "Tensor"):
         """A (M,K) @ B with B stored (N,K), or B = src.t() with src stored (N,K)."""
-        sa, sb = a.as_subclass(torch.Tensor).shape, b.as_subclass(torch.Tensor).shape
+        sa, sb = _AS(a, torch.Tensor).shape, _AS(b, torch.Tensor).shape
         if not (len(sa) == 2 and len(sb) == 2):
             return NotImplemented
         K = sa[-1]
@@ -866,7 +895,7 @@ class Tensor(torch.Tensor):
             if pa.shape[-1] == pb.shape[-1]:
                 return _ops.xnor_popcount_matmul(pa, pb, K)
         src = b.__dict__.get("_t_source")
-        if _is_b1(src) and src.as_subclass(torch.Tensor).shape[-1] == K:
+        if _is_b1(src) and _AS(src, torch.Tensor).shape[-1] == K:
             pa, ps = a._packed_buf_contig(), src._packed_buf_contig()
             if pa.shape[-1] == ps.shape[-1]:
                 return _ops.xnor_popcount_matmul(pa, ps, K)
@@ -904,6 +933,8 @@ class Tensor(torch.Tensor):
 
         # packed-domain fast paths: only when no plain bool tensor is mixed in
         handler = _FAST.get(func)
+        if _streams._ACTIVE is not None and handler not in _KERNEL_ONLY_HANDLERS:
+            _streams._ACTIVE.join()
         if handler is not None and (not other_bools or func in _MATMUL_FUNCS):
             out = handler(func, args, kwargs, bit1_ins)
             if out is not NotImplemented:
@@ -1014,7 +1045,7 @@ _LAZY_VIEW_FUNCS = frozenset([
 
 
 def _plain_leaf(x):
-    return x.as_subclass(torch.Tensor) if isinstance(x, Tensor) else x
+    return _AS(x, torch.Tensor) if isinstance(x, Tensor) else x
 
 
 def _wrap_plain(out):
@@ -1136,7 +1167,7 @@ def _h_binary(func, args, kwargs, b1):
 @_fast(torch.bitwise_not, torch.logical_not, torch.Tensor.bitwise_not, torch.Tensor.logical_not,
        torch.Tensor.__invert__)
 def _h_not(func, args, kwargs, b1):
-    if len(b1) == 1 and not kwargs and b1[0].as_subclass(torch.Tensor).dim() >= 1:
+    if len(b1) == 1 and not kwargs and _AS(b1[0], torch.Tensor).dim() >= 1:
         return b1[0].__invert__()
     return NotImplemented
 
@@ -1316,21 +1347,20 @@ def _h_fill(func, args, kwargs, b1):
     if not isinstance(value, (bool, int)):
         return NotImplemented
     plain = _plain(a)
-    plain.copy_(torch.tensor(bool(value), dtype=torch.bool, device=plain.device).expand_as(plain))
-    K = int(a.shape[-1])
-    pb = a.__dict__.get("_packed_buf_cache")
-    want = list(a.shape[:-1]) + [_words(K)]
-    if pb is None or list(pb.shape) != want or not pb.is_contiguous():
-        pb = torch.empty(want, dtype=_PACK_STORAGE_DTYPE, device=plain.device)
-    if value:
-        pb.fill_(-1)
-        if K > 0 and K % _PACK_WIDTH:
-            pb[..., -1] = (1 << (K % _PACK_WIDTH)) - 1
-    else:
-        pb.zero_()
     d = a.__dict__
+    dirty = d.get("_bool_dirty", False)
+    if not dirty:
+        # the bool storage is live (maybe a strided view of another tensor): write it, so that
+        # aliases see the fill; the version bump tells their owners to re-pack
+        plain.fill_(bool(value))
+    K = int(a.shape[-1])
+    # always a fresh buffer: the old one may be shared with packed-domain views of this tensor
+    pb = torch.full(list(a.shape[:-1]) + [_words(K)], -1 if value else 0, dtype=_PACK_STORAGE_DTYPE,
+                    device=plain.device)
+    if value and K > 0 and K % _PACK_WIDTH:
+        pb[..., -1] = (1 << (K % _PACK_WIDTH)) - 1
+    # a packed-only tensor stays packed-only: nothing is allocated for a fill
     d["_packed_buf_cache"] = pb
-    d["_bool_dirty"] = False
     d["_packed_ver"] = plain._version
     return a
 
@@ -1447,5 +1477,8 @@ def _h_repeat_interleave(func, args, kwargs, b1):
                 return Tensor._make_bit1_from_packed(a._packed_buf.repeat_interleave(repeats, dim=d), shape)
     return NotImplemented
 
+
+# handlers that do nothing but launch this package's kernels on packed buffers (see _join_streams)
+_KERNEL_ONLY_HANDLERS = frozenset([_h_matmul, _h_sum, _h_binary, _h_not])
 
 __all__ = ["Tensor", "bit1"]

@@ -240,7 +240,8 @@ int brute_b200_signed_bundle(const int8_t* W, const uint64_t* V, uint64_t* out,
  * brute_b200_signed_bundle_workspace_bytes(B, N, D) bytes of device memory, 8-byte aligned; the
  * library allocates nothing, so the caller provides it (BRUTE_ERR_WORKSPACE if it is missing or too
  * small). Shapes the tensor path does not take (W not 16-byte aligned, N not a multiple of 16, N < 128,
- * M < 64) run the kernel of brute_b200_signed_bundle and ignore the workspace. Same reference lines. */
+ * M < 64, rows padded beyond ceil(D/64) words) run the kernel of brute_b200_signed_bundle and ignore the
+ * workspace. Same reference lines. */
 int64_t brute_b200_signed_bundle_workspace_bytes(int64_t B, int64_t N, int64_t D);
 int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, uint64_t* out,
                                 int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D,

@@ -386,17 +386,125 @@ def test_flip_roll_index_select_on_packed_axis(brute):
         assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
     with pytest.raises(IndexError):
         torch.index_select(b, -1, torch.tensor([131], device=DEV))
-    more = {
-        "slice": (b[..., 3:100], x[..., 3:100]), "slice_step": (b[:, :, 1::3], x[:, :, 1::3]),
-        "slice_neg": (b[..., -70:-1:2], x[..., -70:-1:2]),
-        "repeat_ragged": (b.repeat(2, 1, 3), x.repeat(2, 1, 3)),
-    }
-    for name, (got, want) in more.items():
+    rep = b.repeat(2, 1, 3)
+    assert rep.__dict__.get("_bool_dirty") is True, "repeat of a ragged last dim should stay packed"
+    assert same(as_bool(rep), x.repeat(2, 1, 3)) and int(rep.popcount()) == int(x.repeat(2, 1, 3).sum())
+    # a slice of the packed axis is a VIEW in torch (a write through it reaches the base), so it is a
+    # bool view here as in the reference (brute/tensor.py:846-853), not a packed-domain copy
+    for name, got, want in (("slice", b[..., 3:100], x[..., 3:100]), ("slice_step", b[:, :, 1::3], x[:, :, 1::3]),
+                            ("slice_neg", b[..., -70:-1:2], x[..., -70:-1:2])):
         assert got.dtype == brute.bit1 and tuple(got.shape) == tuple(want.shape), name
-        assert got.__dict__.get("_bool_dirty") is True, f"{name}: should stay in the packed domain"
         assert same(as_bool(got), want), name
         assert int(got.popcount()) == int(want.sum()), f"{name}: pad bits leaked"
     assert same(as_bool(b[..., 5:5]), x[..., 5:5])          # empty: the generic path
+
+
+# ---------------------------------------------------------------------------
+# a packed-only (lazy) result must behave like the reference's, which owns real bool storage
+# (brute/tensor.py:288-352): strides, in-place fills, aliasing; and it must cost no memory until read
+# ---------------------------------------------------------------------------
+def test_lazy_result_reports_contiguous_strides(brute):
+    # reference tests/unit/test_layout.py:46
+    z = brute.zeros((3, 4, 5), dtype=brute.bit1, device=DEV)
+    assert z.stride() == (20, 5, 1) and z.stride(0) == 20 and z.stride(-1) == 1
+    assert z.is_contiguous() and z.storage_offset() == 0
+    y = b1(brute, rnd((2, 1, 7), 3)) ^ b1(brute, rnd((2, 1, 7), 4))
+    assert y.__dict__["_bool_dirty"] is True
+    assert y.stride() == torch.empty((2, 1, 7)).stride()
+
+
+def test_fill_and_zero_on_a_lazy_result(brute):
+    # reference tests/unit/test_lazy_bool.py:142, tests/stress/test_cache_rebuilds.py:15,
+    # catalog specs fill_true / fill_false / zero_ (tests/ops_catalog.py:607-619)
+    for shape in ((64,), (3, 13), (2, 3, 65)):
+        a, c = rnd(shape, 31), rnd(shape, 32)
+        lazy = b1(brute, a) & b1(brute, c)
+        assert lazy.__dict__["_bool_dirty"] is True
+        out = lazy.fill_(True)
+        assert out is lazy and int(lazy.sum()) == lazy.numel()
+        assert lazy.__dict__["_bool_dirty"] is True, "a fill of a packed-only tensor must not allocate bool storage"
+        assert same(as_bool(lazy), torch.ones(shape, dtype=torch.bool))
+        lazy.fill_(False)
+        assert int(lazy.popcount()) == 0 and same(as_bool(lazy), torch.zeros(shape, dtype=torch.bool))
+        z = brute.ones(shape, dtype=brute.bit1, device=DEV)
+        z.zero_()
+        assert int(z.sum()) == 0 and same(as_bool(z), torch.zeros(shape, dtype=torch.bool))
+    x = brute.zeros(64, dtype=brute.bit1, device=DEV)
+    pb0 = x._packed_buf.clone()
+    x.fill_(True)
+    assert not torch.equal(pb0, x._packed_buf)
+    x.fill_(False)
+    assert torch.equal(pb0, x._packed_buf)
+
+
+def test_fill_through_a_view_reaches_the_base(brute):
+    # reference tests/unit/test_aliasing.py:15-18,44
+    base = brute.zeros((8, 8), dtype=brute.bit1, device=DEV)
+    view = base[:, ::2]
+    pa = cpu(base).untyped_storage().data_ptr()
+    assert cpu(view).untyped_storage().data_ptr() == pa or DEV == "cuda"
+    assert base.as_subclass(torch.Tensor).untyped_storage().data_ptr() == \
+        view.as_subclass(torch.Tensor).untyped_storage().data_ptr()
+    view.fill_(True)
+    want = torch.zeros((8, 8), dtype=torch.bool)
+    want[:, ::2] = True
+    assert same(as_bool(base), want) and int(base.popcount()) == 32
+    # the packed buffer of the base follows (version-tracked re-pack)
+    assert int(base.sum()) == 32
+
+
+def test_aliases_taken_before_materialisation_share_storage(brute):
+    a, c = rnd((5, 70), 41), rnd((5, 70), 42)
+    lazy = b1(brute, a) | b1(brute, c)
+    assert lazy.__dict__["_bool_dirty"] is True
+    plain_before = torch.Tensor.as_subclass(lazy, torch.Tensor)       # the raw alias: no materialisation
+    assert plain_before.untyped_storage().nbytes() == 0, "a lazy result must own no bool storage"
+    got = as_bool(lazy)                                               # materialises in place
+    assert same(got, a | c)
+    assert plain_before.untyped_storage().nbytes() == 5 * 70
+    assert torch.equal(plain_before.cpu(), (a | c).cpu()), "an alias taken before the read must see the data"
+    assert lazy.stride() == (70, 1)
+    # the public as_subclass hands out valid memory, never the empty placeholder
+    other = b1(brute, a) ^ b1(brute, c)
+    assert torch.equal(other.as_subclass(torch.Tensor).cpu(), (a ^ c).cpu())
+
+
+def test_large_lazy_result_allocates_no_bool_tensor(brute):
+    """2^30 bits: the operands are 128 MiB each; the lazy result may add its 128 MiB of packed words
+    but not the 1 GiB bool tensor the reference allocates (brute/tensor.py:316), not even briefly."""
+    if DEV != "cuda":
+        pytest.skip("needs the CUDA allocator's counters")
+    n = 1 << 30
+    g = torch.Generator(device="cuda").manual_seed(7)
+    pa = torch.randint(-2 ** 62, 2 ** 62, (n // 64,), dtype=torch.int64, device="cuda", generator=g)
+    pb = torch.randint(-2 ** 62, 2 ** 62, (n // 64,), dtype=torch.int64, device="cuda", generator=g)
+    a = brute.Tensor._make_bit1_from_packed(pa, [n])
+    b = brute.Tensor._make_bit1_from_packed(pb, [n])
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    before = torch.cuda.memory_allocated()
+    c = (a ^ b) & ~a
+    c.fill_(True)
+    pop = int(c.popcount())
+    torch.cuda.synchronize()
+    grown = torch.cuda.memory_allocated() - before
+    peak = torch.cuda.max_memory_allocated() - before
+    assert pop == n and c.__dict__["_bool_dirty"] is True
+    assert c.stride() == (1,) and c.shape == (n,)
+    assert grown <= (n // 8) + (1 << 20), f"a lazy result kept {grown} bytes"
+    assert peak <= 4 * (n // 8), f"peak {peak} bytes: a bool tensor of 2^30 bytes was allocated on the way"
+    # reading it as bool is what allocates
+    row = c[:8]
+    assert bool(row.all()) and torch.cuda.memory_allocated() - before >= n
+
+
+def test_clone_then_write_plain_alias_leaves_the_source_alone(brute):
+    # reference tests/unit/test_aliasing.py:65-72
+    x = brute.zeros(16, dtype=brute.bit1, device=DEV)
+    c = x.clone()
+    c.as_subclass(torch.Tensor).fill_(True)
+    assert same(as_bool(x), torch.zeros(16, dtype=torch.bool))
+    assert int(c.popcount()) == 16
 
 
 # ---------------------------------------------------------------------------

@@ -56,6 +56,83 @@ def test_parallel_streams_pool(brute):
         assert torch.equal(got.bool().as_subclass(torch.Tensor), want)
 
 
+def _bools(brute, shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    t = torch.rand(shape, device="cuda", generator=g) < 0.5
+    return t, brute.Tensor(t, dtype=brute.bit1)
+
+
+def test_parallel_streams_dependent_chain_and_freed_temporaries(brute):
+    """Inside the block every op runs on another stream. A chain must still see its producer's
+    result, and a temporary freed in the middle of the chain must not be handed to a later op while
+    its reader is still queued."""
+    shape = (2048, 4096 + 13)
+    xb, x = _bools(brute, shape, 1)
+    yb, y = _bools(brute, shape, 2)
+    zb, z = _bools(brute, shape, 3)
+    want = ((xb & yb) ^ zb) | ~xb
+    torch.cuda.synchronize()
+    for _ in range(20):
+        with brute.parallel_streams(4):
+            r = (x & y) ^ z                 # (x & y) is freed as soon as the xor is queued
+            r = r | ~x
+            junk = [(x ^ y) for _ in range(3)]      # same-size blocks the allocator can recycle
+            del junk
+            total = r.popcount()
+        assert int(total) == int(want.sum())
+        assert torch.equal(r.bool().as_subclass(torch.Tensor), want)
+
+
+def test_parallel_streams_with_plain_torch_ops_between(brute):
+    """randn -> pack_sign (a plain torch producer), and a plain torch consumer of a packed result."""
+    torch.cuda.synchronize()
+    for i in range(10):
+        with brute.parallel_streams(3):
+            f = torch.randn((1024, 2048), device="cuda")
+            b = brute.Tensor(f, dtype=brute.bit1)           # pack_sign on a pool stream
+            inv = ~b
+            words = torch.bitwise_and(inv._packed_buf, b._packed_buf)     # plain torch on the caller's stream
+            col = inv[:, 5]                                  # goes through the bool view
+        torch.cuda.synchronize()
+        assert torch.equal(b.bool().as_subclass(torch.Tensor), f > 0)
+        assert int(words.ne(0).sum()) == 0
+        assert torch.equal(col.bool().as_subclass(torch.Tensor), ~(f[:, 5] > 0))
+
+
+def test_parallel_streams_two_signed_bundles_in_a_row(brute):
+    """Both calls allocate a workspace; on different streams they must not share it."""
+    from oracle import c_oracle as co
+    g = torch.Generator().manual_seed(5)
+    W1 = torch.randint(-128, 128, (2, 128, 256), generator=g, dtype=torch.int64).to(torch.int8)
+    W2 = torch.randint(-128, 128, (2, 128, 256), generator=g, dtype=torch.int64).to(torch.int8)
+    v1 = torch.rand((2, 256, 128), generator=g) < 0.5
+    v2 = torch.rand((2, 256, 128), generator=g) < 0.5
+    p1, p2 = torch.ops.brute.pack_bool(v1.cuda()), torch.ops.brute.pack_bool(v2.cuda())
+    W1c, W2c = W1.cuda(), W2.cuda()
+    want1 = co.signed_bundle(W1.numpy(), co.pack_bool(v1.numpy()), 128)
+    want2 = co.signed_bundle(W2.numpy(), co.pack_bool(v2.numpy()), 128)
+    torch.cuda.synchronize()
+    for _ in range(10):
+        with brute.parallel_streams(2):
+            o1 = torch.ops.brute.signed_bundle(W1c, p1, 128)
+            o2 = torch.ops.brute.signed_bundle(W2c, p2, 128)
+        torch.cuda.synchronize()
+        assert np.array_equal(o1.cpu().numpy().view(np.uint64), want1)
+        assert np.array_equal(o2.cpu().numpy().view(np.uint64), want2)
+
+
+def test_parallel_streams_restores_the_current_stream(brute):
+    before = torch.cuda.current_stream()
+    x = brute.randint(0, 2, (64, 64), dtype=brute.bit1, device="cuda")
+    with brute.parallel_streams(2):
+        _ = x & x
+        with pytest.raises(RuntimeError):
+            torch.ops.brute.bitwise_packed(x._packed_buf, x._packed_buf.cpu(), 0, 64)   # mixed devices: raises, no launch
+        _ = x | x
+    assert torch.cuda.current_stream() == before
+    assert torch.cuda.current_stream is brute.streams._REAL_CURRENT_STREAM
+
+
 def test_cuda_graph_capture_replay(brute):
     M, K, N = 256, 1024, 512
     a = brute.randint(0, 2, (M, K), dtype=brute.bit1, device="cuda")

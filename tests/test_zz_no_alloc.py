@@ -43,7 +43,61 @@ def test_static_scratch_matches_workspace_entry_twice_in_a_row(lib_built):
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
         assert torch.equal(got, want), (B, M, N, D)
+        # the workspace entry shares the transpose and the kernel with the static one: the oracle
+        # is the independent check
+        from oracle import c_oracle as co
+        assert np.array_equal(got.cpu().numpy().view(np.uint64),
+                              co.signed_bundle(W.cpu().numpy(), vp.cpu().numpy().view(np.uint64), D)), (B, M, N, D)
     assert lib.brute_b200_device_status() == 0
+
+
+def test_static_scratch_rows_padded_beyond_the_logical_width(lib_built):
+    """V rows may carry more words than D needs (Dp > ceil(D/64)); the words past D are output as 0."""
+    import brute_b200  # noqa: F401
+    from brute_b200 import _lib as L
+    from oracle import c_oracle as co
+    lib = L.load()
+    st = torch.cuda.current_stream().cuda_stream
+    B, M, N, D, Dp = 2, 128, 256, 64, 2
+    g = torch.Generator().manual_seed(11)
+    W = torch.randint(-128, 128, (B, M, N), generator=g, dtype=torch.int64).to(torch.int8).to(DEV)
+    vp = torch.randint(-2 ** 62, 2 ** 62, (B, N, Dp), generator=g, dtype=torch.int64).to(DEV)   # junk in the padding word
+    want = co.signed_bundle(W.cpu().numpy(), vp.cpu().numpy().view(np.uint64), D)
+    ws = torch.empty(max(int(lib.brute_b200_signed_bundle_workspace_bytes(B, N, D)), 8) // 8, dtype=torch.int64, device=DEV)
+    for entry in ("static", "ws"):
+        got = torch.full((B, M, Dp), -1, dtype=torch.int64, device=DEV)
+        if entry == "static":
+            rc = lib.brute_b200_signed_bundle_static(W.data_ptr(), vp.data_ptr(), got.data_ptr(), B, M, N, Dp, D, st)
+        else:
+            rc = lib.brute_b200_signed_bundle_ws(W.data_ptr(), vp.data_ptr(), got.data_ptr(), B, M, N, Dp, D,
+                                                 ws.data_ptr(), ws.numel() * 8, st)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy().view(np.uint64), want), entry
+    assert np.array_equal(torch.ops.brute.signed_bundle(W, vp, D).cpu().numpy().view(np.uint64), want)
+
+
+def test_static_scratch_on_every_visible_device(lib_built):
+    """The array's address is looked up once per device, with that device current."""
+    import brute_b200  # noqa: F401
+    from brute_b200 import _lib as L
+    from oracle import c_oracle as co
+    lib = L.load()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    B, M, N, D = 2, 128, 512, 128
+    for dev in (1, 0, 1):
+        with torch.cuda.device(dev):
+            g = torch.Generator().manual_seed(20 + dev)
+            W = torch.randint(-128, 128, (B, M, N), generator=g, dtype=torch.int64).to(torch.int8).to(f"cuda:{dev}")
+            vp = torch.ops.brute.pack_bool((torch.rand((B, N, D), generator=g) < 0.5).to(f"cuda:{dev}"))
+            got = torch.zeros((B, M, vp.size(2)), dtype=torch.int64, device=f"cuda:{dev}")
+            st = torch.cuda.current_stream().cuda_stream
+            assert lib.brute_b200_signed_bundle_static(W.data_ptr(), vp.data_ptr(), got.data_ptr(), B, M, N,
+                                                       vp.size(2), D, st) == 0
+            torch.cuda.synchronize()
+            assert np.array_equal(got.cpu().numpy().view(np.uint64),
+                                  co.signed_bundle(W.cpu().numpy(), vp.cpu().numpy().view(np.uint64), D))
 
 
 def test_static_scratch_rejects_what_does_not_fit(lib_built):
