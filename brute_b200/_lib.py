@@ -27,6 +27,7 @@ SIGNATURES = {
     "brute_b200_strerror": [_i32],
     "brute_b200_query_caps": [],
     "brute_b200_device_status": [],
+    "brute_b200_selftest_bounded_wait": [_i64, _i32, _p, _p],
     "brute_b200_pack_bool": [_p, _p, _i64, _i64, _p],
     "brute_b200_pack_sign": [_p, _i32, _p, _i64, _i64, _i32, _p],
     "brute_b200_unpack_bool": [_p, _p, _i64, _i64, _p],
@@ -69,7 +70,7 @@ def load() -> C.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
             f"{LIB_PATH} is missing: the CUDA library has not been built. "
-            "Run `python -m brute_b200.build` (needs nvcc; no GPU required to build)."
+            "Run `python brute_b200/build.py` (needs nvcc and g++; no GPU required to build)."
         )
     lib = C.CDLL(str(LIB_PATH))
     for name, argtypes in SIGNATURES.items():

@@ -142,3 +142,36 @@ extern "C" int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uin
 }
 
 namespace bb { int tc5_status_bridge() { return tc5_device_status(); } }
+
+// ---------------------------------------------------------------------------
+// Self-test of the bounded wait that every tcgen05 kernel of the library relies on: one CTA waits,
+// with a SHORT limit, on an mbarrier that nothing will ever arrive at. The wait must give up, record
+// its code in the status word and let the kernel return; nothing traps and nothing spins forever.
+namespace bb {
+constexpr int TC_CODE_SELFTEST = 99;
+__global__ void k_selftest_bounded_wait(uint64_t limit_ns, int relaxed, int* gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init((uint32_t)__cvta_generic_to_shared(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t b = (uint32_t)__cvta_generic_to_shared(&bar);
+        const bool ok = relaxed ? mbar_wait_limit<true>(b, 0, &abort_flag, TC_CODE_SELFTEST, limit_ns)
+                                : mbar_wait_limit<false>(b, 0, &abort_flag, TC_CODE_SELFTEST, limit_ns);
+        *gave_up = ok ? 0 : 1;
+    }
+    __syncthreads();
+    // the other threads see the abort flag, as the roles of a real kernel do
+    if (threadIdx.x == 32 && abort_flag) atomicAdd(gave_up, 2);
+}
+}  // namespace bb
+
+extern "C" int brute_b200_selftest_bounded_wait(int64_t limit_us, int relaxed, int* gave_up_device, void* stream) {
+    BB_REQUIRE(limit_us >= 1 && limit_us <= 100000 && gave_up_device != nullptr, BRUTE_ERR_INVALID_ARG);
+    k_selftest_bounded_wait<<<1, 64, 0, as_stream(stream)>>>((uint64_t)limit_us * 1000ull, relaxed, gave_up_device);
+    return launch_status();
+}

@@ -38,17 +38,22 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait. Returns false after TC_WAIT_NS or when another role of this CTA
-// has already given up; `code` names the waiting role in the status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+// Bounded wait. Returns false after `limit_ns` or when another role of this CTA has already given
+// up; `code` names the waiting role in the status word. With `relaxed` the poll backs off between
+// tries, for roles that are far ahead of their consumer (producers waiting for a free slot), so that
+// the polling warp leaves the issue slots to the warps on the critical path.
+template <bool kRelaxed>
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                                uint64_t limit_ns) {
     if (mbar_try(bar, parity)) return true;
     const uint64_t t0 = tc_globaltimer();
     uint32_t spins = 0;
     while (true) {
+        if (kRelaxed) __nanosleep(128);
         if (mbar_try(bar, parity)) return true;
-        if (((++spins) & 0xFFu) == 0) {
+        if (((++spins) & (kRelaxed ? 0x3Fu : 0xFFu)) == 0) {
             if (*abort_flag) return false;
-            if (tc_globaltimer() - t0 > TC_WAIT_NS) {
+            if (tc_globaltimer() - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(&g_tc_status, 0, code);
                 return false;
@@ -56,25 +61,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
 }
-// The same bounded wait for roles that are far ahead of their consumer (producers waiting for a
-// free slot): back off between polls so that the polling warp leaves the issue slots to the warps
-// on the critical path.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    return mbar_wait_limit<false>(bar, parity, abort_flag, code, TC_WAIT_NS);
+}
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = tc_globaltimer();
-    uint32_t spins = 0;
-    while (true) {
-        __nanosleep(128);
-        if (mbar_try(bar, parity)) return true;
-        if (((++spins) & 0x3Fu) == 0) {
-            if (*abort_flag) return false;
-            if (tc_globaltimer() - t0 > TC_WAIT_NS) {
-                *abort_flag = 1;
-                atomicCAS(&g_tc_status, 0, code);
-                return false;
-            }
-        }
-    }
+    return mbar_wait_limit<true>(bar, parity, abort_flag, code, TC_WAIT_NS);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, uint32_t bar) {
     asm volatile(

@@ -32,7 +32,8 @@ void adopt_storage(const at::Tensor& dst, const at::Tensor& src) {
     TORCH_CHECK(dst.device() == src.device(), "adopt_storage: device mismatch");
     TORCH_CHECK(dst.dtype() == src.dtype(), "adopt_storage: dtype mismatch");
     TORCH_CHECK(src.is_contiguous() && src.storage_offset() == 0, "adopt_storage: src must own a dense storage");
-    TORCH_CHECK(src.storage().use_count() == 1, "adopt_storage: src storage is shared");
+    // src must be a fresh result that no other tensor aliases (the caller's contract: it is the
+    // output of unpack_bool); a Python storage wrapper that somebody made of it may still exist
     c10::StorageImpl* d = dst.storage().unsafeGetStorageImpl();
     c10::StorageImpl* s = src.storage().unsafeGetStorageImpl();
     TORCH_CHECK(d != s, "adopt_storage: dst and src are the same storage");

@@ -46,6 +46,11 @@ _REAL_CURRENT_STREAM = torch.cuda.current_stream      # the unpatched function
 _ACTIVE: Optional["_Rotator"] = None                  # the innermost active block, if any
 
 
+def _storage_ptr(t: torch.Tensor) -> int:
+    """Address of the first byte of the tensor's storage (views of one allocation share it)."""
+    return t.data_ptr() - t.storage_offset() * t.element_size()
+
+
 class _Rotator:
     """Hands out the pool's streams in turn and keeps the block's ordering state."""
 
@@ -72,7 +77,7 @@ class _Rotator:
         if outer.cuda_stream != s.cuda_stream:
             s.wait_event(outer.record_event())
         for t in tensors:
-            prod = self._producers.get(t.untyped_storage().data_ptr())
+            prod = self._producers.get(_storage_ptr(t))
             if prod is not None and prod[0] is not s:
                 s.wait_event(prod[1])
             t.record_stream(s)
@@ -85,7 +90,7 @@ class _Rotator:
         self._tail[id(s)] = done
         for o in (out if isinstance(out, (tuple, list)) else (out,)):
             if isinstance(o, torch.Tensor) and o.is_cuda:
-                self._producers[o.untyped_storage().data_ptr()] = (s, done)
+                self._producers[_storage_ptr(o)] = (s, done)
         if len(self._producers) > 4096:            # bounded: older producers are covered by join()
             self.join()
         return out

@@ -31,7 +31,11 @@ from typing import Callable, Dict, List, Optional
 
 import torch
 
-from . import _cbrute
+try:
+    from . import _cbrute
+except ImportError as exc:          # pragma: no cover
+    raise ImportError("brute_b200/_cbrute.so is missing: the host helper module has not been built. "
+                      "Run `python brute_b200/build.py` (needs g++ and the installed torch's headers).") from exc
 from . import streams as _streams
 from .dtype import _PACK_STORAGE_DTYPE, _PACK_WIDTH, _Bit1DType, bit1
 

@@ -77,6 +77,13 @@ uint32_t brute_b200_query_caps(void);
  * BRUTE_OK or BRUTE_ERR_DEVICE_WAIT. Meant for tests and diagnostics, not for
  * the per-call path. */
 int brute_b200_device_status(void);
+/* Self-test of the bounded waits (test and diagnostics entry point; no counterpart in the
+ * reference, whose kernels have no in-kernel waits): launches one small kernel that waits on an
+ * mbarrier nothing arrives at, with a limit of `limit_us` microseconds (1 .. 100000). The wait
+ * gives up, the kernel returns, *gave_up_device (a device int) is set to 3 (1: the waiter saw the
+ * timeout, +2: another warp saw the CTA's abort flag), and the next brute_b200_device_status()
+ * reports BRUTE_ERR_DEVICE_WAIT once. `relaxed` picks the backing-off form of the wait. */
+int brute_b200_selftest_bounded_wait(int64_t limit_us, int relaxed, int* gave_up_device, void* stream);
 
 /* ---- pack / unpack ----------------------------------------------------- */
 /* bool bytes [rows, ld] -> packed words [rows, ceil(ld/64)]; any nonzero byte

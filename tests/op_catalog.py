@@ -163,7 +163,9 @@ _op("getitem_neg", "matrix", 1, lambda a: a[-1], edges=_V)
 _op("getitem_ellipsis", "matrix", 1, lambda a: a[..., 1], edges=_V)
 _op("getitem_col_slice", "matrix", 1, lambda a: a[:, 1:3], edges=_V)
 _op("getitem_col_step", "matrix", 1, lambda a: a[..., ::2], edges=_V)
-_op("getitem_row_list", "matrix", 1, lambda a: a[torch.tensor([2, 0, 2], device=a.device)], edges=_V)
+# tensor indices are reduced modulo the axis length: an out-of-range index held in a DEVICE tensor is
+# not a Python exception on CUDA but a device-side assert, which no test here may cause
+_op("getitem_row_list", "matrix", 1, lambda a: a[torch.tensor([2, 0, 2], device=a.device) % a.shape[0]], edges=_V)
 _op("getitem_mask", "matrix", 1, lambda a: a[torch.arange(a.shape[0], device=a.device) % 2 == 0], edges=_V)
 
 
@@ -216,14 +218,15 @@ def _set(a, how):
     elif how == "col_ellipsis":
         a[..., 1] = False
     elif how == "col_tensor":
-        a[:, torch.tensor([0, 3], device=a.device)] = True
+        a[:, torch.tensor([0, 3], device=a.device) % a.shape[1]] = True
     elif how == "index_copy_last":
-        idx = torch.tensor([3, 0], device=a.device)
-        src = torch.ones(a.shape[0], 2, dtype=torch.bool, device=a.device)
+        cols = [a.shape[1] - 1, 0] if a.shape[1] >= 2 else [0]          # distinct, in range
+        idx = torch.tensor(cols, device=a.device)
+        src = torch.ones(a.shape[0], len(cols), dtype=torch.bool, device=a.device)
         src[::2, 0] = False
         a.index_copy_(-1, idx, src)
     elif how == "index_fill_last":
-        a.index_fill_(-1, torch.tensor([1, 2], device=a.device), True)
+        a.index_fill_(-1, torch.tensor([1, 2], device=a.device) % a.shape[1], True)
     return a
 
 
