@@ -305,6 +305,28 @@ k_gather_bits(const uint64_t* __restrict__ in, const int64_t* __restrict__ idx, 
     }
 }
 
+// scatter (x[..., idx] = value, index_copy_ / index_fill_ along the last axis): thread (j, row)
+// writes ONE bit, position idx[j] of its row, with a word-wide atomic (several positions may share
+// a word). The source bit is bit j of the row of `src`, or the constant `value` when src is null.
+// A thread keeps its j (and idx[j]) and walks the rows.
+__global__ void __launch_bounds__(256)
+k_scatter_bits(unsigned long long* __restrict__ packed, const int64_t* __restrict__ idx,
+               const uint64_t* __restrict__ src, int value,
+               int64_t rows, int64_t n, int64_t n_idx, int64_t wpr, int64_t wpr_src) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n_idx) return;
+    const int64_t s = __ldg(idx + j);
+    if (s < 0 || s >= n) return;                              // out of range: the caller has checked; write nothing
+    const unsigned long long bit = 1ull << (s & 63);
+    const int64_t w = s >> 6, ws = j >> 6;
+    const int sb = (int)(j & 63);
+    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const int on = src ? (int)((__ldg(src + r * wpr_src + ws) >> sb) & 1ull) : value;
+        if (on) atomicOr(packed + r * wpr + w, bit);
+        else    atomicAnd(packed + r * wpr + w, ~bit);
+    }
+}
+
 }  // namespace bb
 
 namespace bb { int ly_status_bridge() { return tc5_device_status(); } }
@@ -402,5 +424,23 @@ extern "C" int brute_b200_gather_bits(const uint64_t* in, const int64_t* idx, ui
     const int64_t chunks = (n_out + 1023) / 1024;
     k_gather_bits<<<stream_grid(rows * chunks, 8, 8), 256, 0, as_stream(stream)>>>(
         in, idx, reinterpret_cast<uint32_t*>(out), rows, n_in, n_out, wpr_in, wpr_out, chunks);
+    return launch_status();
+}
+
+extern "C" int brute_b200_scatter_bits(uint64_t* packed, const int64_t* idx, const uint64_t* src, int value,
+                                       int64_t rows, int64_t n, int64_t n_idx, void* stream) {
+    BB_REQUIRE(rows >= 0 && n >= 0 && n_idx >= 0, BRUTE_ERR_INVALID_ARG);
+    if (rows == 0 || n == 0 || n_idx == 0) return BRUTE_OK;
+    BB_REQUIRE(packed != nullptr && idx != nullptr && packed != src, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(packed) && aligned8(idx) && aligned8(src), BRUTE_ERR_MISALIGNED);
+    const int64_t gx = (n_idx + 255) / 256;
+    BB_REQUIRE(gx <= 0x7fffffffll, BRUTE_ERR_UNSUPPORTED);
+    // enough row lanes to fill the SMs a few times over when the index vector is short
+    int64_t gy = (8 * (int64_t)kNumSMs + gx - 1) / gx;
+    if (gy > rows) gy = rows;
+    if (gy > 65535) gy = 65535;
+    const dim3 grid((unsigned)gx, (unsigned)gy);
+    k_scatter_bits<<<grid, 256, 0, as_stream(stream)>>>(reinterpret_cast<unsigned long long*>(packed), idx, src,
+                                                        value != 0, rows, n, n_idx, (n + 63) / 64, (n_idx + 63) / 64);
     return launch_status();
 }

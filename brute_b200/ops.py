@@ -12,7 +12,7 @@ Ops beyond the reference's eleven carry new names and never change the eleven:
 ``pack_sign``, ``bitwise_packed``, ``select_packed``, ``row_any``, ``row_all``,
 ``xnor_popcount_matmul_impl``, ``xnor_matmul_scale_sign_pack``,
 ``binary_attention``, ``transpose_packed``, ``reduce_rows_packed``, ``flip_packed``,
-``roll_packed``, ``gather_packed``. ``signed_bundle`` keeps the reference's schema and
+``roll_packed``, ``gather_packed``, ``scatter_packed_``. ``signed_bundle`` keeps the reference's schema and
 runs on the tensor cores; the scratch it needs is allocated here, never by the library.
 """
 from __future__ import annotations
@@ -51,6 +51,7 @@ _DEF.define("reduce_rows_packed(Tensor packed, int dim, bool use_or) -> Tensor")
 _DEF.define("flip_packed(Tensor packed, int n) -> Tensor")
 _DEF.define("roll_packed(Tensor packed, int n, int shift) -> Tensor")
 _DEF.define("gather_packed(Tensor packed, Tensor idx, int n_in) -> Tensor")
+_DEF.define("scatter_packed_(Tensor(a!) packed, Tensor idx, Tensor? src, bool value, int n) -> Tensor(a!)")
 
 _PACK_WIDTH = 64
 _SIGN_DTYPES = {torch.float32: L.DT_F32, torch.bfloat16: L.DT_BF16, torch.float16: L.DT_F16}
@@ -479,6 +480,27 @@ def gather_packed(packed: torch.Tensor, idx: torch.Tensor, n_in: int) -> torch.T
     return out
 
 
+def scatter_packed_(packed: torch.Tensor, idx: torch.Tensor, src, value: bool, n: int) -> torch.Tensor:
+    """In place: bit idx[j] of every row of ``packed`` = bit j of the row of ``src`` (packed), or ``value``."""
+    _check(packed.dim() >= 1 and packed.dtype == torch.int64 and packed.is_contiguous(),
+           "scatter_packed_: packed must be a contiguous int64 tensor with >= 1 dim")
+    _check(packed.size(-1) == _words(int(n)), "scatter_packed_: last dimension must be ceil(n/64) words")
+    _check(idx.dim() == 1 and idx.dtype == torch.int64, "scatter_packed_: idx must be a 1-D int64 tensor")
+    ic = idx.contiguous()
+    n_idx = int(ic.numel())
+    rows = packed.numel() // packed.size(-1) if packed.size(-1) else 0
+    sc = None
+    if src is not None:
+        _check(src.dtype == torch.int64 and tuple(src.shape) == tuple(packed.shape[:-1]) + (_words(n_idx),),
+               "scatter_packed_: src must be int64 packed [..., ceil(len(idx)/64)] with packed's leading shape")
+        sc = src.contiguous()
+    if rows and n_idx:
+        with _device_guard(packed.device):
+            L.check(_lib.brute_b200_scatter_bits(packed.data_ptr(), ic.data_ptr(), sc.data_ptr() if sc is not None else None,
+                                                 int(bool(value)), rows, int(n), n_idx, _stream(packed)), "scatter_packed_")
+    return packed
+
+
 def randomize_bits(out: torch.Tensor) -> torch.Tensor:
     out.random_()          # cbrute/cuda/ops_cuda.cu:340, a plain ATen call
     return out
@@ -516,6 +538,7 @@ _CUDA_IMPLS = {
     "xnor_matmul_scale_sign_pack": xnor_matmul_scale_sign_pack, "binary_attention": binary_attention,
     "transpose_packed": transpose_packed, "reduce_rows_packed": reduce_rows_packed,
     "flip_packed": flip_packed, "roll_packed": roll_packed, "gather_packed": gather_packed,
+    "scatter_packed_": scatter_packed_,
 }
 _IMPL = torch.library.Library("brute", "IMPL", "CUDA")
 for _name, _fn in _CUDA_IMPLS.items():
@@ -557,6 +580,7 @@ def _register_fakes() -> None:
     reg("brute::roll_packed")(lambda packed, n, shift: torch.empty_like(packed))
     reg("brute::gather_packed")(
         lambda packed, idx, n_in: packed.new_empty(tuple(packed.shape[:-1]) + (_words(idx.shape[0]),), dtype=torch.int64))
+    reg("brute::scatter_packed_")(lambda packed, idx, src, value, n: packed)
     reg("brute::reduce_rows_packed")(
         lambda packed, dim, use_or: packed.new_empty(tuple(s for i, s in enumerate(packed.shape) if i != dim % packed.dim()),
                                                      dtype=torch.int64))

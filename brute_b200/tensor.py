@@ -567,6 +567,48 @@ class Tensor(torch.Tensor):
             view.copy_(torch.tensor(bool(value), dtype=torch.bool, device=plain.device).expand_as(view))
         d["_packed_ver"] = _plain(self)._version
 
+    def _last_axis_tensor_index(self, idx) -> Optional[torch.Tensor]:
+        """``x[..., t]`` / ``x[:, ..., :, t]`` with t a 1-D integer tensor on the packed axis: t, else None."""
+        if not (_is_b1(self) and self.dim() >= 1) or not isinstance(idx, tuple) or not idx:
+            return None
+        t = idx[-1]
+        if not (isinstance(t, torch.Tensor) and t.dim() == 1 and t.dtype in (torch.int64, torch.int32)):
+            return None
+        lead = idx[:-1]
+        if lead == (Ellipsis,) or (len(lead) == self.dim() - 1
+                                   and all(isinstance(x, slice) and x == slice(None) for x in lead)):
+            return _plain(t)
+        return None
+
+    def _scatter_last_axis(self, index: torch.Tensor, src, value: bool, bool_write: Callable,
+                           negative_ok: bool = True) -> None:
+        """Write through a tensor index on the packed axis without leaving the packed domain
+        (the reference re-packs the whole tensor after the bool write, brute/tensor.py:362-388).
+        ``src``: None (every indexed position takes ``value``), or a tensor of shape
+        ``shape[:-1] + [len(index)]``. ``bool_write(plain)`` applies the same write to the bool
+        storage; it runs only when that storage is live, so that aliasing views see the write."""
+        plain = _plain(self)
+        n = int(plain.shape[-1])
+        ix = index.to(device=plain.device, dtype=torch.int64)
+        if ix.numel():
+            lo, hi = int(ix.min()), int(ix.max())       # torch raises on an index out of range; so does this
+            if lo < (-n if negative_ok else 0) or hi >= n:
+                raise IndexError(f"index {hi if hi >= n else lo} is out of bounds for dimension {plain.dim() - 1} with size {n}")
+            if lo < 0:
+                ix = torch.where(ix < 0, ix + n, ix)
+        d = self.__dict__
+        pb = self._packed_buf_contig()
+        if pb._base is not None:
+            pb = pb.clone()                  # a view into another tensor's words: never written in place
+        sp = None
+        if src is not None:
+            sp = src._packed_buf_contig() if _is_b1(src) else _pack_bool(_to_bool(_plain(src)))
+        if not d.get("_bool_dirty", False):
+            bool_write(plain)
+        _ops.scatter_packed_(pb, ix, sp, bool(value), n)
+        d["_packed_buf_cache"] = pb
+        d["_packed_ver"] = plain._version
+
     def __getitem__(self, idx):
         _join_streams()
         if self._leading_axis_fast(idx):
@@ -611,6 +653,22 @@ class Tensor(torch.Tensor):
         if scalar and j is not None:
             self._column_scatter(j, bool(value))
             return
+        t = self._last_axis_tensor_index(idx)
+        if t is not None and self.numel():
+            if scalar:
+                def write(plain, t=t, v=bool(value)):
+                    plain[..., t.to(plain.device)] = v
+                self._scatter_last_axis(t, None, bool(value), write)
+                return
+            if (isinstance(value, torch.Tensor) and _plain(value).dtype == torch.bool
+                    and tuple(value.shape) == tuple(self.shape[:-1]) + (int(t.numel()),)):
+                if _is_b1(value):
+                    value._ensure_bool_valid()
+
+                def write(plain, t=t, v=_plain(value)):
+                    plain[..., t.to(plain.device)] = v
+                self._scatter_last_axis(t, value, False, write)
+                return
         return super().__setitem__(idx, value)
 
     # -------------------------------------------------------- bit1 methods
@@ -1367,6 +1425,37 @@ def _h_fill(func, args, kwargs, b1):
     d["_packed_buf_cache"] = pb
     d["_packed_ver"] = plain._version
     return a
+
+
+@_fast(torch.Tensor.index_fill_)
+def _h_index_fill_(func, args, kwargs, b1):
+    a = args[0] if args else None
+    dim, index, value = _arg(args, kwargs, 1, "dim"), _arg(args, kwargs, 2, "index"), _arg(args, kwargs, 3, "value")
+    if (_is_b1(a) and a.dim() >= 1 and a.numel() and isinstance(dim, int) and dim in (-1, a.dim() - 1)
+            and isinstance(index, torch.Tensor) and not _is_b1(index) and index.dim() == 1
+            and index.dtype in (torch.int64, torch.int32) and isinstance(value, (bool, int))):
+        a._scatter_last_axis(_plain(index), None, bool(value),
+                             lambda plain: plain.index_fill_(-1, _plain(index).to(plain.device), bool(value)))
+        return a
+    return NotImplemented
+
+
+@_fast(torch.Tensor.index_copy_)
+def _h_index_copy_(func, args, kwargs, b1):
+    a = args[0] if args else None
+    dim, index, src = _arg(args, kwargs, 1, "dim"), _arg(args, kwargs, 2, "index"), _arg(args, kwargs, 3, "source")
+    if (_is_b1(a) and a.dim() >= 1 and a.numel() and isinstance(dim, int) and dim in (-1, a.dim() - 1)
+            and isinstance(index, torch.Tensor) and not _is_b1(index) and index.dim() == 1
+            and index.dtype in (torch.int64, torch.int32) and isinstance(src, torch.Tensor)
+            and _plain(src).dtype == torch.bool
+            and tuple(src.shape) == tuple(a.shape[:-1]) + (int(index.numel()),)):
+        if _is_b1(src):
+            src._ensure_bool_valid()
+        a._scatter_last_axis(_plain(index), src, False,
+                             lambda plain: plain.index_copy_(-1, _plain(index).to(plain.device), _plain(src)),
+                             negative_ok=False)          # torch's index_copy_ takes no negative index
+        return a
+    return NotImplemented
 
 
 @_fast(torch.where, torch.Tensor.where)

@@ -212,6 +212,17 @@ int brute_b200_roll_bits(const uint64_t* in, uint64_t* out, int64_t rows, int64_
 int brute_b200_gather_bits(const uint64_t* in, const int64_t* idx, uint64_t* out,
                            int64_t rows, int64_t n_in, int64_t n_out, void* stream);
 
+/* Scatter along the packed axis, IN PLACE: for every row of `packed` [rows, ceil(n/64)] and every
+ * j < n_idx, bit idx[j] of the row becomes bit j of the row of `src` [rows, ceil(n_idx/64)], or the
+ * constant `value` (0 / 1) when src is NULL. idx is a device array of n_idx int64, the same for every
+ * row; an index outside [0, n) writes nothing. Positions that idx names twice take one of the
+ * candidate bits (as torch's index_copy_ with repeated indices); all other bits keep their value.
+ * Replaces the unpack -> bool index_put_ / index_copy_ / index_fill_ -> re-pack round trip the
+ * reference takes for a write through a tensor index on the last axis (the packed column scatter of
+ * brute/tensor.py:715-775 covers one integer column and a scalar only). */
+int brute_b200_scatter_bits(uint64_t* packed, const int64_t* idx, const uint64_t* src, int value,
+                            int64_t rows, int64_t n, int64_t n_idx, void* stream);
+
 /* ---- xnor-popcount GEMM ------------------------------------------------ */
 /* A [M, Kp] words, B [N, Kp] words (rows of B are output features), K logical
  * bits (K <= 64*Kp, pad bits 0) -> C [M, N] int32 with row pitch ldc elements,

@@ -462,3 +462,22 @@ void oracle_move_bits(int mode, const uint64_t* in, const int64_t* idx, uint64_t
             if ((in[r * wi + (s >> 6)] >> (s & 63)) & 1ull) out[r * wo + (j >> 6)] |= 1ull << (j & 63);
         }
 }
+
+
+/* Scatter along the packed axis, in place. The reference has no packed form: a write through a tensor
+ * index on the last axis (x[..., idx] = v, index_copy_, index_fill_) falls to the bool path, i.e.
+ * unpack -> torch index op on the bools -> pack (brute/tensor.py:846-853, 1979-1982); this is that
+ * composition bit by bit, in index order (the last writer of a repeated position wins).
+ * src == NULL: every indexed position takes `value`. */
+void oracle_scatter_bits(uint64_t* packed, const int64_t* idx, const uint64_t* src, int value,
+                         int64_t rows, int64_t n, int64_t n_idx) {
+    const int64_t wp = (n + 63) / 64, ws = (n_idx + 63) / 64;
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t j = 0; j < n_idx; ++j) {
+            const int64_t s = idx[j];
+            if (s < 0 || s >= n) continue;
+            const int on = src ? (int)((src[r * ws + (j >> 6)] >> (j & 63)) & 1ull) : (value != 0);
+            if (on) packed[r * wp + (s >> 6)] |= 1ull << (s & 63);
+            else    packed[r * wp + (s >> 6)] &= ~(1ull << (s & 63));
+        }
+}

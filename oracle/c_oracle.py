@@ -57,6 +57,7 @@ def lib():
         L.oracle_transpose_bits.argtypes = [p, p, i64, i64, i64]
         L.oracle_reduce_rows.argtypes = [i32, p, p, i64, i64, i64]
         L.oracle_move_bits.argtypes = [i32, p, p, p, i64, i64, i64, i64]
+        L.oracle_scatter_bits.argtypes = [p, p, p, i32, i64, i64, i64]
         _lib = L
     return _lib
 
@@ -293,3 +294,16 @@ def roll_bits(packed: np.ndarray, n: int, shift: int) -> np.ndarray:
 
 def gather_bits(packed: np.ndarray, idx: np.ndarray, n_in: int) -> np.ndarray:
     return _move_bits(2, packed, n_in, int(np.asarray(idx).size), idx=idx)
+
+
+def scatter_bits(packed: np.ndarray, idx: np.ndarray, src, value: int, n: int) -> np.ndarray:
+    """A copy of ``packed`` [..., ceil(n/64)] with bit idx[j] of every row set from bit j of ``src``
+    (packed, same leading shape) or, with ``src`` None, from the constant ``value``."""
+    out = _u64(packed).copy()
+    ix = _c(idx, np.int64)
+    rows = int(np.prod(out.shape[:-1], dtype=np.int64)) if out.ndim > 1 else 1
+    sp = None if src is None else _u64(src)
+    if out.size and ix.size:
+        lib().oracle_scatter_bits(_ptr(out), _ptr(ix), None if sp is None else _ptr(sp), int(bool(value)),
+                                  rows, int(n), int(ix.size))
+    return out

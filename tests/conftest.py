@@ -156,6 +156,11 @@ def install_oracle_cpu_ops():
     lib.impl("flip_packed", lambda packed, n: n2t(co.flip_bits(t2n(packed.contiguous()), n), torch.int64))
     lib.impl("roll_packed", lambda packed, n, shift: n2t(co.roll_bits(t2n(packed.contiguous()), n, shift), torch.int64))
     lib.impl("gather_packed", lambda packed, idx, n_in: n2t(co.gather_bits(t2n(packed.contiguous()), t2n(idx), n_in), torch.int64))
+    def scatter_packed_(packed, idx, src, value, n):
+        res = co.scatter_bits(t2n(packed), t2n(idx), None if src is None else t2n(src), int(value), n)
+        packed.copy_(n2t(res).reshape(packed.shape))
+        return packed
+    lib.impl("scatter_packed_", scatter_packed_)
     lib.impl("reduce_rows_packed", lambda packed, dim, use_or: n2t(co.reduce_rows(t2n(packed.contiguous()), dim, use_or), torch.int64))
 
     def randomize(out):

@@ -508,6 +508,76 @@ def test_clone_then_write_plain_alias_leaves_the_source_alone(brute):
 
 
 # ---------------------------------------------------------------------------
+# writes through a tensor index on the packed axis stay in the packed domain
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("state", ["lazy", "valid"])
+def test_scatter_on_the_packed_axis(brute, state):
+    shape = (5, 3, 131)
+    x = rnd(shape, 51)
+    idx = torch.tensor([130, 0, 64, 63, 7, 129, -3], device=DEV)        # -3 -> 128
+    srcb = rnd(shape[:-1] + (7,), 52)
+
+    def fresh():
+        b = b1(brute, x)
+        if state == "lazy":
+            b = b ^ brute.zeros(shape, dtype=brute.bit1, device=DEV)     # packed-only, bool storage empty
+            assert b.__dict__["_bool_dirty"] is True
+        return b
+
+    def twin():
+        return x.clone()
+
+    # x[..., idx] = scalar
+    for v in (True, False):
+        b, t = fresh(), twin()
+        b[..., idx] = v
+        t[..., idx] = v
+        assert same(as_bool(b), t) and int(b.popcount()) == int(t.sum())
+    # x[:, :, idx] = tensor (bool and bit1 sources)
+    for src in (srcb, b1(brute, srcb)):
+        b, t = fresh(), twin()
+        b[:, :, idx] = src
+        t[:, :, idx] = srcb
+        assert same(as_bool(b), t) and int(b.popcount()) == int(t.sum())
+    # index_fill_ / index_copy_ on the last dim
+    b, t = fresh(), twin()
+    assert b.index_fill_(-1, idx, True) is b
+    t.index_fill_(-1, idx, True)
+    assert same(as_bool(b), t)
+    b, t = fresh(), twin()
+    pos = torch.where(idx < 0, idx + 131, idx)            # torch's index_copy_ takes no negative index
+    b.index_copy_(2, pos, b1(brute, srcb))
+    t.index_copy_(2, pos, srcb)
+    assert same(as_bool(b), t) and int(b.popcount()) == int(t.sum())
+    with pytest.raises(IndexError):
+        fresh().index_copy_(2, idx, b1(brute, srcb))
+    if state == "lazy":
+        lz = fresh()
+        lz[..., idx] = True
+        assert lz.__dict__["_bool_dirty"] is True, "a packed-only tensor must stay packed-only"
+    # an index out of range raises before anything is launched
+    with pytest.raises(IndexError):
+        fresh()[..., torch.tensor([131], device=DEV)] = True
+    with pytest.raises(IndexError):
+        fresh().index_fill_(-1, torch.tensor([-132], device=DEV), True)
+
+
+def test_scatter_on_the_packed_axis_reaches_aliases(brute):
+    base = b1(brute, rnd((6, 70), 53))
+    want = as_bool(base).clone()
+    view = base[:, ::2]                      # a bool view that shares base's storage
+    base[:, torch.tensor([0, 2, 69], device=DEV)] = True
+    want[:, [0, 2, 69]] = True
+    assert same(as_bool(base), want)
+    assert same(as_bool(view), want[:, ::2]), "the view must see the write"
+    assert int(base.popcount()) == int(want.sum())
+    # and a write through the plain alias afterwards still re-packs (version tracking intact)
+    base.as_subclass(torch.Tensor)[0, 1] = True
+    want[0, 1] = True
+    assert int(base.popcount()) == int(want.sum())
+
+
+# ---------------------------------------------------------------------------
 # concurrent host threads (the reference requires this of its drivers: tests/unit/test_multithread.py)
 # ---------------------------------------------------------------------------
 def test_threads_share_one_tensor_and_the_library(brute):

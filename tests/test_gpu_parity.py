@@ -765,3 +765,32 @@ def test_bounded_wait_gives_up_and_the_library_recovers(ops, co, relaxed):
     got = ops.xnor_popcount_matmul(ops.pack_bool(a.to(DEV)), ops.pack_bool(b.to(DEV)), K)
     assert np.array_equal(got.cpu().numpy(), co.xnor_gemm(co.pack_bool(a.numpy()), co.pack_bool(b.numpy()), K))
     assert status_ok()
+
+
+# ---------------------------------------------------------------------------
+# scatter along the packed axis
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,n,n_idx", [(1, 64, 1), (7, 131, 40), (33, 1003, 1003), (4096, 4097, 512), (3, 200, 0),
+                                          (70000, 65, 9)])
+def test_scatter_bits_vs_oracle(ops, co, rows, n, n_idx):
+    g = gen(rows + n + n_idx)
+    x = torch.rand((rows, n), generator=g) < 0.5
+    packed = ops.pack_bool(x.to(DEV))
+    idx = torch.randperm(n, generator=g)[:n_idx]                   # distinct positions: the result is unique
+    src = torch.rand((rows, n_idx), generator=g) < 0.5
+    want_base = co.pack_bool(x.numpy())
+    for value in (0, 1):
+        got = ops.scatter_packed_(packed.clone(), idx.to(DEV), None, bool(value), n)
+        assert np.array_equal(u64(got), co.scatter_bits(want_base, idx.numpy(), None, value, n)), value
+    if n_idx:
+        sp = ops.pack_bool(src.to(DEV))
+        got = ops.scatter_packed_(packed.clone(), idx.to(DEV), sp, False, n)
+        want = co.scatter_bits(want_base, idx.numpy(), co.pack_bool(src.numpy()), 0, n)
+        assert np.array_equal(u64(got), want)
+        ref = x.clone()
+        ref[:, idx] = src
+        assert np.array_equal(want, co.pack_bool(ref.numpy())), "oracle vs torch.bool"
+    # repeated positions with one constant value are well defined; out-of-range positions write nothing
+    rep = torch.tensor([0, n - 1, 0, n - 1, n + 5, -1], dtype=torch.int64)
+    got = ops.scatter_packed_(packed.clone(), rep.to(DEV), None, True, n)
+    assert np.array_equal(u64(got), co.scatter_bits(want_base, rep.numpy(), None, 1, n))
