@@ -9,9 +9,11 @@
 // transposed words go through shared memory so that every input and output row of the tile is one
 // contiguous 64-byte run. HBM bound: 2 * R * C / 8 bytes.
 //
-// reduce_rows: in [outer, R, inner] words -> out [outer, inner] words, OR or AND over R. One
-// thread per inner word (coalesced), R cut into chunks across blockIdx.y, partial results merged
-// with 64-bit atomics into an output that the launcher presets (0 for OR, ~0 for AND).
+// reduce_rows: in [outer, R, inner] words -> out [outer, inner] words, OR or AND over R. Rows of
+// whole 16-byte vectors: one launch, no preset, no atomics (k_reduce_rows_slab: a CTA owns a
+// 512-byte slab of the rows, the rows are split over a thread-block cluster and merged through
+// distributed shared memory). Other rows: one thread per inner word, R cut into chunks across
+// blockIdx.y, partial results merged with 64-bit atomics into an output that the launcher presets.
 #include "tcgen05_common.cuh"
 
 namespace bb {
@@ -230,6 +232,94 @@ k_reduce_rows(const uint64_t* __restrict__ in, unsigned long long* __restrict__ 
     else       { if (acc != ~0ull) atomicAnd(out + o * inner + i, acc); }
 }
 
+// The same reduction without the preset and without atomics, for rows of whole 16-byte vectors. A
+// CTA owns a slab of 64 words (512 contiguous bytes of every row) and a share of the rows: its 256
+// threads are 32 column threads (one 16-byte vector each) times 8 row lanes, every thread keeps four
+// loads in flight, the row lanes meet in shared memory (narrower slabs, 16 column threads times 16
+// row lanes, when there are few of them). When the slabs alone do not fill the GPU
+// the rows are split over the 2, 4 or 8 CTAs of a thread-block CLUSTER and the CTAs' partial slabs
+// meet through distributed shared memory: rank 0 reads its peers' partials and stores the slab.
+constexpr int RR_THREADS = 256;
+
+__device__ __forceinline__ uint32_t rr_cluster_rank() {
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ uint32_t rr_cluster_size() {
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ void rr_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <bool IS_OR, int RR_COLS>
+__global__ void __launch_bounds__(RR_THREADS)
+k_reduce_rows_slab(const uint64_t* __restrict__ in, uint64_t* __restrict__ out, int64_t R, int64_t inner) {
+    constexpr int RR_LANES = RR_THREADS / RR_COLS, RR_SLAB = 2 * RR_COLS;      // row lanes; words per slab
+    __shared__ __align__(16) uint64_t part[RR_LANES][RR_SLAB];
+    const int col = threadIdx.x % RR_COLS, rl = threadIdx.x / RR_COLS;
+    const uint32_t crank = rr_cluster_rank(), csize = rr_cluster_size();      // cluster spans blockIdx.y
+    const int64_t o = blockIdx.z;
+    const int64_t w = (int64_t)blockIdx.x * RR_SLAB + 2 * col;                // first word of this thread's vector
+    const bool live = w < inner;                                              // inner is even: both words or none
+    // rows of this CTA: an equal share of R
+    const int64_t per = R / csize, extra = R % csize;
+    const int64_t ra = crank * per + (crank < extra ? crank : extra);
+    const int64_t rb = ra + per + (crank < extra ? 1 : 0);
+    const uint64_t ident = IS_OR ? 0ull : ~0ull;
+    uint64_t a0 = ident, a1 = ident;
+    if (live) {
+        const uint64_t* p = in + (o * R + ra + rl) * inner + w;
+        const int64_t step = (int64_t)RR_LANES * inner;
+        int64_t r = ra + rl;
+        for (; r + 7 * RR_LANES < rb; r += 8 * RR_LANES, p += 8 * step) {      // eight independent loads in flight
+            uint4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = ldg_stream(p + k * step);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint64_t x = ((uint64_t)v[k].y << 32) | v[k].x, y = ((uint64_t)v[k].w << 32) | v[k].z;
+                a0 = IS_OR ? (a0 | x) : (a0 & x);
+                a1 = IS_OR ? (a1 | y) : (a1 & y);
+            }
+        }
+        for (; r < rb; r += RR_LANES, p += step) {
+            const uint4 v = ldg_stream(p);
+            const uint64_t x = ((uint64_t)v.y << 32) | v.x, y = ((uint64_t)v.w << 32) | v.z;
+            a0 = IS_OR ? (a0 | x) : (a0 & x);
+            a1 = IS_OR ? (a1 | y) : (a1 & y);
+        }
+    }
+    part[rl][2 * col] = a0;
+    part[rl][2 * col + 1] = a1;
+    __syncthreads();
+    if (rl == 0) {
+#pragma unroll
+        for (int k = 1; k < RR_LANES; ++k) {
+            a0 = IS_OR ? (a0 | part[k][2 * col]) : (a0 & part[k][2 * col]);
+            a1 = IS_OR ? (a1 | part[k][2 * col + 1]) : (a1 & part[k][2 * col + 1]);
+        }
+        part[0][2 * col] = a0;
+        part[0][2 * col + 1] = a1;
+    }
+    if (csize > 1) {
+        rr_cluster_sync();                      // every CTA's part[0] is complete and visible to the cluster
+        if (crank == 0 && rl == 0) {
+            const uint32_t mine = (uint32_t)__cvta_generic_to_shared(&part[0][2 * col]);
+            for (uint32_t k = 1; k < csize; ++k) {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(k));
+                uint64_t b0, b1;
+                asm volatile("ld.shared::cluster.v2.u64 {%0, %1}, [%2];" : "=l"(b0), "=l"(b1) : "r"(remote) : "memory");
+                a0 = IS_OR ? (a0 | b0) : (a0 & b0);
+                a1 = IS_OR ? (a1 | b1) : (a1 & b1);
+            }
+        }
+        rr_cluster_sync();                      // peers keep their shared memory alive until rank 0 has read it
+    }
+    if (crank == 0 && rl == 0 && live)
+        stg_stream(out + o * inner + w, make_uint4((uint32_t)a0, (uint32_t)(a0 >> 32), (uint32_t)a1, (uint32_t)(a1 >> 32)));
+}
+
 // ---------------------------------------------------------------------------
 // Moves along the packed axis, in the packed domain.
 //
@@ -276,6 +366,133 @@ k_flip_roll_bits(const uint64_t* __restrict__ in, uint64_t* __restrict__ out,
         const int64_t valid = n - 64 * w;
         if (valid < 64) v &= (1ull << valid) - 1ull;
         out[i] = v;
+    }
+}
+
+// bits [s, s + 64) of the 128-bit little-endian value (lo, hi), 0 <= s < 64
+__device__ __forceinline__ uint64_t funnel64(uint64_t lo, uint64_t hi, int s) {
+    return s ? (lo >> s) | (hi << (64 - s)) : lo;
+}
+
+// The same two moves for rows of whole 16-byte vectors (wpr even, 16-byte aligned bases): a warp
+// makes 128 consecutive output words of one row per task, a lane four of them (32 bytes). Every lane
+// loads TWO aligned 16-byte vectors of the input, takes the first vector of its neighbour through
+// shuffles, cuts its eight 32-bit output words out of those twelve input words with 32-bit funnel
+// shifts (the word offset is the same for the whole warp) and stores two 16-byte vectors. A task
+// whose window runs over an end of the row (the wrap of a roll, the ragged last words) takes the
+// word-by-word form. Index arithmetic is 32-bit: the launcher checks that it fits.
+template <bool FLIP>
+__device__ __forceinline__ void fr_words_slow(const uint64_t* __restrict__ row, uint64_t* __restrict__ orow,
+                                              int64_t n, int64_t wpr, int64_t shift, int64_t W) {
+    uint64_t v[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int64_t w = W + k;
+        if (FLIP) {
+            v[k] = __brevll(row_window(row, wpr, n, n - 64 * (w + 1)));
+        } else {
+            int64_t p = 64 * w - shift;
+            if (p < 0) p += n;
+            v[k] = row_window(row, wpr, n, p);
+            if (p + 64 > n) v[k] |= row_window(row, wpr, n, p - n);
+        }
+        const int64_t valid = n - 64 * w;
+        if (valid < 64) v[k] = valid > 0 ? (v[k] & ((1ull << valid) - 1ull)) : 0ull;
+    }
+    stg_stream(orow + W, make_uint4((uint32_t)v[0], (uint32_t)(v[0] >> 32), (uint32_t)v[1], (uint32_t)(v[1] >> 32)));
+}
+
+// y[j] = bits [32 (K + j) + s, 32 (K + j) + s + 32) of the little-endian word array x, j < 8
+template <int K>
+__device__ __forceinline__ void fr_cut(const uint32_t (&x)[12], uint32_t s, uint32_t (&y)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = __funnelshift_r(x[K + j], x[K + j + 1], s);
+}
+
+template <bool FLIP>
+__global__ void __launch_bounds__(256, 6)
+k_flip_roll_vec(const uint64_t* __restrict__ in, uint64_t* __restrict__ out,
+                uint32_t tasks, uint32_t chunks_per_row, int64_t n, int64_t wpr, int64_t shift) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t t = warp; t < tasks; t += nwarps) {
+        const uint32_t r = t / chunks_per_row;
+        const int64_t W0 = (int64_t)(t - r * chunks_per_row) * 128;             // first output word of the task
+        const int64_t cw = (wpr - W0) < 128 ? (wpr - W0) : 128;                 // output words of the task
+        const uint64_t* row = in + (int64_t)r * wpr;
+        uint64_t* orow = out + (int64_t)r * wpr;
+        const int64_t W = W0 + 4 * lane;                                        // this lane's four output words
+        bool fast;
+        int64_t start;                                                          // first input bit this lane reads
+        if (FLIP) {
+            fast = n - 64 * (W0 + cw) >= 0;                                     // the window of the task's last word
+            start = n - 64 * (W + 4);
+        } else {
+            int64_t P = (64 * W0 - shift) % n;
+            if (P < 0) P += n;
+            fast = P + 64 * cw <= n;
+            start = P + 256 * lane;
+        }
+        if (!fast) {                                                            // warp-uniform
+            if (W < wpr) fr_words_slow<FLIP>(row, orow, n, wpr, shift, W);
+            if (W + 2 < wpr) fr_words_slow<FLIP>(row, orow, n, wpr, shift, W + 2);
+            continue;
+        }
+        const int64_t q = start >> 6;                                           // word that holds the first bit
+        const int64_t qa = q & ~1ll;
+        uint32_t x[12];
+        {
+            uint4 a = make_uint4(0, 0, 0, 0), b = a, c = a;
+            if (qa >= 0 && qa < wpr) a = ldg_stream(row + qa);
+            if (qa + 2 >= 0 && qa + 2 < wpr) b = ldg_stream(row + qa + 2);
+            // the vector after these two is the first vector of a neighbour, except at the end of the warp
+            const bool edge = FLIP ? (lane == 0) : (lane == 31);
+            if (edge && qa + 4 >= 0 && qa + 4 < wpr) c = ldg_stream(row + qa + 4);
+            uint4 nb;
+            if (FLIP) {
+                nb.x = __shfl_up_sync(0xffffffffu, a.x, 1); nb.y = __shfl_up_sync(0xffffffffu, a.y, 1);
+                nb.z = __shfl_up_sync(0xffffffffu, a.z, 1); nb.w = __shfl_up_sync(0xffffffffu, a.w, 1);
+            } else {
+                nb.x = __shfl_down_sync(0xffffffffu, a.x, 1); nb.y = __shfl_down_sync(0xffffffffu, a.y, 1);
+                nb.z = __shfl_down_sync(0xffffffffu, a.z, 1); nb.w = __shfl_down_sync(0xffffffffu, a.w, 1);
+            }
+            if (!edge) c = nb;
+            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+            x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+            x[8] = c.x; x[9] = c.y; x[10] = c.z; x[11] = c.w;
+        }
+        if (W >= wpr) continue;
+        // bit offset of the window inside x: 64 (q odd) + start mod 64, the same for every lane
+        const uint32_t o = (uint32_t)(start & 63) + ((q & 1) ? 64u : 0u);
+        const uint32_t s5 = o & 31u;
+        uint32_t y[8];
+        switch (o >> 5) {
+            case 0: fr_cut<0>(x, s5, y); break;
+            case 1: fr_cut<1>(x, s5, y); break;
+            case 2: fr_cut<2>(x, s5, y); break;
+            default: fr_cut<3>(x, s5, y); break;
+        }
+        uint4 lo4, hi4;                                                         // output words (W, W+1) and (W+2, W+3)
+        if (FLIP) {
+            lo4 = make_uint4(__brev(y[7]), __brev(y[6]), __brev(y[5]), __brev(y[4]));
+            hi4 = make_uint4(__brev(y[3]), __brev(y[2]), __brev(y[1]), __brev(y[0]));
+        } else {
+            lo4 = make_uint4(y[0], y[1], y[2], y[3]);
+            hi4 = make_uint4(y[4], y[5], y[6], y[7]);
+        }
+        // the last word of a ragged row keeps its pad bits 0 (a roll fills it from anywhere in the ring)
+        const int64_t last = wpr - 1 - W;                                       // which of the four is the row's last word
+        if ((n & 63) && last >= 0 && last < 4) {
+            const uint64_t m = (1ull << (n & 63)) - 1ull;
+            const uint32_t m0 = (uint32_t)m, m1 = (uint32_t)(m >> 32);
+            if (last == 0)      { lo4.x &= m0; lo4.y &= m1; }
+            else if (last == 1) { lo4.z &= m0; lo4.w &= m1; }
+            else if (last == 2) { hi4.x &= m0; hi4.y &= m1; }
+            else                { hi4.z &= m0; hi4.w &= m1; }
+        }
+        stg_stream(orow + W, lo4);
+        if (W + 2 < wpr) stg_stream(orow + W + 2, hi4);
     }
 }
 
@@ -372,6 +589,34 @@ extern "C" int brute_b200_reduce_rows(int op, const uint64_t* in, uint64_t* out,
     BB_REQUIRE(aligned8(in) && aligned8(out), BRUTE_ERR_MISALIGNED);
     BB_REQUIRE(outer <= 65535, BRUTE_ERR_UNSUPPORTED);
     cudaStream_t st = as_stream(stream);
+    if (R > 0 && (inner & 1) == 0 && aligned16(in) && aligned16(out)) {
+        // whole 16-byte vectors: the slab kernel, rows split over a cluster when the slabs are few
+        const bool narrow = ((inner + 63) / 64) * outer * 8 < 2 * (int64_t)kNumSMs;     // very few slabs: 256-byte ones
+        const int slab = narrow ? 32 : 64;
+        const int64_t slabs = (inner + slab - 1) / slab;
+        BB_REQUIRE(slabs <= 0x7fffffffll, BRUTE_ERR_UNSUPPORTED);
+        const int lanes = RR_THREADS / (slab / 2);
+        int csize = 1;
+        while (csize < 8 && slabs * outer * csize < 6 * (int64_t)kNumSMs && R / (2 * csize) >= 4 * lanes) csize *= 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)slabs, (unsigned)csize, (unsigned)outer);
+        cfg.blockDim = dim3(RR_THREADS);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = (unsigned)csize;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e;
+        if (narrow) e = (op == BRUTE_OP_OR) ? cudaLaunchKernelEx(&cfg, k_reduce_rows_slab<true, 16>, in, out, R, inner)
+                                            : cudaLaunchKernelEx(&cfg, k_reduce_rows_slab<false, 16>, in, out, R, inner);
+        else        e = (op == BRUTE_OP_OR) ? cudaLaunchKernelEx(&cfg, k_reduce_rows_slab<true, 32>, in, out, R, inner)
+                                            : cudaLaunchKernelEx(&cfg, k_reduce_rows_slab<false, 32>, in, out, R, inner);
+        return e == cudaSuccess ? launch_status() : BRUTE_ERR_LAUNCH;
+    }
     // identity of the reduction; an empty axis leaves it (any -> 0, all -> ~0, as torch does)
     if (cudaMemsetAsync(out, op == BRUTE_OP_OR ? 0x00 : 0xFF, (size_t)(outer * inner) * 8, st) != cudaSuccess)
         return BRUTE_ERR_LAUNCH;
@@ -398,6 +643,12 @@ extern "C" int brute_b200_flip_bits(const uint64_t* in, uint64_t* out, int64_t r
     BB_REQUIRE(in != nullptr && out != nullptr && in != out, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(aligned8(in) && aligned8(out), BRUTE_ERR_MISALIGNED);
     const int64_t wpr = (n + 63) / 64;
+    const int64_t chunks = (wpr + 127) / 128;
+    if ((wpr & 1) == 0 && wpr >= 64 && aligned16(in) && aligned16(out) && rows * chunks < (1ll << 31)) {
+        k_flip_roll_vec<true><<<stream_grid(rows * chunks, 8, 6), 256, 0, as_stream(stream)>>>(
+            in, out, (uint32_t)(rows * chunks), (uint32_t)chunks, n, wpr, 0);
+        return launch_status();
+    }
     k_flip_roll_bits<true><<<stream_grid(rows * wpr, 256, 8), 256, 0, as_stream(stream)>>>(in, out, rows, n, wpr, 0);
     return launch_status();
 }
@@ -410,6 +661,12 @@ extern "C" int brute_b200_roll_bits(const uint64_t* in, uint64_t* out, int64_t r
     const int64_t wpr = (n + 63) / 64;
     int64_t s = shift % n;
     if (s < 0) s += n;
+    const int64_t chunks = (wpr + 127) / 128;
+    if ((wpr & 1) == 0 && wpr >= 64 && aligned16(in) && aligned16(out) && rows * chunks < (1ll << 31)) {
+        k_flip_roll_vec<false><<<stream_grid(rows * chunks, 8, 6), 256, 0, as_stream(stream)>>>(
+            in, out, (uint32_t)(rows * chunks), (uint32_t)chunks, n, wpr, s);
+        return launch_status();
+    }
     k_flip_roll_bits<false><<<stream_grid(rows * wpr, 256, 8), 256, 0, as_stream(stream)>>>(in, out, rows, n, wpr, s);
     return launch_status();
 }

@@ -57,27 +57,96 @@ def shard_bounds(n: int, world_size: int, rank: int) -> tuple:
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+_comm_streams = {}
+
+
+def _comm_stream(dev: torch.device) -> "torch.cuda.Stream":
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _comm_streams:
+        _comm_streams[key] = torch.cuda.Stream(dev)
+    return _comm_streams[key]
+
+
+def _as_bytes(t: torch.Tensor) -> torch.Tensor:
+    """The collective moves bytes; neither NCCL nor gloo has a 16-bit integer type."""
+    return t.view(torch.uint8)
+
+
+def _gather_row_blocks(a_packed, b_local, K: int, world: int, group, row_blocks: Optional[int]) -> torch.Tensor:
+    """The replicated [M, N] result of an evenly column-sharded GEMM, every rank's block exchanged.
+
+    Two things keep the exchange from dominating (at 8 GPUs the plain int32 all-gather of a 16384^2
+    result takes five times as long as the rank's GEMM):
+    * for K <= 32767 the blocks travel as int16 (|C| <= K fits), half the bytes; the receiver widens
+      them while it lays them out, in one pass (``unstack_rank_blocks``);
+    * A's rows are cut into blocks: the all-gather of block i runs on a second stream while the GEMM
+      of block i+1 runs, ordered by events, no host synchronisation.
+    On CPU tensors (gloo) the same steps run one after the other.
+    """
+    import torch.distributed as dist
+
+    M, n_loc = int(a_packed.shape[0]), int(b_local.shape[0])
+    dev = a_packed.device
+    on_gpu = dev.type == "cuda"
+    narrow = int(K) <= 32767
+    nb = int(row_blocks) if row_blocks else max(1, min(8, M // 2048))
+    nb = max(1, min(nb, M)) if M else 1
+    out = torch.empty((M, world * n_loc), dtype=torch.int32, device=dev)
+    if on_gpu:
+        cur = torch.cuda.current_stream(dev)
+        comm = _comm_stream(dev)
+        comm.wait_stream(cur)
+    pending = None                        # (stage, first row, event) of the block whose gather is in flight
+    for i in range(nb):
+        m0, m1 = shard_bounds(M, nb, i)
+        if m1 == m0:
+            continue
+        c = _ops.xnor_popcount_matmul(a_packed[m0:m1], b_local, K)
+        send = _ops.narrow_i32_i16(c) if narrow else c
+        stage = torch.empty((world, m1 - m0, n_loc), dtype=send.dtype, device=dev)
+        done = None
+        if on_gpu:
+            ready = torch.cuda.Event()
+            ready.record(cur)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ready)
+                dist.all_gather_into_tensor(_as_bytes(stage.view(world * (m1 - m0), n_loc)), _as_bytes(send), group=group)
+                done = torch.cuda.Event()
+                done.record(comm)
+            send.record_stream(comm)
+            stage.record_stream(comm)
+        else:
+            dist.all_gather_into_tensor(_as_bytes(stage.view(world * (m1 - m0), n_loc)), _as_bytes(send), group=group)
+        if pending is not None:           # behind this block's GEMM: the previous gather ran under it
+            if on_gpu:
+                cur.wait_event(pending[2])
+            _ops.unstack_rank_blocks(pending[0], out, pending[1])
+        pending = (stage, m0, done)
+    if pending is not None:
+        if on_gpu:
+            cur.wait_event(pending[2])
+        _ops.unstack_rank_blocks(pending[0], out, pending[1])
+    return out
+
+
 def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group=None,
-                   gather: bool = False) -> torch.Tensor:
+                   gather: bool = False, row_blocks: Optional[int] = None) -> torch.Tensor:
     """Column-sharded xnor GEMM: this rank computes C[:, lo:hi] for its block of
-    B's rows. With ``gather`` the blocks are all-gathered (NCCL on GPUs) and
-    concatenated so every rank returns the full [M, N] matrix; the collective is
-    queued on the same stream right behind the GEMM, with no host sync between."""
+    B's rows. With ``gather`` the blocks are all-gathered (NCCL on GPUs) so that every rank
+    returns the full [M, N] matrix; the collective is ordered behind the GEMM by events, with no
+    host sync between (``_gather_row_blocks``)."""
     import torch.distributed as dist
 
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     N = b_packed.shape[0]
     lo, hi = shard_bounds(N, world, rank)
+    if gather and world > 1 and N % world == 0:
+        return _gather_row_blocks(a_packed, b_packed[lo:hi], K, world, group, row_blocks)
     c_local = _ops.xnor_popcount_matmul(a_packed, b_packed[lo:hi], K)
     if not gather or world == 1:
         return c_local
     M = a_packed.shape[0]
-    if N % world == 0:
-        # rank blocks arrive stacked along dim 0: [world * M, N / world]
-        stacked = torch.empty((world * M, N // world), dtype=c_local.dtype, device=c_local.device)
-        dist.all_gather_into_tensor(stacked, c_local.contiguous(), group=group)
-        return stacked.view(world, M, N // world).permute(1, 0, 2).reshape(M, N)
     # uneven blocks: pad every block to the widest one, gather, drop the padding
     widths = [shard_bounds(N, world, r)[1] - shard_bounds(N, world, r)[0] for r in range(world)]
     wmax = max(widths)

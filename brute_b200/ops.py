@@ -12,7 +12,8 @@ Ops beyond the reference's eleven carry new names and never change the eleven:
 ``pack_sign``, ``bitwise_packed``, ``select_packed``, ``row_any``, ``row_all``,
 ``xnor_popcount_matmul_impl``, ``xnor_matmul_scale_sign_pack``,
 ``binary_attention``, ``transpose_packed``, ``reduce_rows_packed``, ``flip_packed``,
-``roll_packed``, ``gather_packed``, ``scatter_packed_``. ``signed_bundle`` keeps the reference's schema and
+``roll_packed``, ``gather_packed``, ``scatter_packed_``, ``narrow_i32_i16``,
+``unstack_rank_blocks``. ``signed_bundle`` keeps the reference's schema and
 runs on the tensor cores; the scratch it needs is allocated here, never by the library.
 """
 from __future__ import annotations
@@ -51,6 +52,8 @@ _DEF.define("reduce_rows_packed(Tensor packed, int dim, bool use_or) -> Tensor")
 _DEF.define("flip_packed(Tensor packed, int n) -> Tensor")
 _DEF.define("roll_packed(Tensor packed, int n, int shift) -> Tensor")
 _DEF.define("gather_packed(Tensor packed, Tensor idx, int n_in) -> Tensor")
+_DEF.define("narrow_i32_i16(Tensor x) -> Tensor")
+_DEF.define("unstack_rank_blocks(Tensor stacked, Tensor(a!) out, int row0) -> Tensor(a!)")
 _DEF.define("scatter_packed_(Tensor(a!) packed, Tensor idx, Tensor? src, bool value, int n) -> Tensor(a!)")
 
 _PACK_WIDTH = 64
@@ -501,6 +504,35 @@ def scatter_packed_(packed: torch.Tensor, idx: torch.Tensor, src, value: bool, n
     return packed
 
 
+def narrow_i32_i16(x: torch.Tensor) -> torch.Tensor:
+    """int32 -> int16, exact for |v| <= 32767: the transport form of a GEMM block with K <= 32767."""
+    _check(x.dtype == torch.int32, "narrow_i32_i16: input must be int32")
+    xc = x.contiguous()
+    out = torch.empty(xc.shape, dtype=torch.int16, device=xc.device)
+    if xc.numel():
+        with _device_guard(xc.device):
+            L.check(_lib.brute_b200_narrow_i32_i16(xc.data_ptr(), out.data_ptr(), xc.numel(), _stream(xc)), "narrow_i32_i16")
+    return out
+
+
+def unstack_rank_blocks(stacked: torch.Tensor, out: torch.Tensor, row0: int) -> torch.Tensor:
+    """stacked [world, rows, n_loc] (int16 or int32: what an all-gather of the rank blocks delivers)
+    -> out[row0 : row0 + rows, :] of the row-major int32 result [M, world * n_loc], in place."""
+    _check(stacked.dim() == 3 and stacked.dtype in (torch.int16, torch.int32) and stacked.is_contiguous(),
+           "unstack_rank_blocks: stacked must be a contiguous int16/int32 [world, rows, n_loc] tensor")
+    world, rows, n_loc = (int(v) for v in stacked.shape)
+    _check(out.dim() == 2 and out.dtype == torch.int32 and out.is_contiguous() and out.size(1) == world * n_loc,
+           "unstack_rank_blocks: out must be a contiguous int32 [M, world * n_loc] tensor")
+    row0 = int(row0)
+    _check(0 <= row0 and row0 + rows <= out.size(0), "unstack_rank_blocks: rows out of range")
+    if stacked.numel():
+        with _device_guard(out.device):
+            L.check(_lib.brute_b200_unstack_rank_blocks(stacked.data_ptr(), stacked.element_size(),
+                                                        out.data_ptr() + row0 * out.size(1) * 4, world, rows, n_loc,
+                                                        out.size(1), _stream(out)), "unstack_rank_blocks")
+    return out
+
+
 def randomize_bits(out: torch.Tensor) -> torch.Tensor:
     out.random_()          # cbrute/cuda/ops_cuda.cu:340, a plain ATen call
     return out
@@ -538,7 +570,7 @@ _CUDA_IMPLS = {
     "xnor_matmul_scale_sign_pack": xnor_matmul_scale_sign_pack, "binary_attention": binary_attention,
     "transpose_packed": transpose_packed, "reduce_rows_packed": reduce_rows_packed,
     "flip_packed": flip_packed, "roll_packed": roll_packed, "gather_packed": gather_packed,
-    "scatter_packed_": scatter_packed_,
+    "scatter_packed_": scatter_packed_, "narrow_i32_i16": narrow_i32_i16, "unstack_rank_blocks": unstack_rank_blocks,
 }
 _IMPL = torch.library.Library("brute", "IMPL", "CUDA")
 for _name, _fn in _CUDA_IMPLS.items():
@@ -580,6 +612,8 @@ def _register_fakes() -> None:
     reg("brute::roll_packed")(lambda packed, n, shift: torch.empty_like(packed))
     reg("brute::gather_packed")(
         lambda packed, idx, n_in: packed.new_empty(tuple(packed.shape[:-1]) + (_words(idx.shape[0]),), dtype=torch.int64))
+    reg("brute::narrow_i32_i16")(lambda x: torch.empty_like(x, dtype=torch.int16))
+    reg("brute::unstack_rank_blocks")(lambda stacked, out, row0: out)
     reg("brute::scatter_packed_")(lambda packed, idx, src, value, n: packed)
     reg("brute::reduce_rows_packed")(
         lambda packed, dim, use_or: packed.new_empty(tuple(s for i, s in enumerate(packed.shape) if i != dim % packed.dim()),

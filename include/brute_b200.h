@@ -265,6 +265,18 @@ int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, uint64_t* ou
                                 int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D,
                                 void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ---- transport of the GEMM result between GPUs -------------------------- */
+/* The reference has no multi-GPU path; these serve the all-gather of the column-sharded GEMM
+ * (the result of cbrute/cuda/ops_cuda.cu:144-221 split by B's rows across ranks).
+ * narrow: int32 [n] -> int16 [n], exact for |v| <= 32767 (C = K - 2H with K <= 32767), so that the
+ * ranks exchange half the bytes.
+ * unstack: what an all-gather delivers, the rank blocks stacked as in [world, rows, n_loc]
+ * (elem_bytes 2: int16, 4: int32), becomes row-major int32: out[m * ldc + r * n_loc + j] =
+ * in[r, m, j]; ldc >= world * n_loc. in and out must not overlap. */
+int brute_b200_narrow_i32_i16(const int32_t* in, int16_t* out, int64_t n, void* stream);
+int brute_b200_unstack_rank_blocks(const void* in, int elem_bytes, int32_t* out,
+                                   int64_t world, int64_t rows, int64_t n_loc, int64_t ldc, void* stream);
+
 /* ---- binary attention -------------------------------------------------- */
 /* Qp, Kp_ [B, H, S, D/64] words (sign-binarised Q and K), V and O bf16
  * [B, H, S, D]; score(i,j) = (D - 2*popcount(q_i ^ k_j)) * scale, optional

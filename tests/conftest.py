@@ -161,6 +161,13 @@ def install_oracle_cpu_ops():
         packed.copy_(n2t(res).reshape(packed.shape))
         return packed
     lib.impl("scatter_packed_", scatter_packed_)
+    lib.impl("narrow_i32_i16", lambda x: x.to(torch.int16))
+
+    def unstack_rank_blocks(stacked, out, row0):
+        world, rows, n_loc = stacked.shape
+        out[row0:row0 + rows] = stacked.permute(1, 0, 2).reshape(rows, world * n_loc).to(torch.int32)
+        return out
+    lib.impl("unstack_rank_blocks", unstack_rank_blocks)
     lib.impl("reduce_rows_packed", lambda packed, dim, use_or: n2t(co.reduce_rows(t2n(packed.contiguous()), dim, use_or), torch.int64))
 
     def randomize(out):

@@ -46,7 +46,9 @@ def pack_lsb_first(bits: np.ndarray) -> np.ndarray:
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference>")
+    ref_root = Path(sys.argv[1])
     ref = load_reference_ops(ref_root)
     rng = np.random.default_rng(1234)          # the reference's default BRUTE_TEST_SEED
     out = {}

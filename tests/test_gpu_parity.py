@@ -525,7 +525,10 @@ def test_transpose_packed(ops, co, shape):
 
 
 @pytest.mark.parametrize("shape,dim", [((5, 70), 0), ((1, 3), 0), ((4, 6, 130), 1), ((4, 6, 130), 0), ((2, 1, 64), 1),
-                                       ((1000, 4097), 0), ((3, 100000, 65), 1), ((70000, 64), 0)])
+                                       ((1000, 4097), 0), ((3, 100000, 65), 1), ((70000, 64), 0),
+                                       # rows of whole 16-byte vectors: the slab kernel, with and without a cluster split of the rows
+                                       ((4096, 128), 0), ((5000, 8192), 0), ((3, 70, 256), 1), ((2, 1000, 128 * 70), 1),
+                                       ((9, 20000), 0), ((33, 2, 64 * 6), 0), ((1, 128), 0), ((64, 64 * 66 - 3), 0)])
 def test_reduce_rows_packed(ops, co, shape, dim):
     import brute_b200 as brute
     x = torch.rand(shape, generator=gen(sum(shape))) < 0.999
@@ -541,7 +544,11 @@ def test_reduce_rows_packed(ops, co, shape, dim):
         ops.reduce_rows_packed(p, len(shape) - 1, True)
 
 
-@pytest.mark.parametrize("shape", [(1,), (5,), (64,), (65,), (3, 130), (2, 3, 257), (4, 1003), (7, 4097), (1, 1 << 20), (300, 6400)])
+@pytest.mark.parametrize("shape", [(1,), (5,), (64,), (65,), (3, 130), (2, 3, 257), (4, 1003), (7, 4097), (1, 1 << 20), (300, 6400),
+                                   # even word counts >= 64 per row: the vector kernel (exact, ragged, partial last chunk)
+                                   (3, 4096), (5, 4096 + 64), (4, 64 * 66 - 5), (2, 64 * 130 - 63), (9, 8192 + 128 - 1),
+                                   (2, 3, 64 * 64 * 3), (1, (1 << 20) - 5), (17, 64 * 200),
+                                   (3, 64 * 130 - 7), (2, 64 * 258 - 1), (5, 64 * 126), (2, 64 * 254 - 33)])
 def test_flip_roll_gather_packed(ops, co, shape):
     x = torch.rand(shape, generator=gen(sum(shape))) < 0.5
     n = shape[-1]
@@ -794,3 +801,24 @@ def test_scatter_bits_vs_oracle(ops, co, rows, n, n_idx):
     rep = torch.tensor([0, n - 1, 0, n - 1, n + 5, -1], dtype=torch.int64)
     got = ops.scatter_packed_(packed.clone(), rep.to(DEV), None, True, n)
     assert np.array_equal(u64(got), co.scatter_bits(want_base, rep.numpy(), None, 1, n))
+
+
+# ---------------------------------------------------------------------------
+# transport of GEMM blocks between ranks (int16 on the wire, widened and laid out on arrival)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("world,rows,n_loc", [(2, 64, 128), (8, 33, 8), (3, 5, 7), (4, 1, 1000), (1, 17, 24)])
+def test_narrow_and_unstack_rank_blocks(ops, world, rows, n_loc):
+    g = gen(world * rows + n_loc)
+    c = torch.randint(-32767, 32768, (world, rows, n_loc), generator=g, dtype=torch.int32)
+    c[0, 0, 0], c[-1, -1, -1] = -32767, 32767
+    cd = c.to(DEV)
+    n16 = ops.narrow_i32_i16(cd)
+    assert n16.dtype == torch.int16 and torch.equal(n16.cpu(), c.to(torch.int16))
+    assert torch.equal(ops.narrow_i32_i16(cd.view(-1)[1:]).cpu(), c.view(-1)[1:].to(torch.int16))   # unaligned base
+    want = c.permute(1, 0, 2).reshape(rows, world * n_loc)
+    M = rows + 3
+    for stacked in (n16, cd):
+        out = torch.full((M, world * n_loc), 12345, dtype=torch.int32, device=DEV)
+        ops.unstack_rank_blocks(stacked, out, 2)
+        assert torch.equal(out[2:2 + rows].cpu(), want)
+        assert bool((out[:2] == 12345).all()) and bool((out[2 + rows:] == 12345).all())

@@ -37,6 +37,14 @@ def _worker(rank, world, port, n_rows, result_dir):
     assert torch.equal(local, full[:, lo:hi])
     gathered = sharded_matmul(ap, bp, K, gather=True)
     assert torch.equal(gathered, full)
+    # the pipelined gather: several row blocks, int16 transport (K <= 32767) and int32 transport
+    for blocks in (1, 2, 4, 9):
+        assert torch.equal(sharded_matmul(ap, bp, K, gather=True, row_blocks=blocks), full), blocks
+    import brute_b200.kernels as kernels
+    full_wide = torch.ops.brute.xnor_popcount_matmul(ap, bp, K)
+    wide = kernels._gather_row_blocks(ap, bp[lo:hi], 40000, world, None, 3) if n_rows % world == 0 else None
+    if wide is not None:          # K > 32767 keeps int32 on the wire; the integers differ only by the K offset
+        assert torch.equal(wide - (40000 - K), full_wide)
     np.save(os.path.join(result_dir, f"ok{rank}.npy"), np.array([lo, hi]))
     dist.barrier()
     dist.destroy_process_group()
