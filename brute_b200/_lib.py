@@ -42,6 +42,7 @@ SIGNATURES = {
     "brute_b200_row_any": [_p, _p, _i64, _i64, _p],
     "brute_b200_row_all": [_p, _p, _i64, _i64, _i64, _p],
     "brute_b200_xnor_gemm": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _p],
+    "brute_b200_xnor_gemm_leave_sms": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _p],
     "brute_b200_xnor_gemm_scale_sign_pack": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32, _p],
     "brute_b200_signed_bundle": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p],
     "brute_b200_signed_bundle_workspace_bytes": [_i64, _i64, _i64],

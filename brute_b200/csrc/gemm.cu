@@ -18,6 +18,7 @@ struct GemmArgs {
     // fused scale + sign + pack output
     const float* scale; uint64_t* out; int mode;
     bool pack;
+    int leave_sms = 0;          // SMs the persistent tensor-core kernel leaves to other streams
 };
 
 static int run_popc(const GemmArgs& g, cudaStream_t st) {
@@ -98,7 +99,7 @@ static int dispatch(const GemmArgs& g, int impl, cudaStream_t st) {
         case BRUTE_GEMM_TCGEN05:
             return tc5_run(g.A, g.B, g.M, g.N, g.Kp, g.K, g.C, g.ldc, g.scale, g.out, g.mode, g.pack, st);
         case BRUTE_GEMM_TCGEN05_PAIR:
-            return tc5_pair_run(g.A, g.B, g.M, g.N, g.Kp, g.K, g.C, g.ldc, g.scale, g.out, g.mode, g.pack, st);
+            return tc5_pair_run(g.A, g.B, g.M, g.N, g.Kp, g.K, g.C, g.ldc, g.scale, g.out, g.mode, g.pack, st, g.leave_sms);
         default: return BRUTE_ERR_INVALID_ARG;
     }
 }
@@ -121,6 +122,23 @@ extern "C" int brute_b200_xnor_gemm(const uint64_t* A, const uint64_t* B, int32_
     GemmArgs g{A, B, M, N, Kp, K, C, ldc, nullptr, nullptr, 0, false};
     if (Kp == 0) return run_popc(g, as_stream(stream));     // C = K (= 0) everywhere
     return dispatch(g, impl, as_stream(stream));
+}
+
+extern "C" int brute_b200_xnor_gemm_leave_sms(const uint64_t* A, const uint64_t* B, int32_t* C,
+                                              int64_t M, int64_t N, int64_t Kp, int64_t K, int64_t ldc,
+                                              int leave_sms, void* stream) {
+    BB_REQUIRE(M >= 0 && N >= 0 && Kp >= 0 && K >= 0 && K <= 64 * Kp, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(K < (1ll << 30) && M < (1ll << 31) && N < (1ll << 31), BRUTE_ERR_UNSUPPORTED);
+    BB_REQUIRE(leave_sms >= 0 && leave_sms <= kNumSMs - 2, BRUTE_ERR_INVALID_ARG);
+    if (M == 0 || N == 0) return BRUTE_OK;
+    BB_REQUIRE(C != nullptr && ldc >= N, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE((reinterpret_cast<uintptr_t>(C) & 3u) == 0, BRUTE_ERR_MISALIGNED);
+    BB_REQUIRE(Kp == 0 || (A != nullptr && B != nullptr), BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(aligned8(A) && aligned8(B), BRUTE_ERR_MISALIGNED);
+    GemmArgs g{A, B, M, N, Kp, K, C, ldc, nullptr, nullptr, 0, false};
+    g.leave_sms = leave_sms;
+    if (Kp == 0) return run_popc(g, as_stream(stream));
+    return dispatch(g, BRUTE_GEMM_AUTO, as_stream(stream));
 }
 
 extern "C" int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B,

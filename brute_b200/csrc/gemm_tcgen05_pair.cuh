@@ -540,7 +540,7 @@ template <int STORE>
 static int tc5_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                            int64_t M, int64_t N, int32_t nkb, int32_t klogical, int32_t tiles_m, int32_t ntiles,
                            int32_t* C, int64_t ldc, const float* scale, uint32_t* out32, int64_t halves_per_row, int mode,
-                           cudaStream_t st) {
+                           cudaStream_t st, int leave_sms = 0) {
     static int max_pairs_dev[64] = {0};     // per device: pairs of SMs that can hold this kernel at once
     auto kern = k_xnor_gemm_tcgen05_pair<STORE>;
     int dev = 0;
@@ -559,7 +559,11 @@ static int tc5_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const
         if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sms / 2; }
         max_pairs = n < sms / 2 ? n : sms / 2;
     }
-    const int pairs = ntiles < max_pairs ? ntiles : max_pairs;
+    // leave_sms: SMs that the caller wants free for kernels of other streams (a collective that runs
+    // under this GEMM); the persistent grid walks the same tiles with fewer CTA pairs
+    int cap = max_pairs - (leave_sms + 1) / 2;
+    if (cap < 1) cap = 1;
+    const int pairs = ntiles < cap ? ntiles : cap;
     cfg.gridDim = dim3((unsigned)(2 * pairs));
     if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, M, N, nkb, klogical, tiles_m, ntiles, C, ldc, scale, out32,
                            halves_per_row, mode) != cudaSuccess)
@@ -569,7 +573,7 @@ static int tc5_pair_launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const
 
 static int tc5_pair_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp, int64_t K,
                         int32_t* C, int64_t ldc, const float* scale, uint64_t* out, int mode, bool pack,
-                        cudaStream_t st) {
+                        cudaStream_t st, int leave_sms = 0) {
     BB_REQUIRE(tc5_accepts(A, B, M, N, Kp) && tc5_pair_accepts(M, N), BRUTE_ERR_UNSUPPORTED);
     CUtensorMap tmA, tmB, tmC;
     BB_REQUIRE(tc5_make_map(&tmA, A, M, Kp * 8, TP_BM) && tc5_make_map(&tmB, B, N, Kp * 8, TP_BNH), BRUTE_ERR_DRIVER);
@@ -582,9 +586,9 @@ static int tc5_pair_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t
                                   reinterpret_cast<uint32_t*>(out), 2 * ((N + 63) / 64), mode, st);
     }
     if (aligned16(C) && (ldc % 4) == 0 && tc5_make_c_map(&tmC, C, M, N, ldc))
-        return tc5_pair_launch<0>(tmA, tmB, tmC, M, N, nkb, (int32_t)K, tiles_m, ntiles, C, ldc, nullptr, nullptr, 0, 0, st);
+        return tc5_pair_launch<0>(tmA, tmB, tmC, M, N, nkb, (int32_t)K, tiles_m, ntiles, C, ldc, nullptr, nullptr, 0, 0, st, leave_sms);
     tmC = tmA;
-    return tc5_pair_launch<1>(tmA, tmB, tmC, M, N, nkb, (int32_t)K, tiles_m, ntiles, C, ldc, nullptr, nullptr, 0, 0, st);
+    return tc5_pair_launch<1>(tmA, tmB, tmC, M, N, nkb, (int32_t)K, tiles_m, ntiles, C, ldc, nullptr, nullptr, 0, 0, st, leave_sms);
 }
 
 }  // namespace bb

@@ -63,7 +63,8 @@ _comm_streams = {}
 def _comm_stream(dev: torch.device) -> "torch.cuda.Stream":
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     if key not in _comm_streams:
-        _comm_streams[key] = torch.cuda.Stream(dev)
+        # high priority: its kernels take the SMs that a co-running GEMM leaves free as soon as they are due
+        _comm_streams[key] = torch.cuda.Stream(dev, priority=-1)
     return _comm_streams[key]
 
 
@@ -72,15 +73,19 @@ def _as_bytes(t: torch.Tensor) -> torch.Tensor:
     return t.view(torch.uint8)
 
 
-def _gather_row_blocks(a_packed, b_local, K: int, world: int, group, row_blocks: Optional[int]) -> torch.Tensor:
+def _gather_row_blocks(a_packed, b_local, K: int, world: int, group, row_blocks: Optional[int],
+                       leave_sms: int = 32) -> torch.Tensor:
     """The replicated [M, N] result of an evenly column-sharded GEMM, every rank's block exchanged.
 
-    Two things keep the exchange from dominating (at 8 GPUs the plain int32 all-gather of a 16384^2
-    result takes five times as long as the rank's GEMM):
+    Three things keep the exchange from dominating (at 8 GPUs the plain int32 all-gather of a
+    16384^2 result takes five times as long as the rank's GEMM):
     * for K <= 32767 the blocks travel as int16 (|C| <= K fits), half the bytes; the receiver widens
       them while it lays them out, in one pass (``unstack_rank_blocks``);
     * A's rows are cut into blocks: the all-gather of block i runs on a second stream while the GEMM
-      of block i+1 runs, ordered by events, no host synchronisation.
+      of block i+1 runs, ordered by events, no host synchronisation;
+    * the GEMM of a block that runs next to a gather leaves ``leave_sms`` SMs free: its persistent
+      kernel would otherwise hold every SM and the collective's kernel could only start after it
+      (NCCL moves about 30 GB/s per CTA here: 32 SMs carry the full rate of the links).
     On CPU tensors (gloo) the same steps run one after the other.
     """
     import torch.distributed as dist
@@ -89,44 +94,67 @@ def _gather_row_blocks(a_packed, b_local, K: int, world: int, group, row_blocks:
     dev = a_packed.device
     on_gpu = dev.type == "cuda"
     narrow = int(K) <= 32767
-    nb = int(row_blocks) if row_blocks else max(1, min(8, M // 2048))
+    nb = int(row_blocks) if row_blocks else max(1, min(4, M // 2048))
     nb = max(1, min(nb, M)) if M else 1
+    bounds = [shard_bounds(M, nb, i) for i in range(nb)]
+    bounds = [(m0, m1) for m0, m1 in bounds if m1 > m0]
     out = torch.empty((M, world * n_loc), dtype=torch.int32, device=dev)
+    # scratch of the call, kept between calls of one shape (see release_gather_workspace): this rank's
+    # int32 blocks, their int16 form, and the staging area the rank blocks of every row block land in
+    c_all, send_all, stage = _gather_workspace(dev, M, n_loc, world, narrow)
     if on_gpu:
         cur = torch.cuda.current_stream(dev)
         comm = _comm_stream(dev)
         comm.wait_stream(cur)
-    pending = None                        # (stage, first row, event) of the block whose gather is in flight
-    for i in range(nb):
-        m0, m1 = shard_bounds(M, nb, i)
-        if m1 == m0:
-            continue
-        c = _ops.xnor_popcount_matmul(a_packed[m0:m1], b_local, K)
-        send = _ops.narrow_i32_i16(c) if narrow else c
-        stage = torch.empty((world, m1 - m0, n_loc), dtype=send.dtype, device=dev)
+    pending = None                        # (first row, last row, event) of the block whose gather is in flight
+    for i, (m0, m1) in enumerate(bounds):
+        leave = int(leave_sms) if (on_gpu and i > 0) else 0
+        c = _ops.xnor_popcount_matmul_out(a_packed[m0:m1], b_local, K, leave, c_all[m0:m1])
+        send = _ops.narrow_i32_i16_out(c, send_all[m0:m1]) if narrow else c
+        recv = stage[m0 * world:m1 * world]
         done = None
         if on_gpu:
             ready = torch.cuda.Event()
             ready.record(cur)
             with torch.cuda.stream(comm):
                 comm.wait_event(ready)
-                dist.all_gather_into_tensor(_as_bytes(stage.view(world * (m1 - m0), n_loc)), _as_bytes(send), group=group)
+                dist.all_gather_into_tensor(_as_bytes(recv), _as_bytes(send), group=group)
                 done = torch.cuda.Event()
                 done.record(comm)
-            send.record_stream(comm)
-            stage.record_stream(comm)
         else:
-            dist.all_gather_into_tensor(_as_bytes(stage.view(world * (m1 - m0), n_loc)), _as_bytes(send), group=group)
+            dist.all_gather_into_tensor(_as_bytes(recv), _as_bytes(send), group=group)
         if pending is not None:           # behind this block's GEMM: the previous gather ran under it
+            p0, p1, ev = pending
             if on_gpu:
-                cur.wait_event(pending[2])
-            _ops.unstack_rank_blocks(pending[0], out, pending[1])
-        pending = (stage, m0, done)
+                cur.wait_event(ev)
+            _ops.unstack_rank_blocks(stage[p0 * world:p1 * world].view(world, p1 - p0, n_loc), out, p0)
+        pending = (m0, m1, done)
     if pending is not None:
+        p0, p1, ev = pending
         if on_gpu:
-            cur.wait_event(pending[2])
-        _ops.unstack_rank_blocks(pending[0], out, pending[1])
+            cur.wait_event(ev)             # the caller's stream is now behind every collective of the call
+        _ops.unstack_rank_blocks(stage[p0 * world:p1 * world].view(world, p1 - p0, n_loc), out, p0)
     return out
+
+
+_gather_ws = {}
+
+
+def _gather_workspace(dev, M: int, n_loc: int, world: int, narrow: bool):
+    key = (str(dev), M, n_loc, world, narrow)
+    ws = _gather_ws.get(key)
+    if ws is None:
+        c_all = torch.empty((M, n_loc), dtype=torch.int32, device=dev)
+        send_all = torch.empty((M, n_loc), dtype=torch.int16, device=dev) if narrow else None
+        stage = torch.empty((world * M, n_loc), dtype=torch.int16 if narrow else torch.int32, device=dev)
+        _gather_ws.clear()                # one shape at a time: a new shape replaces the old scratch
+        ws = _gather_ws[key] = (c_all, send_all, stage)
+    return ws
+
+
+def release_gather_workspace() -> None:
+    """Free the scratch that ``sharded_matmul(gather=True)`` keeps between calls of one shape."""
+    _gather_ws.clear()
 
 
 def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group=None,

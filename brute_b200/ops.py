@@ -10,7 +10,7 @@ CPU kernel and no fallback, an op on a CPU tensor fails in the dispatcher.
 
 Ops beyond the reference's eleven carry new names and never change the eleven:
 ``pack_sign``, ``bitwise_packed``, ``select_packed``, ``row_any``, ``row_all``,
-``xnor_popcount_matmul_impl``, ``xnor_matmul_scale_sign_pack``,
+``xnor_popcount_matmul_impl``, ``xnor_popcount_matmul_leave_sms``, ``xnor_matmul_scale_sign_pack``,
 ``binary_attention``, ``transpose_packed``, ``reduce_rows_packed``, ``flip_packed``,
 ``roll_packed``, ``gather_packed``, ``scatter_packed_``, ``narrow_i32_i16``,
 ``unstack_rank_blocks``. ``signed_bundle`` keeps the reference's schema and
@@ -45,6 +45,7 @@ _DEF.define("select_packed(Tensor cond, Tensor A, Tensor B) -> Tensor")
 _DEF.define("row_any(Tensor A) -> Tensor")
 _DEF.define("row_all(Tensor A, int last_dim_bits) -> Tensor")
 _DEF.define("xnor_popcount_matmul_impl(Tensor A, Tensor B, int K, int impl) -> Tensor")
+_DEF.define("xnor_popcount_matmul_leave_sms(Tensor A, Tensor B, int K, int leave_sms) -> Tensor")
 _DEF.define("xnor_matmul_scale_sign_pack(Tensor A, Tensor B, Tensor scale, int K, int mode) -> Tensor")
 _DEF.define("binary_attention(Tensor Qp, Tensor Kp, Tensor V, bool causal, float scale) -> Tensor")
 _DEF.define("transpose_packed(Tensor packed, int rows, int cols) -> Tensor")
@@ -53,6 +54,8 @@ _DEF.define("flip_packed(Tensor packed, int n) -> Tensor")
 _DEF.define("roll_packed(Tensor packed, int n, int shift) -> Tensor")
 _DEF.define("gather_packed(Tensor packed, Tensor idx, int n_in) -> Tensor")
 _DEF.define("narrow_i32_i16(Tensor x) -> Tensor")
+_DEF.define("narrow_i32_i16_out(Tensor x, Tensor(a!) out) -> Tensor(a!)")
+_DEF.define("xnor_popcount_matmul_out(Tensor A, Tensor B, int K, int leave_sms, Tensor(a!) out) -> Tensor(a!)")
 _DEF.define("unstack_rank_blocks(Tensor stacked, Tensor(a!) out, int row0) -> Tensor(a!)")
 _DEF.define("scatter_packed_(Tensor(a!) packed, Tensor idx, Tensor? src, bool value, int n) -> Tensor(a!)")
 
@@ -243,6 +246,19 @@ def xnor_popcount_matmul_impl(A: torch.Tensor, B: torch.Tensor, K: int, impl: in
 
 def xnor_popcount_matmul(A: torch.Tensor, B: torch.Tensor, K: int) -> torch.Tensor:
     return xnor_popcount_matmul_impl(A, B, K, L.GEMM_AUTO)
+
+
+def xnor_popcount_matmul_leave_sms(A: torch.Tensor, B: torch.Tensor, K: int, leave_sms: int) -> torch.Tensor:
+    """The same GEMM with `leave_sms` SMs left free for kernels of other streams (a collective)."""
+    Ac, Bc = _gemm_args(A, B, K, "xnor_popcount_matmul")
+    M, N, Kp = Ac.size(0), Bc.size(0), Ac.size(1)
+    C = torch.empty((M, N), dtype=torch.int32, device=Ac.device)
+    if M == 0 or N == 0:
+        return C
+    with _device_guard(Ac.device):
+        L.check(_lib.brute_b200_xnor_gemm_leave_sms(Ac.data_ptr(), Bc.data_ptr(), C.data_ptr(), M, N, Kp, int(K), N,
+                                                    int(leave_sms), _stream(Ac)), "xnor_popcount_matmul")
+    return C
 
 
 def xnor_matmul_scale_sign_pack(A, B, scale, K: int, mode: int) -> torch.Tensor:
@@ -515,6 +531,28 @@ def narrow_i32_i16(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def narrow_i32_i16_out(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _check(x.dtype == torch.int32 and out.dtype == torch.int16 and x.is_contiguous() and out.is_contiguous()
+           and x.numel() == out.numel(), "narrow_i32_i16_out: contiguous int32 input and int16 output of one size")
+    if x.numel():
+        with _device_guard(x.device):
+            L.check(_lib.brute_b200_narrow_i32_i16(x.data_ptr(), out.data_ptr(), x.numel(), _stream(x)), "narrow_i32_i16")
+    return out
+
+
+def xnor_popcount_matmul_out(A: torch.Tensor, B: torch.Tensor, K: int, leave_sms: int, out: torch.Tensor) -> torch.Tensor:
+    """The GEMM into a caller-provided contiguous int32 [M, N] tensor (no allocation in the call)."""
+    Ac, Bc = _gemm_args(A, B, K, "xnor_popcount_matmul")
+    M, N, Kp = Ac.size(0), Bc.size(0), Ac.size(1)
+    _check(out.dtype == torch.int32 and tuple(out.shape) == (M, N) and out.is_contiguous(),
+           "xnor_popcount_matmul_out: out must be a contiguous int32 [M, N] tensor")
+    if M and N:
+        with _device_guard(Ac.device):
+            L.check(_lib.brute_b200_xnor_gemm_leave_sms(Ac.data_ptr(), Bc.data_ptr(), out.data_ptr(), M, N, Kp, int(K), N,
+                                                        int(leave_sms), _stream(Ac)), "xnor_popcount_matmul")
+    return out
+
+
 def unstack_rank_blocks(stacked: torch.Tensor, out: torch.Tensor, row0: int) -> torch.Tensor:
     """stacked [world, rows, n_loc] (int16 or int32: what an all-gather of the rank blocks delivers)
     -> out[row0 : row0 + rows, :] of the row-major int32 result [M, world * n_loc], in place."""
@@ -567,10 +605,12 @@ _CUDA_IMPLS = {
     "randomize_bits": randomize_bits,
     "pack_sign": pack_sign, "bitwise_packed": bitwise_packed, "select_packed": select_packed,
     "row_any": row_any, "row_all": row_all, "xnor_popcount_matmul_impl": xnor_popcount_matmul_impl,
+    "xnor_popcount_matmul_leave_sms": xnor_popcount_matmul_leave_sms,
     "xnor_matmul_scale_sign_pack": xnor_matmul_scale_sign_pack, "binary_attention": binary_attention,
     "transpose_packed": transpose_packed, "reduce_rows_packed": reduce_rows_packed,
     "flip_packed": flip_packed, "roll_packed": roll_packed, "gather_packed": gather_packed,
     "scatter_packed_": scatter_packed_, "narrow_i32_i16": narrow_i32_i16, "unstack_rank_blocks": unstack_rank_blocks,
+    "narrow_i32_i16_out": narrow_i32_i16_out, "xnor_popcount_matmul_out": xnor_popcount_matmul_out,
 }
 _IMPL = torch.library.Library("brute", "IMPL", "CUDA")
 for _name, _fn in _CUDA_IMPLS.items():
@@ -592,6 +632,7 @@ def _register_fakes() -> None:
     reg("brute::unpack_bool")(lambda packed, logical_shape: packed.new_empty(list(logical_shape), dtype=torch.bool))
     reg("brute::unpack_bits")(lambda packed, logical_shape: packed.new_empty(list(logical_shape), dtype=torch.float32))
     reg("brute::xnor_popcount_matmul")(lambda A, B, K: A.new_empty((A.shape[0], B.shape[0]), dtype=torch.int32))
+    reg("brute::xnor_popcount_matmul_leave_sms")(lambda A, B, K, leave_sms: A.new_empty((A.shape[0], B.shape[0]), dtype=torch.int32))
     reg("brute::xnor_popcount_matmul_impl")(lambda A, B, K, impl: A.new_empty((A.shape[0], B.shape[0]), dtype=torch.int32))
     reg("brute::xnor_matmul_scale_sign_pack")(
         lambda A, B, scale, K, mode: A.new_empty((A.shape[0], _words(B.shape[0])), dtype=torch.int64))
@@ -613,6 +654,8 @@ def _register_fakes() -> None:
     reg("brute::gather_packed")(
         lambda packed, idx, n_in: packed.new_empty(tuple(packed.shape[:-1]) + (_words(idx.shape[0]),), dtype=torch.int64))
     reg("brute::narrow_i32_i16")(lambda x: torch.empty_like(x, dtype=torch.int16))
+    reg("brute::narrow_i32_i16_out")(lambda x, out: out)
+    reg("brute::xnor_popcount_matmul_out")(lambda A, B, K, leave_sms, out: out)
     reg("brute::unstack_rank_blocks")(lambda stacked, out, row0: out)
     reg("brute::scatter_packed_")(lambda packed, idx, src, value, n: packed)
     reg("brute::reduce_rows_packed")(

@@ -235,6 +235,15 @@ int brute_b200_xnor_gemm(const uint64_t* A, const uint64_t* B, int32_t* C,
                          int64_t M, int64_t N, int64_t Kp, int64_t K, int64_t ldc,
                          int impl, void* stream);
 
+/* The same GEMM (instruction path chosen as by BRUTE_GEMM_AUTO), leaving `leave_sms` SMs of the GPU
+ * to kernels of other streams: the persistent tensor-core kernel then walks its tiles with fewer CTA
+ * pairs, so that e.g. the all-gather of the previous row block can run under it. Same result, bit
+ * for bit; paths that are not persistent ignore the hint. The reference has no counterpart (it has
+ * no multi-GPU path); the contraction is that of cbrute/cuda/ops_cuda.cu:144-221. */
+int brute_b200_xnor_gemm_leave_sms(const uint64_t* A, const uint64_t* B, int32_t* C,
+                                   int64_t M, int64_t N, int64_t Kp, int64_t K, int64_t ldc,
+                                   int leave_sms, void* stream);
+
 /* Same contraction with the binarised-MLP epilogue fused: the int32 count is
  * scaled by scale[n] (fp32), thresholded per `mode` and re-packed, so
  * out [M, ceil(N/64)] words holds bit(m,n) = sign(scale[n] * C[m,n]).

@@ -138,6 +138,7 @@ def install_oracle_cpu_ops():
     lib.impl("unpack_bits", unpack_bits)
     lib.impl("xnor_popcount_matmul", gemm)
     lib.impl("xnor_popcount_matmul_impl", lambda A, B, K, impl: gemm(A, B, K))
+    lib.impl("xnor_popcount_matmul_leave_sms", lambda A, B, K, leave: gemm(A, B, K))
     lib.impl("xnor_matmul_scale_sign_pack", mlp)
     lib.impl("popcount", popcount)
     lib.impl("packed_popcount", packed_popcount)
@@ -162,6 +163,8 @@ def install_oracle_cpu_ops():
         return packed
     lib.impl("scatter_packed_", scatter_packed_)
     lib.impl("narrow_i32_i16", lambda x: x.to(torch.int16))
+    lib.impl("narrow_i32_i16_out", lambda x, out: out.copy_(x.to(torch.int16)))
+    lib.impl("xnor_popcount_matmul_out", lambda A, B, K, leave, out: out.copy_(gemm(A, B, K)))
 
     def unstack_rank_blocks(stacked, out, row0):
         world, rows, n_loc = stacked.shape
