@@ -87,7 +87,10 @@ def build_host_module(force: bool = False) -> Path:
     import sysconfig
     import torch
     tdir = Path(torch.__file__).resolve().parent
-    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    # The system g++, not $CXX: a toolchain that links libstdc++ statically (some CI wrappers do)
+    # would put a second copy of the iostream locale state into this module, and formatting a
+    # number in an error message would then crash. Checked below.
+    cxx = next((c for c in ("/usr/bin/g++", shutil.which("g++"), os.environ.get("CXX")) if c and Path(c).exists()), "g++")
     cuda_home = Path(_nvcc()).resolve().parent.parent
     cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-attributes",
            "-DTORCH_EXTENSION_NAME=_cbrute", "-DTORCH_API_INCLUDE_EXTENSION_H",
@@ -101,6 +104,11 @@ def build_host_module(force: bool = False) -> Path:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"building _cbrute failed:\n{res.stdout}\n{res.stderr}")
+    syms = subprocess.run(["nm", "-D", "--defined-only", str(HOST_MOD)], capture_output=True, text=True).stdout
+    if "_ZNKSt6locale2id5_M_idEv" in syms:
+        HOST_MOD.unlink()
+        raise RuntimeError(f"{cxx} linked libstdc++ statically into _cbrute.so; build it with a g++ that links "
+                           "libstdc++.so (the system compiler)")
     return HOST_MOD
 
 

@@ -18,6 +18,8 @@ runs on the tensor cores; the scratch it needs is allocated here, never by the l
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib as L
@@ -612,9 +614,25 @@ _CUDA_IMPLS = {
     "scatter_packed_": scatter_packed_, "narrow_i32_i16": narrow_i32_i16, "unstack_rank_blocks": unstack_rank_blocks,
     "narrow_i32_i16_out": narrow_i32_i16_out, "xnor_popcount_matmul_out": xnor_popcount_matmul_out,
 }
-_IMPL = torch.library.Library("brute", "IMPL", "CUDA")
-for _name, _fn in _CUDA_IMPLS.items():
-    _IMPL.impl(_name, _guarded(_name, _fn))
+# Two bindings of the CUDA dispatch key to the same C ABI, chosen by BRUTE_B200_BINDING at import:
+#   "cpp"     (default) the compiled functions of csrc_host/cbrute.cpp, the layer the reference has in
+#             cbrute/ext.cpp + cbrute/cuda/ops_cuda.cu: no Python between the dispatcher and the
+#             launch (6.4-7.5 us of host time per op against 11.4-14.7 us through ctypes). They ask
+#             the runtime for the current stream, as the reference's do, so inside a
+#             ``parallel_streams`` block they stay on the caller's stream;
+#   "ctypes"  the Python functions above, through ctypes: the binding whose ops rotate over the pool
+#             streams of ``parallel_streams``, and the one to read when following a call.
+BINDING = os.environ.get("BRUTE_B200_BINDING", "cpp").strip().lower() or "cpp"
+if BINDING not in ("cpp", "ctypes"):
+    raise ImportError(f"BRUTE_B200_BINDING must be 'cpp' or 'ctypes', got {BINDING!r}")
+_IMPL = None
+if BINDING == "cpp":
+    from . import _cbrute
+    _cbrute.register_cuda_ops()
+else:
+    _IMPL = torch.library.Library("brute", "IMPL", "CUDA")
+    for _name, _fn in _CUDA_IMPLS.items():
+        _IMPL.impl(_name, _guarded(_name, _fn))
 
 
 # Shape-only kernels so that FakeTensor / torch.compile tracing sees the ops
