@@ -18,32 +18,6 @@
 
 namespace bb {
 
-// lane L holds rows L (lo) and L + 32 (hi) of a 64 x 64 bit block; afterwards it holds rows L and
-// L + 32 of the transposed block
-__device__ __forceinline__ void transpose64x64(uint64_t& lo, uint64_t& hi, int lane) {
-    {
-        const uint64_t t = ((lo >> 32) ^ hi) & 0x00000000FFFFFFFFull;
-        lo ^= t << 32;
-        hi ^= t;
-    }
-    const uint64_t masks[5] = {0x0000FFFF0000FFFFull, 0x00FF00FF00FF00FFull, 0x0F0F0F0F0F0F0F0Full,
-                               0x3333333333333333ull, 0x5555555555555555ull};
-#pragma unroll
-    for (int s = 0; s < 5; ++s) {
-        const int j = 16 >> s;
-        const uint64_t m = masks[s];
-        // Rows k (lane bit j clear) and k + j (set) swap the bit blocks (m << j) of the first with
-        // the blocks m of the second. Both lanes compute the same t = ((x_k >> j) ^ x_{k+j}) & m
-        // from what they send and what they receive, and differ only in a shift amount.
-        const int sh = (lane & j) ? 0 : j;
-        const uint64_t slo = lo >> sh, shi = hi >> sh;
-        const uint64_t tlo = (slo ^ __shfl_xor_sync(0xffffffffu, slo, j)) & m;
-        const uint64_t thi = (shi ^ __shfl_xor_sync(0xffffffffu, shi, j)) & m;
-        lo ^= tlo << sh;
-        hi ^= thi << sh;
-    }
-}
-
 constexpr int TB_TILE = 512;            // bits per tile side = 8 blocks of 64: 64-byte runs on both sides
 constexpr int TB_BLOCKS = TB_TILE / 64;
 constexpr int TB_THREADS = 32 * TB_BLOCKS;

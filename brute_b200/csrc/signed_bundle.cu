@@ -74,6 +74,11 @@ extern "C" int brute_b200_signed_bundle(const int8_t* W, const uint64_t* V, uint
     if (B * M * Dp == 0) return BRUTE_OK;
     BB_REQUIRE(out != nullptr && (N == 0 || (W != nullptr && V != nullptr)), BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(aligned8(V) && aligned8(out), BRUTE_ERR_MISALIGNED);
+    // The tensor-core kernel with the bit transpose of V fused into its expander warps: one launch,
+    // no scratch. Shapes outside the TMA rules, and rows padded beyond ceil(D/64) words (the tensor
+    // path writes only that many words of every output row), take the CUDA-core kernel below.
+    if (st_accepts(W, B, M, N, D) && Dp == (D + 63) / 64)
+        return st_run(W, V, out, B, M, N, Dp, D, as_stream(stream), /*fused=*/true);
     BB_REQUIRE(B <= 65535 && (M + SB_ROWS - 1) / SB_ROWS <= 65535, BRUTE_ERR_UNSUPPORTED);
     const dim3 grid((unsigned)Dp, (unsigned)((M + SB_ROWS - 1) / SB_ROWS), (unsigned)B);
     k_signed_bundle<<<grid, SB_THREADS, 0, as_stream(stream)>>>(W, V, out, M, N, Dp, D);
@@ -108,7 +113,7 @@ extern "C" int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, u
     // V [B, N, Dp] holds D valid bits per row: transpose the [N x D] bit matrices into [D x N]
     const int rc = brute_b200_transpose_bits(V, Vt, B, N, D, stream);
     if (rc != BRUTE_OK) return rc;
-    return st_run(W, Vt, out, B, M, N, Dp, D, as_stream(stream));
+    return st_run(W, Vt, out, B, M, N, Dp, D, as_stream(stream), /*fused=*/false);
 }
 
 // ---------------------------------------------------------------------------

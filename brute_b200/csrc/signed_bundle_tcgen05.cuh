@@ -4,9 +4,12 @@
 //                = ( 2*T[m, d] - S[m] >= 0 ),  T = sum_n W[m, n] * bit(V[n, d]),  S[m] = sum_n W[m, n].
 // T is a GEMM with M = rows of W, N = d, K = n: W [M, N] int8 is already the K-major A operand and
 // goes from global memory straight into SWIZZLE_128B shared memory by TMA; the B operand is V
-// TRANSPOSED ([d, n], n contiguous), so the launcher first bit-transposes V into a workspace
-// (brute_b200_transpose_bits) and the kernel expands 128 bits of a Vt row into 128 bytes of 0/1
-// per k-block. S comes out of the same MMAs from one extra B row of ones (accumulator column 128).
+// TRANSPOSED ([d, n], n contiguous). FUSED: the expander warps read V itself and transpose each
+// 128 (n) x 128 (d) bit block in registers, one 64 x 64 butterfly per warp and k-block, so the op is
+// ONE launch and needs no workspace. Otherwise (the entry points that take a workspace) the launcher
+// first bit-transposes V into it (brute_b200_transpose_bits) and a thread expands 128 bits of a Vt
+// row. Either way a bit becomes a byte of 0/1 in the K-major SWIZZLE_128B tile.
+// S comes out of the same MMAs from one extra B row of ones (accumulator column 128).
 // kind::i8 with A signed, B unsigned; M128 N144 K32, 4 per 128 bytes of n.
 //
 // The kernel streams W once: B*M*N bytes against B*M*N*D MACs, i.e. it is HBM bound once the
@@ -52,9 +55,10 @@ __device__ __forceinline__ uint32_t st_bits4_to_bytes(uint32_t w, int p) {
     return (((w >> p) & 0xFu) * 0x00204081u) & 0x01010101u;
 }
 
+template <bool FUSED>
 __global__ void __launch_bounds__(ST_THREADS, 2)
 k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
-                        const uint64_t* __restrict__ Vt /* [B, D, wpn] words, bit n of row d */,
+                        const uint64_t* __restrict__ Vt /* FUSED: V itself, [B, N, Dp] words; else [B, D, wpn] words, bit n of row d */,
                         uint64_t* __restrict__ out /* [B, M, Dp] */,
                         int64_t M, int64_t N, int64_t D, int64_t Dp, int64_t wpn,
                         int32_t m_tiles, int32_t d_blocks, int64_t items) {
@@ -192,12 +196,24 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
         for (int64_t it = blockIdx.x; it < items && ok; it += gridDim.x, ++n_items) {
             int64_t m0, dblk, b;
             item_coords(it, m0, dblk, b);
-            const int64_t d = dblk * ST_DB + t;
-            const uint64_t* vrow = Vt + (b * D + (d < D ? d : 0)) * wpn;
+            // FUSED: warp (rb, cb) owns the 64 (n) x 64 (d) bit block rb, cb of the k-block's 128 x 128:
+            // lane L loads word cb of rows n0 + 64 rb + L and + 32, the butterfly turns them into the
+            // 64 n-bits of d rows 64 cb + L and + 32, and the lane writes those two half rows.
+            const int wq = warp - 2, rb = wq >> 1, cb = wq & 1;
+            const int64_t d = FUSED ? dblk * ST_DB + 64 * cb + lane : dblk * ST_DB + t;      // FUSED: the first of its two d rows
+            const int64_t vword = 2 * dblk + cb;                                             // FUSED: word of a V row
+            const uint64_t* vrow = FUSED ? Vt + b * N * Dp : Vt + (b * D + (d < D ? d : 0)) * wpn;
             auto load_bits = [&](int32_t kb, uint64_t (&w)[2]) {
-                const int64_t w0 = 2 * (int64_t)kb;
-                w[0] = (kb < nkb && d < D && w0 < wpn) ? __ldg(vrow + w0) : 0ull;
-                w[1] = (kb < nkb && d < D && w0 + 1 < wpn) ? __ldg(vrow + w0 + 1) : 0ull;
+                if (FUSED) {
+                    const int64_t n = (int64_t)kb * ST_KB + 64 * rb + lane;
+                    const bool live = kb < nkb && vword < Dp;
+                    w[0] = (live && n < N) ? __ldg(vrow + n * Dp + vword) : 0ull;
+                    w[1] = (live && n + 32 < N) ? __ldg(vrow + (n + 32) * Dp + vword) : 0ull;
+                } else {
+                    const int64_t w0 = 2 * (int64_t)kb;
+                    w[0] = (kb < nkb && d < D && w0 < wpn) ? __ldg(vrow + w0) : 0ull;
+                    w[1] = (kb < nkb && d < D && w0 + 1 < wpn) ? __ldg(vrow + w0 + 1) : 0ull;
+                }
             };
             // the packed words are fetched ST_VPF k-blocks ahead (a ring of registers): one ahead
             // leaves the load latency on the path of every k-block
@@ -215,13 +231,32 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
                     ok = __all_sync(0xffffffffu, mbar_wait(b_empty(sb), ((g / ST_BSTAGES) & 1u) ^ 1u, abort_flag, 24));
                     if (!ok) break;
                     ++g;
-                    const uint64_t (&cur)[2] = ring[u];
-                    uint8_t* row = gb + sb * ST_B_TILE + t * 128;
+                    if (FUSED) {
+                        uint64_t lo = ring[u][0], hi = ring[u][1];
+                        transpose64x64(lo, hi, lane);         // lo: d row 64 cb + lane, hi: + 32; bit j = n0 + 64 rb + j
+                        if (d >= D) lo = 0ull;
+                        if (d + 32 >= D) hi = 0ull;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {             // chunk c: bytes 16c .. 16c+15 = bits 16c .. 16c+15
-                        const uint32_t w32 = (uint32_t)(cur[c >> 2] >> (16 * (c & 3)));
-                        *reinterpret_cast<uint4*>(row + ((c ^ (t & 7)) << 4)) =
-                            make_uint4(st_bits4_to_bytes(w32, 0), st_bits4_to_bytes(w32, 4), st_bits4_to_bytes(w32, 8), st_bits4_to_bytes(w32, 12));
+                        for (int h = 0; h < 2; ++h) {
+                            const int r = 64 * cb + lane + 32 * h;
+                            const uint64_t bitsr = h ? hi : lo;
+                            uint8_t* row = gb + sb * ST_B_TILE + r * 128;
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {     // chunk 4 rb + c of the row: its 16 bits 16 c .. 16 c + 15
+                                const uint32_t w32 = (uint32_t)(bitsr >> (16 * c));
+                                *reinterpret_cast<uint4*>(row + (((4 * rb + c) ^ (r & 7)) << 4)) =
+                                    make_uint4(st_bits4_to_bytes(w32, 0), st_bits4_to_bytes(w32, 4), st_bits4_to_bytes(w32, 8), st_bits4_to_bytes(w32, 12));
+                            }
+                        }
+                    } else {
+                        const uint64_t (&cur)[2] = ring[u];
+                        uint8_t* row = gb + sb * ST_B_TILE + t * 128;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {         // chunk c: bytes 16c .. 16c+15 = bits 16c .. 16c+15
+                            const uint32_t w32 = (uint32_t)(cur[c >> 2] >> (16 * (c & 3)));
+                            *reinterpret_cast<uint4*>(row + ((c ^ (t & 7)) << 4)) =
+                                make_uint4(st_bits4_to_bytes(w32, 0), st_bits4_to_bytes(w32, 4), st_bits4_to_bytes(w32, 8), st_bits4_to_bytes(w32, 12));
+                        }
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -290,17 +325,23 @@ static bool st_accepts(const int8_t* W, int64_t B, int64_t M, int64_t N, int64_t
            B <= 65535 && (M + ST_BM - 1) / ST_BM <= 0x7fffffffll && (D + ST_DB - 1) / ST_DB <= 65535;
 }
 
+// fused: `Vt` is V itself ([B, N, Dp]) and the kernel transposes on the fly; else the bit-transposed V
 static int st_run(const int8_t* W, const uint64_t* Vt, uint64_t* out, int64_t B, int64_t M, int64_t N,
-                  int64_t Dp, int64_t D, cudaStream_t st) {
+                  int64_t Dp, int64_t D, cudaStream_t st, bool fused) {
     CUtensorMap tmW;
     BB_REQUIRE(st_make_w_map(&tmW, W, B, M, N), BRUTE_ERR_DRIVER);
-    if (!kernel_smem_ready<k_signed_bundle_tcgen05>(ST_SMEM)) return BRUTE_ERR_LAUNCH;
+    if (!(fused ? kernel_smem_ready<k_signed_bundle_tcgen05<true>>(ST_SMEM)
+                : kernel_smem_ready<k_signed_bundle_tcgen05<false>>(ST_SMEM))) return BRUTE_ERR_LAUNCH;
     const int64_t m_tiles = (M + ST_BM - 1) / ST_BM, d_blocks = (D + ST_DB - 1) / ST_DB;
     const int64_t items = m_tiles * d_blocks * B;
     const int64_t resident = 2 * (int64_t)kNumSMs;                     // two CTAs per SM (shared memory)
     const unsigned grid = (unsigned)(items < resident ? items : resident);
-    k_signed_bundle_tcgen05<<<grid, ST_THREADS, ST_SMEM, st>>>(tmW, Vt, out, M, N, D, Dp, (N + 63) / 64,
-                                                              (int32_t)m_tiles, (int32_t)d_blocks, items);
+    if (fused)
+        k_signed_bundle_tcgen05<true><<<grid, ST_THREADS, ST_SMEM, st>>>(tmW, Vt, out, M, N, D, Dp, (N + 63) / 64,
+                                                                       (int32_t)m_tiles, (int32_t)d_blocks, items);
+    else
+        k_signed_bundle_tcgen05<false><<<grid, ST_THREADS, ST_SMEM, st>>>(tmW, Vt, out, M, N, D, Dp, (N + 63) / 64,
+                                                                        (int32_t)m_tiles, (int32_t)d_blocks, items);
     return launch_status();
 }
 

@@ -221,13 +221,9 @@ Tensor signed_bundle(const Tensor& W, const Tensor& V, int64_t D) {
     const c10::cuda::CUDAGuard guard(V.device());
     Tensor Wc = W.contiguous(), Vc = V.contiguous();
     Tensor out = at::empty({B, M, Dp}, Vc.options());
-    if (out.numel()) {
-        // the library allocates nothing: the scratch for the bit-transposed V comes from here
-        const int64_t ws_bytes = brute_b200_signed_bundle_workspace_bytes(B, N, D);
-        Tensor ws = at::empty({std::max<int64_t>(ws_bytes, 8) / 8}, Vc.options());
-        ok(brute_b200_signed_bundle_ws(ptr<const int8_t>(Wc), ptr<const uint64_t>(Vc), static_cast<uint64_t*>(out.data_ptr()),
-                                       B, M, N, Dp, D, ws.data_ptr(), ws_bytes, cur_stream(Vc)), "signed_bundle");
-    }
+    if (out.numel())      // one launch, no scratch: the tensor-core kernel transposes V's bit blocks itself
+        ok(brute_b200_signed_bundle(ptr<const int8_t>(Wc), ptr<const uint64_t>(Vc), static_cast<uint64_t*>(out.data_ptr()),
+                                    B, M, N, Dp, D, cur_stream(Vc)), "signed_bundle");
     return out;
 }
 

@@ -14,7 +14,7 @@ Ops beyond the reference's eleven carry new names and never change the eleven:
 ``binary_attention``, ``transpose_packed``, ``reduce_rows_packed``, ``flip_packed``,
 ``roll_packed``, ``gather_packed``, ``scatter_packed_``, ``narrow_i32_i16``,
 ``unstack_rank_blocks``. ``signed_bundle`` keeps the reference's schema and
-runs on the tensor cores; the scratch it needs is allocated here, never by the library.
+runs on the tensor cores in one launch.
 """
 from __future__ import annotations
 
@@ -290,13 +290,10 @@ def signed_bundle(W: torch.Tensor, V: torch.Tensor, D: int) -> torch.Tensor:
     out = torch.empty((B, M, Dp), dtype=torch.int64, device=V.device)
     if out.numel():
         with _device_guard(V.device):
-            # the library allocates nothing: the scratch for the bit-transposed V comes from here
-            ws_bytes = int(_lib.brute_b200_signed_bundle_workspace_bytes(B, N, int(D)))
-            ws = torch.empty(max(ws_bytes, 8) // 8, dtype=torch.int64, device=V.device)
-            L.check(_lib.brute_b200_signed_bundle_ws(Wc.data_ptr() if Wc.numel() else None,
-                                                     Vc.data_ptr() if Vc.numel() else None, out.data_ptr(),
-                                                     B, M, N, Dp, int(D), ws.data_ptr(), ws_bytes, _stream(V)),
-                    "signed_bundle")
+            # one launch, no scratch: the tensor-core kernel transposes V's bit blocks itself
+            L.check(_lib.brute_b200_signed_bundle(Wc.data_ptr() if Wc.numel() else None,
+                                                  Vc.data_ptr() if Vc.numel() else None, out.data_ptr(),
+                                                  B, M, N, Dp, int(D), _stream(V)), "signed_bundle")
     return out
 
 

@@ -262,8 +262,11 @@ int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B,
 int brute_b200_signed_bundle(const int8_t* W, const uint64_t* V, uint64_t* out,
                              int64_t B, int64_t M, int64_t N, int64_t Dp, int64_t D, void* stream);
 
-/* The same result on the tensor cores: V is bit-transposed into `workspace` and the vote becomes an
- * int8 GEMM that streams W once (HBM bound). `workspace` must hold
+/* brute_b200_signed_bundle runs on the tensor cores where the shape allows (W 16-byte aligned, N a
+ * multiple of 16 and >= 128, M >= 64, Dp == ceil(D/64)): the vote is an int8 GEMM that streams W once
+ * (HBM bound), and the bit transpose of V that it needs happens inside the kernel, block by block.
+ * The variant below does that transpose as a pass of its own into a caller-provided `workspace`
+ * (the earlier form of the tensor path, kept for callers that hold such a workspace): `workspace` must hold
  * brute_b200_signed_bundle_workspace_bytes(B, N, D) bytes of device memory, 8-byte aligned; the
  * library allocates nothing, so the caller provides it (BRUTE_ERR_WORKSPACE if it is missing or too
  * small). Shapes the tensor path does not take (W not 16-byte aligned, N not a multiple of 16, N < 128,
