@@ -60,5 +60,10 @@ def save_packed(obj: Any, f) -> None:
 
 
 def load_packed(f, device=None) -> Any:
-    """Load what ``save_packed`` wrote; bit1 tensors come back packed on ``device`` (default: CPU)."""
+    """Load what ``save_packed`` wrote; bit1 tensors come back packed-only on ``device``.
+
+    With the default (``device=None``) the packed words stay in host memory. The package has CUDA
+    kernels only, so such a tensor can be moved (``t.to("cuda")`` carries the packed words, an eighth
+    of the bool bytes, and leaves the bool view lazy) but not computed with or read as bool before it
+    has been moved: pass ``device="cuda"`` to load straight onto the GPU."""
     return _decode(torch.load(f, map_location="cpu", weights_only=True), device)

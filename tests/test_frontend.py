@@ -498,6 +498,23 @@ def test_large_lazy_result_allocates_no_bool_tensor(brute):
     assert bool(row.all()) and torch.cuda.memory_allocated() - before >= n
 
 
+def test_move_between_devices_carries_the_packed_words(brute, tmp_path):
+    """load_packed() leaves the words on the host; .to('cuda') must move THEM (no CPU kernel exists in
+    the product to unpack with) and keep the result packed-only."""
+    if DEV != "cuda":
+        pytest.skip("needs two device types")
+    x = rnd((5, 131), 61)
+    b = b1(brute, x) ^ brute.zeros((5, 131), dtype=brute.bit1, device="cuda")
+    path = tmp_path / "t.pt"
+    brute.save_packed({"w": b}, path)
+    host = brute.load_packed(path)["w"]
+    assert host._packed_buf.device.type == "cpu" and host.__dict__["_bool_dirty"] is True
+    back = host.to("cuda")
+    assert back.dtype == brute.bit1 and back.__dict__["_bool_dirty"] is True and back._packed_buf.is_cuda
+    assert same(as_bool(back), x) and int(back.popcount()) == int(x.sum())
+    assert same(as_bool(brute.load_packed(path, device="cuda")["w"]), x)
+
+
 def test_clone_then_write_plain_alias_leaves_the_source_alone(brute):
     # reference tests/unit/test_aliasing.py:65-72
     x = brute.zeros(16, dtype=brute.bit1, device=DEV)
