@@ -32,6 +32,18 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same test with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds
+// and is woken when the phase completes, instead of polling: waiting roles then leave the issue slots
+// to the roles that work (in a profile of an attention kernel with five waiting roles, the polling
+// loops were a third of all issued instructions).
+__device__ __forceinline__ bool mbar_try_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
@@ -46,14 +58,19 @@ template <bool kRelaxed>
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
                                                 uint64_t limit_ns) {
     if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = tc_globaltimer();
+    // Each further try may sleep in hardware (2 us; 8 us for the relaxed form). The clock is read only
+    // every 16 failed tries, the first of those readings being the start of the limit: a wait that
+    // ends within a few tries (the usual case on a pipeline's critical path) costs no read of the
+    // global timer at all.
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
-        if (kRelaxed) __nanosleep(128);
-        if (mbar_try(bar, parity)) return true;
-        if (((++spins) & (kRelaxed ? 0x3Fu : 0xFFu)) == 0) {
+        if (mbar_try_suspend(bar, parity, kRelaxed ? 8000u : 2000u)) return true;
+        if (((++spins) & 0xFu) == 0) {
             if (*abort_flag) return false;
-            if (tc_globaltimer() - t0 > limit_ns) {
+            const uint64_t now = tc_globaltimer();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(&g_tc_status, 0, code);
                 return false;
