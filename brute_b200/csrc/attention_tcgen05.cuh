@@ -71,7 +71,9 @@ __device__ __forceinline__ uint64_t ax_v_desc(uint32_t saddr) {
 }
 // 4 bits (j, 8+j, 16+j, 24+j of h) -> 4 int8: query side +1 / -1, key side -2 / +2
 __device__ __forceinline__ uint32_t ax_enc_q(uint32_t h, int j) { return 0xFFFFFFFFu ^ (((h >> j) & 0x01010101u) * 0xFEu); }
-__device__ __forceinline__ uint32_t ax_enc_k(uint32_t h, int j) { return 0x02020202u ^ (((h >> j) & 0x01010101u) * 0xFCu); }
+// key side as multiply-ADD (per byte 0x02 + {0, 0xFC}: no carry leaves a byte), one instruction less
+// than multiply, then XOR: the expander warps' instruction count is what their tile rate hangs on
+__device__ __forceinline__ uint32_t ax_enc_k(uint32_t h, int j) { return ((h >> j) & 0x01010101u) * 0xFCu + 0x02020202u; }
 
 // acc (two packed fp32) += {p0, p1}: one instruction on sm_100
 __device__ __forceinline__ void ax_add2(uint64_t& acc, float p0, float p1) {

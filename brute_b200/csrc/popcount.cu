@@ -1,6 +1,7 @@
 // popcount family: per-element, whole-buffer total, fused xor totals.
 // All are HBM-bound: 128-bit loads, grid sized in whole waves over the SMs,
 // one 64-bit atomic per block for the totals.
+#include <atomic>
 #include "common.cuh"
 #include <algorithm>
 
@@ -72,6 +73,34 @@ k_hamming_words(const uint64_t* __restrict__ a, const uint64_t* __restrict__ b,
 }
 
 // ---------------------------------------------------------------------------
+// A total in ONE launch, with no memset of the result before it: the blocks add their partial sums
+// into an accumulator that is zero at rest, take a ticket, and the block that draws the last ticket
+// moves the sum to the caller's word and leaves accumulator and ticket zero again. The accumulators
+// are static device memory (the library allocates nothing); the host hands the slots out round
+// robin, so two totals collide only if kTotalSlots launches separate them and the first is still
+// running (or if two captured graphs that hold the same slot are replayed at the same time).
+// ---------------------------------------------------------------------------
+constexpr int kTotalSlots = 256;
+struct TotalSlot { unsigned long long acc; unsigned int ticket; unsigned int pad; };
+__device__ TotalSlot g_total_slots[kTotalSlots];
+
+__device__ __forceinline__ void total_finish(uint64_t block_sum, int slot, unsigned long long* out) {
+    TotalSlot* s = &g_total_slots[slot];
+    if (block_sum) atomicAdd(&s->acc, (unsigned long long)block_sum);
+    __threadfence();
+    if (atomicAdd(&s->ticket, 1u) == gridDim.x - 1) {      // every other block's sum is in
+        __threadfence();
+        *out = atomicExch(&s->acc, 0ull);
+        s->ticket = 0;
+    }
+}
+
+static inline int next_total_slot() {
+    static std::atomic<unsigned> seq{0};
+    return (int)(seq.fetch_add(1, std::memory_order_relaxed) % kTotalSlots);
+}
+
+// ---------------------------------------------------------------------------
 // totals. TWO = false: sum popcount(a); TWO = true: sum popcount(a ^ b).
 // `a` (and `b`) point at the first 16-byte aligned vector; head and tail bytes
 // outside the vector range are added by thread 0 of block 0.
@@ -79,7 +108,7 @@ k_hamming_words(const uint64_t* __restrict__ a, const uint64_t* __restrict__ b,
 template <bool TWO>
 __global__ void __launch_bounds__(256)
 k_popcount_total(const uint8_t* __restrict__ a, const uint8_t* __restrict__ b,
-                 int64_t head, int64_t nvec, int64_t tail, unsigned long long* __restrict__ out) {
+                 int64_t head, int64_t nvec, int64_t tail, unsigned long long* __restrict__ out, int slot) {
     __shared__ uint64_t red[32];
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const uint8_t* av = a + head;
@@ -117,20 +146,20 @@ k_popcount_total(const uint8_t* __restrict__ a, const uint8_t* __restrict__ b,
         for (int64_t k = 0; k < tail; ++k) acc += __popc((uint32_t)(a[t0 + k] ^ (TWO ? b[t0 + k] : (uint8_t)0)));
     }
     acc = block_sum_u64(acc, red);
-    if (threadIdx.x == 0 && acc) atomicAdd(out, (unsigned long long)acc);
+    if (threadIdx.x == 0) total_finish(acc, slot, out);
 }
 
 // a and b are misaligned differently: byte-granular scalar path (rare)
 __global__ void __launch_bounds__(512)
 k_hamming_total_bytes(const uint8_t* __restrict__ a, const uint8_t* __restrict__ b, int64_t n,
-                      unsigned long long* __restrict__ out) {
+                      unsigned long long* __restrict__ out, int slot) {
     __shared__ uint64_t red[32];
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     uint64_t acc = 0;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         acc += __popc((uint32_t)(a[i] ^ b[i]));
     acc = block_sum_u64(acc, red);
-    if (threadIdx.x == 0 && acc) atomicAdd(out, (unsigned long long)acc);
+    if (threadIdx.x == 0) total_finish(acc, slot, out);
 }
 
 static inline void split_aligned(const void* p, int64_t n_bytes, int64_t& head, int64_t& nvec, int64_t& tail) {
@@ -196,15 +225,14 @@ extern "C" int brute_b200_popcount_total(const void* in, int64_t n_bytes, uint64
     BB_REQUIRE(n_bytes >= 0 && out != nullptr, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(aligned8(out), BRUTE_ERR_MISALIGNED);
     cudaStream_t st = as_stream(stream);
-    if (cudaMemsetAsync(out, 0, sizeof(uint64_t), st) != cudaSuccess) return BRUTE_ERR_LAUNCH;
-    if (n_bytes == 0) return BRUTE_OK;
+    if (n_bytes == 0) return cudaMemsetAsync(out, 0, sizeof(uint64_t), st) == cudaSuccess ? BRUTE_OK : BRUTE_ERR_LAUNCH;
     BB_REQUIRE(in != nullptr, BRUTE_ERR_INVALID_ARG);
     int64_t head, nvec, tail;
     split_aligned(in, n_bytes, head, nvec, tail);
     static const int per_launch = resident_grid(k_popcount_total<false>, 256, 1 << 30);
     const int grid = (int)std::min<int64_t>(per_launch, std::max<int64_t>(1, (nvec + 256 * 4 - 1) / (256 * 4)));
     k_popcount_total<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(in), nullptr, head, nvec, tail,
-                                                  reinterpret_cast<unsigned long long*>(out));
+                                                  reinterpret_cast<unsigned long long*>(out), next_total_slot());
     return launch_status();
 }
 
@@ -213,13 +241,12 @@ extern "C" int brute_b200_hamming_total(const void* a, const void* b, int64_t n_
     BB_REQUIRE(n_bytes >= 0 && out != nullptr, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(aligned8(out), BRUTE_ERR_MISALIGNED);
     cudaStream_t st = as_stream(stream);
-    if (cudaMemsetAsync(out, 0, sizeof(uint64_t), st) != cudaSuccess) return BRUTE_ERR_LAUNCH;
-    if (n_bytes == 0) return BRUTE_OK;
+    if (n_bytes == 0) return cudaMemsetAsync(out, 0, sizeof(uint64_t), st) == cudaSuccess ? BRUTE_OK : BRUTE_ERR_LAUNCH;
     BB_REQUIRE(a != nullptr && b != nullptr, BRUTE_ERR_INVALID_ARG);
     auto* o = reinterpret_cast<unsigned long long*>(out);
     if ((reinterpret_cast<uintptr_t>(a) & 15u) != (reinterpret_cast<uintptr_t>(b) & 15u)) {
         k_hamming_total_bytes<<<stream_grid(n_bytes, 512 * 16, 4), 512, 0, st>>>(
-            static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), n_bytes, o);
+            static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), n_bytes, o, next_total_slot());
         return launch_status();
     }
     int64_t head, nvec, tail;
@@ -227,6 +254,6 @@ extern "C" int brute_b200_hamming_total(const void* a, const void* b, int64_t n_
     static const int per_launch = resident_grid(k_popcount_total<true>, 256, 1 << 30);
     const int grid = (int)std::min<int64_t>(per_launch, std::max<int64_t>(1, (nvec + 256 * 4 - 1) / (256 * 4)));
     k_popcount_total<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b),
-                                                 head, nvec, tail, o);
+                                                 head, nvec, tail, o, next_total_slot());
     return launch_status();
 }

@@ -314,7 +314,7 @@ def popcount(x: torch.Tensor) -> torch.Tensor:
 
 def packed_popcount(x: torch.Tensor) -> torch.Tensor:
     p = x.contiguous()
-    out = torch.empty((), dtype=torch.int64, device=p.device)      # zeroed by the call itself
+    out = torch.empty((), dtype=torch.int64, device=p.device)      # overwritten by the call itself
     with _device_guard(p.device):
         L.check(_lib.brute_b200_popcount_total(p.data_ptr() if p.numel() else None,
                                                p.numel() * p.element_size(), out.data_ptr(), _stream(p)),

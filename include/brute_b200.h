@@ -120,13 +120,18 @@ int brute_b200_unpack_pm1_f32(const uint64_t* in, float* out,
 int brute_b200_popcount_elems(const void* in, int32_t* out,
                               int64_t n, int elem_bytes, void* stream);
 
-/* total popcount of n_bytes bytes -> *out (uint64, zeroed by the call itself).
+/* total popcount of n_bytes bytes -> *out (uint64; the call overwrites it, it need not be zero).
+ * One launch: the blocks sum into one of 256 accumulators in static device memory (zero at
+ * rest, handed out round robin) and the last block to finish moves the sum to *out. Two
+ * totals may therefore not be in flight 256 launches apart on one device, and two captured
+ * graphs that contain the same accumulator slot should not be replayed concurrently.
  * Replaces cbrute::cuda::packed_popcount, cbrute/cuda/ops_cuda.cu:283-304 and
  * k_packed_popcount_total/k_popcount_tail_byte, cbrute/cuda/kernels/popcount.cuh:75-98,129-136. */
 int brute_b200_popcount_total(const void* in, int64_t n_bytes,
                               uint64_t* out, void* stream);
 
-/* total popcount(a ^ b) over n_bytes bytes -> *out, no XOR temporary.
+/* total popcount(a ^ b) over n_bytes bytes -> *out, no XOR temporary; one launch, same
+ * accumulator scheme as brute_b200_popcount_total.
  * Replaces cbrute::cuda::bit1_hamming_total, cbrute/cuda/ops_cuda.cu:312-338 and
  * k_hamming_total/k_hamming_tail_byte, cbrute/cuda/kernels/popcount.cuh:101-124,138-149. */
 int brute_b200_hamming_total(const void* a, const void* b, int64_t n_bytes,

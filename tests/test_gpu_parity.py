@@ -184,6 +184,31 @@ def test_popcount_elems_dtypes(ops, co, dtype, n):
         ops.popcount(torch.zeros(4, device=DEV))
 
 
+def test_totals_many_launches_in_flight_on_two_streams(ops, co):
+    """The totals run as one launch each: blocks add into an accumulator in static device memory that the
+    last block hands over and leaves zero. 700 launches queued without a sync, on two streams, walk the
+    ring of accumulators almost three times; every result must still be its own input's count."""
+    sizes = [1, 77, 4096, 100003, 1 << 18]
+    hosts = [torch.randint(-2 ** 63, 2 ** 63 - 1, (n,), generator=gen(900 + i), dtype=torch.int64) for i, n in enumerate(sizes)]
+    devs = [h.to(DEV) for h in hosts]
+    want_pop = [co.popcount_total(h.numpy()) for h in hosts]
+    want_ham = [co.hamming_total(hosts[i].numpy(), hosts[i].flip(0).contiguous().numpy()) for i in range(len(hosts))]
+    flipped = [d.flip(0).contiguous() for d in devs]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    got = []
+    for k in range(700):
+        i = k % len(sizes)
+        with torch.cuda.stream(streams[k & 1]):
+            if k % 3 == 0:
+                got.append((ops.bit1_hamming_total(devs[i], flipped[i]), want_ham[i]))
+            else:
+                got.append((ops.packed_popcount(devs[i]), want_pop[i]))
+    torch.cuda.synchronize()
+    bad = [(k, int(t), w) for k, (t, w) in enumerate(got) if int(t) != w]
+    assert not bad, bad[:5]
+
+
 @pytest.mark.parametrize("n_words", [0, 1, 2, 3, 255, 256, 257, 100003, 1 << 20])
 def test_totals(ops, co, n_words):
     a = torch.randint(-2 ** 63, 2 ** 63 - 1, (n_words,), generator=gen(n_words), dtype=torch.int64)
