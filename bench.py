@@ -491,6 +491,19 @@ def secondary_workloads(dev, peaks, flush, sync):
         gbs = alg_bytes / (ms * 1e-3) / 1e9
         out[name] = {"ms": ms, "GB/s": gbs, "frac_of_hbm": gbs / hbm, "algorithmic_bytes": alg_bytes}
 
+    def rotating(name, fns, alg_bytes, steps=10):
+        """A 30 us op bracketed by two events carries about 5 us of event and launch-gap time (ncu sees the
+        same kernel at 25 us). Second figure for such ops: len(fns) launches on DISTINCT inputs, together
+        several times the L2, inside one event pair with no flush in between (every input was evicted by the
+        others before its turn comes again); per-op time = span / len(fns)."""
+        for _ in range(2):
+            for f in fns:
+                f()
+        ts = time_steps(lambda: [f() for f in fns], steps, 2, flush, sync)
+        ms = statistics.median(ts) / len(fns)
+        out[name]["rotating_inputs"] = {"launches_per_span": len(fns), "ms_per_op": ms,
+                                        "frac_of_hbm": alg_bytes / (ms * 1e-3) / 1e9 / hbm}
+
     side = torch.cuda.Stream(dev)
 
     def graph_us(fn):
@@ -544,6 +557,8 @@ def secondary_workloads(dev, peaks, flush, sync):
     del xb
     bw("unpack_pm1_f32_2^30", lambda: ops.unpack_bits(p, [n]), n // 8 + 4 * n, steps=5)
     bw("popcount_total_2^30", lambda: ops.packed_popcount(p), n // 8)
+    rot = [p, q] + [torch.randint(-2 ** 63, 2 ** 63 - 1, (n // 64,), generator=g, dtype=torch.int64, device=dev) for _ in range(2)]
+    rotating("popcount_total_2^30", [(lambda t=t: ops.packed_popcount(t)) for t in rot], n // 8)
     bw("hamming_total_2^30", lambda: ops.bit1_hamming_total(p, q), 2 * n // 8)
     bw("word_popcount_2^30", lambda: ops.popcount(p), n // 8 + n // 16)
     bw("xor_2^30", lambda: ops.bitwise_packed(p, q, 2, n), 3 * n // 8)
@@ -551,6 +566,8 @@ def secondary_workloads(dev, peaks, flush, sync):
     p2 = p.view(32768, 512)
     bw("transpose_bits_32768x32768", lambda: ops.transpose_packed(p2, 32768, 32768), 2 * n // 8)
     bw("any_dim0_4096x2^18", lambda: ops.reduce_rows_packed(p.view(4096, 4096), 0, True), n // 8 + (1 << 18) // 8)
+    rotating("any_dim0_4096x2^18", [(lambda t=t: ops.reduce_rows_packed(t.view(4096, 4096), 0, True)) for t in rot], n // 8 + (1 << 18) // 8)
+    del rot
     p3 = p.view(1024, -1)                  # 1024 rows of 2^20 bits; the -5 makes every row ragged
     nrow = (1 << 20) - 5
     bw("flip_last_axis_1024x(2^20-5)", lambda: ops.flip_packed(p3, nrow), 2 * n // 8)
