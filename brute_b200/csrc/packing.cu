@@ -141,6 +141,48 @@ k_pack_bool(const uint8_t* __restrict__ in, uint64_t* __restrict__ out,
     }
 }
 
+// Ragged rows whose start is not 16-byte aligned (e.g. 4097 bools per row): one OUTPUT WORD per lane.
+// The word's 64 bools start at an arbitrary byte; the lane loads the up to five aligned 16-byte
+// vectors that cover them (default caching: its neighbours' vectors share sectors with it), turns
+// each into 16 bits and shifts the 80-bit window down by the misalignment. No bits move between
+// lanes, there is no per-row task grid (a row of 4097 bools is 65 words, not 9 warp tasks of which
+// the last holds one byte), and a lane amortises its index arithmetic over 64 bytes instead of 16:
+// a third of the instructions of the warp-task form on bool [4096, 4097].
+template <typename IDX>
+__global__ void __launch_bounds__(256, 4)
+k_pack_bool_words(const uint8_t* __restrict__ in, uint64_t* __restrict__ out,
+                  int64_t rows, IDX ld, IDX wpr, int64_t nwords) {
+    const uintptr_t buf_lo = reinterpret_cast<uintptr_t>(in);
+    const uintptr_t buf_hi = buf_lo + (uintptr_t)rows * (uintptr_t)ld;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < nwords; t += stride) {
+        const IDX r = (IDX)t / wpr, w = (IDX)t - r * wpr;
+        const uint64_t col0 = (uint64_t)w * 64u;
+        const uintptr_t src = buf_lo + (uintptr_t)r * (uintptr_t)ld + (uintptr_t)col0;
+        const uint32_t m = (uint32_t)(src & 15u);
+        const uintptr_t base = src - m;
+        uint64_t valid = (uint64_t)ld - col0;
+        if (valid > 64u) valid = 64u;
+        const uint32_t nv = (m + (uint32_t)valid + 15u) >> 4;      // 1..5 vectors hold the word's bools
+        uint4 v[5];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+            v[k] = make_uint4(0u, 0u, 0u, 0u);
+            if ((uint32_t)k < nv) {
+                const uintptr_t a = base + 16u * k;
+                if (a >= buf_lo && a + 16 <= buf_hi) v[k] = __ldg(reinterpret_cast<const uint4*>(a));
+                else v[k] = load16_guarded(a, buf_lo, buf_hi);
+            }
+        }
+        const uint64_t lo = (uint64_t)bools16_to_bits(v[0]) | ((uint64_t)bools16_to_bits(v[1]) << 16) |
+                            ((uint64_t)bools16_to_bits(v[2]) << 32) | ((uint64_t)bools16_to_bits(v[3]) << 48);
+        uint64_t word = lo;
+        if (m) word = (lo >> m) | ((uint64_t)bools16_to_bits(v[4]) << (64u - m));
+        if (valid < 64u) word &= (1ull << valid) - 1ull;
+        out[t] = word;
+    }
+}
+
 // ===========================================================================
 // pack_sign: float / bf16 / f16 -> bits in one pass
 // ===========================================================================
@@ -339,6 +381,57 @@ k_unpack_flat256(const uint32_t* __restrict__ in32, uint8_t* __restrict__ out, i
     }
 }
 
+// Ragged rows (ll not a multiple of 64) with 256-bit stores: the OUTPUT is one dense byte stream
+// (row r starts at element r * ll), so a lane owns a 32-byte aligned group of it wherever that falls.
+// A group lies in one row, or - once per row - straddles the end of row r and the start of row
+// r + 1; both cases take the same path: up to NB = 32 / ELEM bits from row r, and the remainder from
+// the first word of row r + 1. No per-row task quantisation (4097-byte rows cost 8.002 warp stores
+// instead of 9) and half the store instructions of the 16-byte form. Needs ll >= NB (at most two
+// rows per group) and a 32-byte aligned output; the last, partial group is written element by element.
+template <int NB>
+__device__ __forceinline__ uint32_t row_bits_n(const uint64_t* __restrict__ rowp, uint32_t col, int64_t wpr) {
+    const uint32_t w = col >> 6, sh = col & 63u;
+    uint64_t x = __ldg(rowp + w) >> sh;
+    if (sh + NB > 64u && (int64_t)w + 1 < wpr) x |= __ldg(rowp + w + 1) << (64u - sh);
+    return NB == 32 ? (uint32_t)x : ((uint32_t)x & ((1u << NB) - 1u));
+}
+
+template <int ELEM, typename IDX>
+__global__ void __launch_bounds__(256, 8)
+k_unpack_ragged256(const uint64_t* __restrict__ in, uint8_t* __restrict__ out,
+                   int64_t rows, IDX ll, int64_t wpr, int64_t total /* rows * ll elements */, int64_t n32) {
+    constexpr int NB = 32 / ELEM;                  // elements (= bits) per 32-byte group
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < n32; g += stride) {
+        const IDX e0 = (IDX)(g * NB);              // first element of the group
+        const IDX r = e0 / ll;
+        const uint32_t col0 = (uint32_t)(e0 - r * ll);      // ll < 2^32 on this path
+        const uint64_t* rowp = in + (int64_t)r * wpr;
+        uint32_t bits = row_bits_n<NB>(rowp, col0, wpr);
+        const uint64_t n1 = (uint64_t)ll - col0;           // elements left in row r
+        if (n1 < (uint64_t)NB) {                           // the group runs on into row r + 1
+            bits &= (1u << (uint32_t)n1) - 1u;
+            if ((int64_t)r + 1 < rows) bits |= (uint32_t)__ldg(rowp + wpr) << (uint32_t)n1;
+        }
+        uint32_t v[8];
+        if (ELEM == 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = bits4_to_bytes01(bits >> (4 * i));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0xBF800000u ^ (((bits >> i) & 1u) << 31);
+        }
+        if ((int64_t)e0 + NB <= total) {
+            stg_stream_256(out + g * 32, v);
+        } else {                                           // the stream's last, partial group
+            for (int i = 0; (int64_t)e0 + i < total; ++i) {
+                if (ELEM == 1) out[g * 32 + i] = (uint8_t)((bits >> i) & 1u);
+                else reinterpret_cast<float*>(out)[g * 8 + i] = ((bits >> i) & 1u) ? 1.0f : -1.0f;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 static inline void flatten_rows(int64_t& rows, int64_t& len) {
     // rows of a multiple of 64 bits pack back to back: treat as one long row
@@ -375,7 +468,14 @@ extern "C" int brute_b200_pack_bool(const uint8_t* in, uint64_t* out,
     if (flat && aligned)  k_pack_bool<true, true><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
     else if (flat)        k_pack_bool<true, false><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
     else if (aligned)     k_pack_bool<false, true><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
-    else                  k_pack_bool<false, false><<<grid, 256, 0, st>>>(in, out, rows, ld, wpr, tm, tasks);
+    else {
+        const int64_t nwords = rows * wpr;
+        const int wgrid = stream_grid(nwords, 256, 4);
+        if (nwords < (1ll << 32) && ld < (1ll << 32))
+            k_pack_bool_words<uint32_t><<<wgrid, 256, 0, st>>>(in, out, rows, (uint32_t)ld, (uint32_t)wpr, nwords);
+        else
+            k_pack_bool_words<uint64_t><<<wgrid, 256, 0, st>>>(in, out, rows, (uint64_t)ld, (uint64_t)wpr, nwords);
+    }
     return launch_status();
 }
 
@@ -440,6 +540,15 @@ static int launch_unpack(const uint64_t* in, void* out, int64_t rows, int64_t ll
         const int64_t n32 = fll * ELEM / 32;
         k_unpack_flat256<ELEM><<<stream_grid(n32, 256, 8), 256, 0, st>>>(reinterpret_cast<const uint32_t*>(in),
                                                                       static_cast<uint8_t*>(out), n32);
+        return launch_status();
+    }
+    if (frows > 1 && fll >= 32 / ELEM && fll < (1ll << 32) && (reinterpret_cast<uintptr_t>(out) & 31u) == 0) {
+        const int64_t total = frows * fll, n32 = (total * ELEM + 31) / 32;
+        const int grid = stream_grid(n32, 256, 8);
+        if (total < (1ll << 32))
+            k_unpack_ragged256<ELEM, uint32_t><<<grid, 256, 0, st>>>(in, static_cast<uint8_t*>(out), frows, (uint32_t)fll, fwpr, total, n32);
+        else
+            k_unpack_ragged256<ELEM, uint64_t><<<grid, 256, 0, st>>>(in, static_cast<uint8_t*>(out), frows, (uint64_t)fll, fwpr, total, n32);
         return launch_status();
     }
     constexpr int EPG = 16 / ELEM;

@@ -36,7 +36,8 @@ def gen(seed):
 # ---------------------------------------------------------------------------
 TAIL_SHAPES = [(n,) for n in list(range(1, 131)) + [191, 192, 193, 255, 256, 257, 1003, 4096, 4097]]
 ND_SHAPES = [(3, 13), (13,), (4, 64), (7, 130), (2, 3, 65), (33, 1003), (5, 4097), (256, 4097),
-             (1, 1), (1, 65536), (65537,), (17, 16), (1000, 7), (9, 48), (6, 80)]
+             (1, 1), (1, 65536), (65537,), (17, 16), (1000, 7), (9, 48), (6, 80),
+             (3, 32), (5, 33), (4, 8), (11, 9), (2, 31), (129, 95), (64, 63), (2, 4099)]
 
 
 @pytest.mark.parametrize("shape", TAIL_SHAPES[::3] + ND_SHAPES)
