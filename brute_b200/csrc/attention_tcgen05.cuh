@@ -94,10 +94,13 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
                                int64_t S, int causal, float neg2c_log2 /* -2*scale*log2(e) */, float bias_log2,
                                int64_t q_tiles, int qt_major_flag) {
     extern __shared__ uint8_t ax_smem_raw[];
+    // A CTA lives for 2 to 64 key tiles (a few microseconds), so its set-up is a real share of it: every
+    // global load whose latency would head a role - the status word, the first K words, the Q rows, the
+    // tensor map - is issued HERE, before the barrier set-up and the allocation of tensor memory, and
+    // consumed after the one __syncthreads that the set-up needs anyway.
     __shared__ int s_skip;
-    if (threadIdx.x == 0) s_skip = *(volatile int*)&g_tc_status;
-    __syncthreads();
-    if (s_skip != 0) return;                            // an earlier CTA gave up: do not queue behind it
+    int skip_reg = 0;
+    if (threadIdx.x == 0) skip_reg = *(volatile int*)&g_tc_status;      // an earlier CTA gave up: do not queue behind it
 
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(ax_smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -135,6 +138,36 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     const int64_t kend = causal ? (q0 + AX_BM < S ? q0 + AX_BM : S) : S;
     const int32_t ntiles = (int32_t)((kend + AX_BN - 1) / AX_BN);  // >= 1 because q0 < S
 
+    // ---- early loads (see above) ----
+    constexpr int WPK = AX_D / 32;                        // 32-bit words per key: 4 or 2
+    constexpr int AX_KPF = 4;                             // K words are fetched this many tiles ahead (a ring of registers)
+    constexpr int QW = AX_D / 64;                         // 32-bit words of a Q row per softmax thread
+    const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Kp + bh * S * (AX_D / 64));
+    const int khalf = warp - 2;                           // K expanders: keys [32 khalf, 32 khalf + 32) of the tile
+    uint32_t kring[AX_KPF][WPK];
+    // lane -> (key, word): 32 * WPK words per half tile, WPK per lane, coalesced
+    auto load_tile = [&](int32_t j, uint32_t (&w)[WPK]) {
+#pragma unroll
+        for (int i = 0; i < WPK; ++i) {
+            const int idx = lane + 32 * i;                // 0 .. 32 * WPK - 1
+            const int64_t key = (int64_t)j * AX_BN + 32 * khalf + idx / WPK;
+            w[i] = (j < ntiles && key < S) ? __ldg(Kw + key * WPK + idx % WPK) : 0u;
+        }
+    };
+    uint32_t qh[QW];
+    if (warp == 0) {
+        if (lane == 0) asm volatile("prefetch.tensormap [%0];" :: "l"(&tmV) : "memory");
+    } else if (warp == 2 || warp == 3) {
+#pragma unroll
+        for (int u = 0; u < AX_KPF - 1; ++u) load_tile(u, kring[u]);
+    } else if (warp >= 4) {
+        const int grp = (warp - 4) >> 2;
+        const int64_t row = q0 + (warp & 3) * 32 + lane;
+        const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * (AX_D / 64));
+#pragma unroll
+        for (int w = 0; w < QW; ++w) qh[w] = row < S ? __ldg(Qw + row * (2 * QW) + QW * grp + w) : 0u;
+    }
+
     // weights are bf16-exact, so the fp32 row sum adds exactly what the P.V MMA multiplies
     if (tid <= AX_D) T[tid] = __bfloat162float(__float2bfloat16_rn(exp2f(neg2c_log2 * (float)tid - bias_log2)));
     if (tid == 0) {
@@ -143,6 +176,7 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         for (int b = 0; b < 2; ++b) { mbar_init(s_full(b), 1); mbar_init(p_full(b), AX_SOFTMAX_WARPS); }
         mbar_init(q_full, AX_SOFTMAX_WARPS); mbar_init(o_full, 1); mbar_init(drain_bar, 1);
         *abort_flag = 0;
+        s_skip = skip_reg;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async_smem();
     }
@@ -156,7 +190,9 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
+    if (s_skip != 0) {
+        // an earlier CTA of this launch gave up: only hand the tensor memory back
+    } else if (warp == 0) {
         // ================= TMA producer: V tiles =================
         if (lane == 0) {
             bool ok = true;
@@ -245,24 +281,11 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         __syncwarp();
     } else if (warp < 4) {
         // ================= K expanders: packed bits -> int8 tile, K-major SWIZZLE_128B =================
-        constexpr int WPK = AX_D / 32;                    // 32-bit words per key: 4 or 2
-        const uint32_t* Kw = reinterpret_cast<const uint32_t*>(Kp + bh * S * (AX_D / 64));
-        const int half = warp - 2;                        // keys [32 half, 32 half + 32) of the tile
-        // lane -> (key, word): 32 * WPK words per half tile, WPK per lane, coalesced
-        // The packed words are fetched AX_KPF tiles ahead into a ring of registers: one tile ahead left
-        // the load latency (L2, under load) on the path and made this role the slowest of the CTA.
-        constexpr int AX_KPF = 4;
-        uint32_t ring[AX_KPF][WPK];
-        auto load_tile = [&](int32_t j, uint32_t (&w)[WPK]) {
-#pragma unroll
-            for (int i = 0; i < WPK; ++i) {
-                const int idx = lane + 32 * i;            // 0 .. 32 * WPK - 1
-                const int64_t key = (int64_t)j * AX_BN + 32 * half + idx / WPK;
-                w[i] = (j < ntiles && key < S) ? __ldg(Kw + key * WPK + idx % WPK) : 0u;
-            }
-        };
-#pragma unroll
-        for (int u = 0; u < AX_KPF - 1; ++u) load_tile(u, ring[u]);
+        // The packed words are fetched AX_KPF tiles ahead into a ring of registers (the first three tiles'
+        // before the CTA's set-up): one tile ahead left the load latency (L2, under load) on the path
+        // and made this role the slowest of the CTA.
+        const int half = khalf;
+        auto& ring = kring;
         bool ok = true;
         int kb = 0;                                       // K buffer of tile j, j % AX_NK, and its phase
         uint32_t kbp = 0;
@@ -303,12 +326,10 @@ k_binary_attention_fwd_tcgen05(const __grid_constant__ CUtensorMap tmV,
         {
             // Q row: this thread's half of the bits -> int8 chunks of the 128-byte operand row
             // (D = 128: 64 bits -> chunks 4 grp .. 4 grp + 3; D = 64: 32 bits -> chunks 2 grp, 2 grp + 1)
-            constexpr int QW = AX_D / 64;                 // 32-bit words per thread
-            const uint32_t* Qw = reinterpret_cast<const uint32_t*>(Qp + bh * S * (AX_D / 64));
             uint8_t* qrow = gq + r * 128;
 #pragma unroll
             for (int w = 0; w < QW; ++w) {
-                const uint32_t h = row < S ? __ldg(Qw + row * (2 * QW) + QW * grp + w) : 0u;
+                const uint32_t h = qh[w];                 // loaded before the CTA's set-up
                 const int ch = 2 * QW * grp + 2 * w;
                 *reinterpret_cast<uint4*>(qrow + ((ch ^ (r & 7)) << 4)) =
                     make_uint4(ax_enc_q(h, 0), ax_enc_q(h, 1), ax_enc_q(h, 2), ax_enc_q(h, 3));
