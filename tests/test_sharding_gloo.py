@@ -93,6 +93,16 @@ def test_two_rank_sharded_gemm(tmp_path, lib_built, n_rows):
     assert spans[0][0] == 0 and spans[0][1] == spans[1][0] and spans[1][1] == n_rows
 
 
+def test_four_rank_sharded_gemm(tmp_path, lib_built):
+    """The same checks with four ranks: the replicated result is assembled from four rank blocks
+    (int16 transport, row blocks) and must equal the local GEMM on every rank."""
+    port = 29500 + (os.getpid() % 1000) + 77
+    mp.spawn(_worker, args=(4, port, 16, str(tmp_path)), nprocs=4, join=True)
+    spans = [np.load(tmp_path / f"ok{r}.npy") for r in range(4)]
+    assert spans[0][0] == 0 and spans[-1][1] == 16
+    assert all(spans[i][1] == spans[i + 1][0] for i in range(3))
+
+
 def test_shard_bounds_cover_everything():
     from brute_b200.kernels import shard_bounds
     for n in (0, 1, 7, 16, 16384):
