@@ -20,8 +20,11 @@
 // (two per SM) walk over the items:
 //   warp 0      TMA producer for W tiles (4-deep ring of 16 KB)
 //   warp 1      MMA issuer, TMEM owner (256 columns = TWO accumulators; two CTAs per SM)
-//   warps 2-5   expand Vt bits into the B tile (2-deep ring of 128 x 128 bytes), item after item
-//   warps 6-9   epilogue: one thread per row reads its TMEM lane and packs the sign bits, while the
+//   warps 2-9   expand Vt bits into the B tile (2-deep ring of 128 x 128 bytes), item after item: two
+//               groups of four warps, one per ring stage, take the k-blocks alternately (measured with
+//               one group: the MMA warp spent two thirds of every k-block waiting for the expanded
+//               tile, the expanders a tenth of theirs waiting for a free stage)
+//   warps 10-13 epilogue: one thread per row reads its TMEM lane and packs the sign bits, while the
 //               other accumulator already takes the next item's MMAs (an item is only 8 k-blocks
 //               at N = 1024: with one accumulator and the expanders doing the epilogue, every
 //               item drained the W ring).
@@ -38,7 +41,8 @@ constexpr int ST_KB = 128;                   // bytes (= n) per k-block
 constexpr int ST_ASTAGES = 4, ST_BSTAGES = 2;
 constexpr int ST_A_TILE = ST_BM * ST_KB;     // 16 KB
 constexpr int ST_B_TILE = ST_NMMA * ST_KB;   // 16 KB
-constexpr int ST_THREADS = 320;
+constexpr int ST_THREADS = 448;
+constexpr int ST_FIRST_EPI_WARP = 10;      // warps 2-5 and 6-9: two expander groups; 10-13: epilogue
 constexpr int ST_TMEM_COLS = 256;
 constexpr int ST_OFF_B = ST_ASTAGES * ST_A_TILE;
 constexpr int ST_OFF_BARS = ST_OFF_B + ST_BSTAGES * ST_B_TILE;
@@ -183,16 +187,17 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
             while (!mbar_try(drain_bar, 0) && tc_globaltimer() - t0 < TC_WAIT_NS) {}
         }
         __syncwarp();
-    } else if (warp < 6) {
+    } else if (warp < ST_FIRST_EPI_WARP) {
         // ================= B expanders, item after item =================
         // The CTA's k-blocks form one stream over all of its items; the packed words are fetched
         // ST_VPF - 1 k-blocks ahead of the expansion ACROSS item boundaries (a ring of registers), so
         // that no item starts with a global-load latency on its path.
-        const int t = tid - 64;                              // 0..127: non-fused, the thread's d row
+        const int t = (tid - 64) & 127;                      // 0..127: non-fused, the thread's d row
+        const int grp = (warp - 2) >> 2;                     // this group takes the k-blocks g with g % 2 == grp, into stage grp
         // FUSED: warp (rb, cb) owns the 64 (n) x 64 (d) bit block rb, cb of the k-block's 128 x 128:
         // lane L loads word cb of rows n0 + 64 rb + L and + 32, the butterfly turns them into the
         // 64 n-bits of d rows 64 cb + L and + 32, and the lane writes those two half rows.
-        const int wq = warp - 2, rb = wq >> 1, cb = wq & 1;
+        const int wq = (warp - 2) & 3, rb = wq >> 1, cb = wq & 1;
         const int64_t my_items = blockIdx.x < items ? (items - 1 - blockIdx.x) / gridDim.x + 1 : 0;
         const int64_t total = my_items * nkb;                // k-blocks of this CTA
         // the fetch cursor: item, k-block, and what depends on the item only
@@ -215,6 +220,10 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
                 pvrow = Vt + (b * D + (plive ? d : 0)) * wpn;
             }
         };
+        auto advance = [&]() {
+            if (pit >= items) return;
+            if (++pkb == nkb) { pkb = 0; pit += gridDim.x; fetch_item(); }
+        };
         auto fetch = [&](uint64_t (&w)[2]) {
             w[0] = w[1] = 0ull;
             if (pit >= items) return;
@@ -227,21 +236,24 @@ k_signed_bundle_tcgen05(const __grid_constant__ CUtensorMap tmW,
                 if (plive && w0 < wpn) w[0] = __ldg(pvrow + w0);
                 if (plive && w0 + 1 < wpn) w[1] = __ldg(pvrow + w0 + 1);
             }
-            if (++pkb == nkb) { pkb = 0; pit += gridDim.x; fetch_item(); }
+            advance();
+            advance();                                       // the other group takes the k-block in between
         };
         fetch_item();
+        if (grp == 1) advance();
         constexpr int ST_VPF = 4;
         uint64_t ring[ST_VPF][2];
 #pragma unroll
         for (int u = 0; u < ST_VPF - 1; ++u) fetch(ring[u]);
         bool ok = true;
-        for (int64_t g0 = 0; g0 < total && ok; g0 += ST_VPF) {
+        static_assert(ST_BSTAGES == 2, "one expander group per stage");
+        for (int64_t g0 = grp; g0 < total && ok; g0 += 2 * ST_VPF) {
 #pragma unroll
             for (int u = 0; u < ST_VPF; ++u) {                // ring slots are static register names
-                const int64_t g = g0 + u;
+                const int64_t g = g0 + 2 * u;
                 if (g >= total || !ok) break;
                 fetch(ring[(u + ST_VPF - 1) % ST_VPF]);
-                const int sb = (int)(g % ST_BSTAGES);
+                const int sb = grp;
                 ok = __all_sync(0xffffffffu, mbar_wait(b_empty(sb), ((uint32_t)(g / ST_BSTAGES) & 1u) ^ 1u, abort_flag, 24));
                 if (!ok) break;
                 // rows d >= D expand whatever their (zero) words say: those output bits are masked in the epilogue
