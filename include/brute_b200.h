@@ -198,7 +198,9 @@ int brute_b200_transpose_bits(const uint64_t* in, uint64_t* out,
 
 /* OR (BRUTE_OP_OR) or AND (BRUTE_OP_AND) over the middle axis of in [outer, R, inner]
  * words -> out [outer, inner] words: any()/all() over a non-packed dimension in one pass.
- * R == 0 gives the identity (0 / all ones). The output is preset by a memset on `stream`.
+ * R == 0 gives the identity (0 / all ones). Rows of whole 16-byte vectors (inner even, 16-byte
+ * aligned pointers): one launch, every output word written exactly once. Otherwise the output is
+ * preset by a memset on `stream` and the blocks combine with atomics.
  * Replaces the log2(R) halving loop of ATen launches, brute/tensor.py:1440-1457. */
 int brute_b200_reduce_rows(int op, const uint64_t* in, uint64_t* out,
                            int64_t outer, int64_t R, int64_t inner, void* stream);
