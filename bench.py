@@ -394,16 +394,31 @@ def run_ours(args):
         dist.all_reduce(tg, op=dist.ReduceOp.MAX)
         extra["all_gather_C_ms"] = float(tg.item())
         del gathered
-        # (b) the public call, sharded_matmul(gather=True): GEMM by row blocks, int16 on the wire,
-        #     each block's all-gather under the next block's GEMM, widened into place on arrival
+        # (b) the public call, sharded_matmul(gather=True): GEMM by row blocks, int16 blocks, each block's
+        #     exchange under the next block's GEMM. Default: one kernel per row block pulls the peers'
+        #     blocks over NVLink (peer memory) and widens them into place; where no peer mapping is to
+        #     be had, NCCL all-gather + a widening pass (timed here as well, for comparison)
+        from brute_b200 import kernels as bk
         from brute_b200.kernels import sharded_matmul
         rep = {}
 
         def rep_step():
             rep["C"] = sharded_matmul(A, Bfull, k, gather=True)
-        r_times = time_steps(rep_step, 5, 2, flush, sync)
-        tr = torch.tensor([sum(r_times) / 5], dtype=torch.float64, device=dev)
-        dist.all_reduce(tr, op=dist.ReduceOp.MAX)
+
+        def timed_rep():
+            ts = time_steps(rep_step, 5, 2, flush, sync)
+            t = torch.tensor([sum(ts) / 5], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        os.environ["BRUTE_B200_GATHER"] = "nccl"
+        extra["replicated_result_nccl_ms"] = timed_rep()
+        assert torch.equal(rep["C"][:, lo:hi], holder["C"]), "replicated result (NCCL path) differs from the local block"
+        os.environ["BRUTE_B200_GATHER"] = "peer"
+        tr = torch.tensor([timed_rep()], dtype=torch.float64, device=dev)
+        peer_used = torch.tensor([1 if bk._peer_ws and all(bool(v) for v in bk._peer_ws.values()) else 0], device=dev)
+        dist.all_reduce(peer_used, op=dist.ReduceOp.MIN)
+        extra["replicated_result_path"] = "peer memory (own kernel, plain peer loads by bulk copy)" if int(peer_used.item()) else "NCCL all-gather + widening pass"
+        extra["peer_wait_status"] = bk.peer_gather_status()
         extra["replicated_result_ms"] = float(tr.item())
         extra["tops_with_gather"] = macs_all / (float(tr.item()) * 1e-3) / 1e12
         extra["tops_with_plain_int32_gather"] = macs_all / ((ms_per_step + float(tg.item())) * 1e-3) / 1e12

@@ -57,6 +57,10 @@ SIGNATURES = {
     "brute_b200_scatter_bits": [_p, _p, _p, _i32, _i64, _i64, _i64, _p],
     "brute_b200_narrow_i32_i16": [_p, _p, _i64, _p],
     "brute_b200_unstack_rank_blocks": [_p, _i32, _p, _i64, _i64, _i64, _i64, _p],
+    "brute_b200_peer_set_flag": [_p, C.c_uint32, _p],
+    "brute_b200_peer_wait_flags": [_p, _p, _i32, _i32, _i32, C.c_uint32, _i64, _p],
+    "brute_b200_gather_peer_widen": [_p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32, _i32, C.c_uint32, _i32, _i64, _p],
+    "brute_b200_peer_wait_status": [],
     "brute_b200_binary_attention_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _f32, _p],
 }
 _RESTYPES = {"brute_b200_strerror": C.c_char_p, "brute_b200_query_caps": C.c_uint32,

@@ -12,6 +12,7 @@
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -152,9 +153,119 @@ def _gather_workspace(dev, M: int, n_loc: int, world: int, narrow: bool):
     return ws
 
 
+# ---------------------------------------------------------------------------
+# The replicated result over peer memory: gather and widening in ONE kernel per row block
+# ---------------------------------------------------------------------------
+_peer_ws = {}
+_PEER_FLAG_WORDS = 64            # words 0..31: "row block i of call e is there"; word 32: "call e has been read"
+_PEER_DONE = 32
+_PEER_LIMIT_US = 2_000_000       # every flag wait in the kernels gives up after this long
+
+
+def _peer_workspace(dev, M: int, n_loc: int, world: int, rank: int, group):
+    """Symmetric memory of this rank (two send buffers, by call parity, and the flag words), mapped by
+    every peer; None when the platform offers no peer mapping (the caller then takes the NCCL path)."""
+    import ctypes as C
+    import torch.distributed as dist
+    key = (str(dev), M, n_loc, world, rank, id(group))
+    ws = _peer_ws.get(key)
+    if ws is not None:
+        return ws or None
+    try:
+        import torch.distributed._symmetric_memory as symm
+        send_bytes = (M * n_loc * 2 + 255) // 256 * 256
+        total = 2 * send_bytes + 4 * _PEER_FLAG_WORDS
+        buf = symm.empty(total, dtype=torch.uint8, device=dev)
+        buf.zero_()
+        hdl = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        ptrs = [int(x) for x in hdl.buffer_ptrs]
+        if len(ptrs) != world or not all(ptrs):
+            raise RuntimeError("peer mapping incomplete")
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)                    # every rank's flag words are zero before anyone reads them
+    except Exception:                                # no symmetric memory here: remember, and use NCCL
+        _peer_ws[key] = False
+        return None
+    arr = C.c_void_p * world
+    ws = {
+        "buf": buf, "hdl": hdl, "epoch": 0, "send_bytes": send_bytes,
+        "send": [arr(*[p + q * send_bytes for p in ptrs]) for q in (0, 1)],
+        "flags": arr(*[p + 2 * send_bytes for p in ptrs]),
+        "own_flags": ptrs[rank] + 2 * send_bytes,
+        "c_all": torch.empty((M, n_loc), dtype=torch.int32, device=dev),
+    }
+    _peer_ws.clear()                                 # one shape at a time, like the NCCL scratch
+    _peer_ws[key] = ws
+    return ws
+
+
+def _gather_peer_blocks(a_packed, b_local, K: int, world: int, rank: int, group, row_blocks: Optional[int],
+                        leave_sms: Optional[int] = None, ctas_per_peer: Optional[int] = None):
+    """``_gather_row_blocks`` without NCCL and without the staged copy: this rank narrows each row block
+    of its C into memory its peers have mapped and raises a flag; one kernel per row block, on a second
+    stream, waits for each peer's flag, reads that peer's int16 block over NVLink and writes the widened
+    values into the replicated result (``brute_b200_gather_peer_widen``). Returns None when peer
+    mapping is not available or the shape does not qualify (K > 32767, n_loc not a multiple of 8)."""
+    from . import _lib as L
+    lib = L.load()
+    M, n_loc = int(a_packed.shape[0]), int(b_local.shape[0])
+    dev = a_packed.device
+    if dev.type != "cuda" or int(K) > 32767 or n_loc % 8 or world > 16 or M == 0 or n_loc == 0:
+        return None
+    ws = _peer_workspace(dev, M, n_loc, world, rank, group)
+    if ws is None:
+        return None
+    nb = int(row_blocks) if row_blocks else max(1, min(4, M // 2048))
+    nb = max(1, min(nb, M, 32))
+    # Measured at 16384^3 (sweeps over row blocks x SMs left x CTAs per peer): on 8 GPUs the call is fastest
+    # with ONE gather CTA per SM that the GEMM leaves free (56 left, 7 CTAs per peer: 0.894 ms against
+    # 1.32 ms for NCCL + widening pass); on 2 GPUs, where the GEMM of a row block is four times longer,
+    # with 32 SMs left and 32 CTAs for the one peer (1.74 against 2.04 ms).
+    if leave_sms is None:
+        leave_sms = 32 if world == 2 else 56
+    if not ctas_per_peer:
+        ctas_per_peer = 32 if world == 2 else max(2, int(leave_sms) // world)
+    bounds = [b for b in (shard_bounds(M, nb, i) for i in range(nb)) if b[1] > b[0]]
+    ws["epoch"] += 1
+    e = ws["epoch"]
+    q = e & 1
+    out = torch.empty((M, world * n_loc), dtype=torch.int32, device=dev)
+    send_q = ws["buf"][q * ws["send_bytes"]:q * ws["send_bytes"] + M * n_loc * 2].view(torch.int16).view(M, n_loc)
+    cur = torch.cuda.current_stream(dev)
+    comm = _comm_stream(dev)
+    comm.wait_stream(cur)
+    with torch.cuda.device(dev):
+        if e > 2:   # the peers have read what this buffer held two calls ago
+            L.check(lib.brute_b200_peer_wait_flags(ws["send"][q], ws["flags"], world, rank, _PEER_DONE, e - 2,
+                                                   _PEER_LIMIT_US, cur.cuda_stream), "peer_wait_flags")
+        for i, (m0, m1) in enumerate(bounds):
+            leave = int(leave_sms) if i > 0 else 0
+            c = _ops.xnor_popcount_matmul_out(a_packed[m0:m1], b_local, K, leave, ws["c_all"][m0:m1])
+            _ops.narrow_i32_i16_out(c, send_q[m0:m1])
+            L.check(lib.brute_b200_peer_set_flag(ws["own_flags"] + 4 * i, e, cur.cuda_stream), "peer_set_flag")
+            ready = torch.cuda.Event()
+            ready.record(cur)
+            comm.wait_event(ready)                   # the own block is read without a flag
+            L.check(lib.brute_b200_gather_peer_widen(ws["send"][q], ws["flags"], out.data_ptr(), M, n_loc, m0, m1,
+                                                     world, rank, i, e, int(ctas_per_peer), _PEER_LIMIT_US,
+                                                     comm.cuda_stream), "gather_peer_widen")
+        L.check(lib.brute_b200_peer_set_flag(ws["own_flags"] + 4 * _PEER_DONE, e, comm.cuda_stream), "peer_set_flag")
+    done = torch.cuda.Event()
+    done.record(comm)
+    cur.wait_event(done)       # the caller's stream is behind every write to `out`: no record_stream needed
+    return out
+
+
+def peer_gather_status() -> int:
+    """0, or 1 + the rank whose flag a bounded wait of the peer-gather kernels gave up on (synchronises)."""
+    from . import _lib as L
+    return int(L.load().brute_b200_peer_wait_status())
+
+
 def release_gather_workspace() -> None:
     """Free the scratch that ``sharded_matmul(gather=True)`` keeps between calls of one shape."""
     _gather_ws.clear()
+    _peer_ws.clear()
 
 
 def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group=None,
@@ -170,6 +281,10 @@ def sharded_matmul(a_packed: torch.Tensor, b_packed: torch.Tensor, K: int, group
     N = b_packed.shape[0]
     lo, hi = shard_bounds(N, world, rank)
     if gather and world > 1 and N % world == 0:
+        if a_packed.is_cuda and os.environ.get("BRUTE_B200_GATHER", "peer") == "peer":
+            full = _gather_peer_blocks(a_packed, b_packed[lo:hi], K, world, rank, group, row_blocks)
+            if full is not None:
+                return full
         return _gather_row_blocks(a_packed, b_packed[lo:hi], K, world, group, row_blocks)
     c_local = _ops.xnor_popcount_matmul(a_packed, b_packed[lo:hi], K)
     if not gather or world == 1:

@@ -296,6 +296,30 @@ int brute_b200_narrow_i32_i16(const int32_t* in, int16_t* out, int64_t n, void* 
 int brute_b200_unstack_rank_blocks(const void* in, int elem_bytes, int32_t* out,
                                    int64_t world, int64_t rows, int64_t n_loc, int64_t ldc, void* stream);
 
+/* The same exchange over peer memory (no reference counterpart either): gather and widening in one
+ * pass, with plain peer loads over NVLink. Every rank keeps its narrowed blocks [M, n_loc] int16 and
+ * a few 32-bit flag words in memory that its peers have mapped (the caller provides the mappings:
+ * send_ptrs[p] / flag_ptrs[p] are rank p's buffer and flag words as THIS process sees them, host
+ * arrays of `world` <= 16 device pointers).
+ *  - peer_set_flag: *flag = value with release semantics at system scope, queued on `stream` behind
+ *    the work that produced the data the flag announces (flag: this rank's own word).
+ *  - gather_peer_widen: for every rank p, waits until flag_ptrs[p][flag_index] has reached `want`
+ *    (the own rank's block is not waited for), then out[m, p * n_loc + j] = send_ptrs[p][m, j] for
+ *    m in [m0, m1): out is this rank's row-major int32 [M, world * n_loc]. ctas_per_peer CTAs read
+ *    each peer (<= 0: 8).
+ *  - peer_wait_flags: waits until word `index` of every OTHER rank has reached `want` (before a
+ *    send buffer is written again).
+ * Flag values are call numbers that only grow, compared as signed differences. Every wait gives up
+ * after limit_us and records which rank's flag did not arrive: brute_b200_peer_wait_status()
+ * synchronises the device and returns 0, or 1 + that rank, and clears the record. Nothing traps. */
+int brute_b200_peer_set_flag(uint32_t* flag, uint32_t value, void* stream);
+int brute_b200_peer_wait_flags(const void* const* send_ptrs, const void* const* flag_ptrs, int world, int self,
+                               int index, uint32_t want, int64_t limit_us, void* stream);
+int brute_b200_gather_peer_widen(const void* const* send_ptrs, const void* const* flag_ptrs, int32_t* out,
+                                 int64_t M, int64_t n_loc, int64_t m0, int64_t m1, int world, int self,
+                                 int flag_index, uint32_t want, int ctas_per_peer, int64_t limit_us, void* stream);
+int brute_b200_peer_wait_status(void);
+
 /* ---- binary attention -------------------------------------------------- */
 /* Qp, Kp_ [B, H, S, D/64] words (sign-binarised Q and K), V and O bf16
  * [B, H, S, D]; score(i,j) = (D - 2*popcount(q_i ^ k_j)) * scale, optional
