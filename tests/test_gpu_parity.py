@@ -848,3 +848,64 @@ def test_narrow_and_unstack_rank_blocks(ops, world, rows, n_loc):
         ops.unstack_rank_blocks(stacked, out, 2)
         assert torch.equal(out[2:2 + rows].cpu(), want)
         assert bool((out[:2] == 12345).all()) and bool((out[2 + rows:] == 12345).all())
+
+
+def _peer_tables(bufs, flags):
+    import ctypes as C
+    arr = C.c_void_p * len(bufs)
+    return arr(*[b.data_ptr() for b in bufs]), arr(*[f.data_ptr() for f in flags])
+
+
+@pytest.mark.parametrize("world,M,n_loc,m0,m1", [(1, 40, 64, 0, 40), (2, 300, 2048, 0, 300), (4, 129, 136, 7, 120), (8, 2100, 512, 100, 2100)])
+def test_gather_peer_widen_on_one_device(world, M, n_loc, m0, m1):
+    """The peer-memory exchange kernels with every "rank" played by a buffer of this one device: blocks of
+    int16 [M, n_loc] per rank, flags raised through the library, then rank `self`'s replicated int32
+    result must hold every rank's rows [m0, m1) in its column block and nothing else."""
+    from brute_b200 import _lib as L
+    lib = L.load()
+    g = gen(world * M + n_loc)
+    blocks = [torch.randint(-32767, 32768, (M, n_loc), generator=g, dtype=torch.int16) for _ in range(world)]
+    bufs = [b.to(DEV) for b in blocks]
+    flags = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(world)]
+    send, flg = _peer_tables(bufs, flags)
+    stream = torch.cuda.current_stream().cuda_stream
+    for p in range(world):
+        L.check(lib.brute_b200_peer_set_flag(flags[p].data_ptr() + 4 * 3, 9, stream), "peer_set_flag")
+    torch.cuda.synchronize()
+    assert all(int(f[3]) == 9 for f in flags)
+    want = torch.cat(blocks, dim=1).to(torch.int32)
+    for self_rank in {0, world - 1}:
+        for ctas in (1, 5):
+            out = torch.full((M, world * n_loc), 777, dtype=torch.int32, device=DEV)
+            L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, m0, m1, world, self_rank,
+                                                     3, 9, ctas, 2_000_000, stream), "gather_peer_widen")
+            assert lib.brute_b200_peer_wait_status() == 0
+            got = out.cpu()
+            assert torch.equal(got[m0:m1], want[m0:m1])
+            assert bool((got[:m0] == 777).all()) and bool((got[m1:] == 777).all())
+    # waiting for an older call number is satisfied by a newer one (flags only grow)
+    L.check(lib.brute_b200_peer_wait_flags(send, flg, world, 0, 3, 8, 2_000_000, stream), "peer_wait_flags")
+    assert lib.brute_b200_peer_wait_status() == 0
+
+
+def test_peer_wait_gives_up_and_reports_the_rank():
+    """A flag that nobody raises: the bounded waits of the peer kernels run out after their limit (3 ms
+    here), the kernels return, the status names the rank, and the next exchange works. Nothing hangs."""
+    from brute_b200 import _lib as L
+    lib = L.load()
+    world, M, n_loc = 2, 64, 64
+    bufs = [torch.ones((M, n_loc), dtype=torch.int16, device=DEV) * (p + 1) for p in range(world)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(world)]
+    send, flg = _peer_tables(bufs, flags)
+    stream = torch.cuda.current_stream().cuda_stream
+    out = torch.zeros((M, world * n_loc), dtype=torch.int32, device=DEV)
+    L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, 0, M, world, 0, 5, 1, 2, 3000, stream), "gather")
+    assert lib.brute_b200_peer_wait_status() == 1 + 1           # rank 1's flag did not arrive
+    assert bool((out[:, :n_loc] == 1).all()) and bool((out[:, n_loc:] == 0).all())   # the own block needs no flag
+    L.check(lib.brute_b200_peer_wait_flags(send, flg, world, 0, 5, 1, 3000, stream), "wait_flags")
+    assert lib.brute_b200_peer_wait_status() == 1 + 1
+    assert lib.brute_b200_peer_wait_status() == 0               # reading cleared it
+    L.check(lib.brute_b200_peer_set_flag(flags[1].data_ptr() + 4 * 5, 1, stream), "set_flag")
+    L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, 0, M, world, 0, 5, 1, 2, 3000, stream), "gather")
+    assert lib.brute_b200_peer_wait_status() == 0
+    assert bool((out[:, n_loc:] == 2).all())
