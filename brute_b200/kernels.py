@@ -171,6 +171,8 @@ def _peer_workspace(dev, M: int, n_loc: int, world: int, rank: int, group):
     ws = _peer_ws.get(key)
     if ws is not None:
         return ws or None
+    buf = hdl = None
+    ptrs = []
     try:
         import torch.distributed._symmetric_memory as symm
         send_bytes = (M * n_loc * 2 + 255) // 256 * 256
@@ -179,11 +181,15 @@ def _peer_workspace(dev, M: int, n_loc: int, world: int, rank: int, group):
         buf.zero_()
         hdl = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
         ptrs = [int(x) for x in hdl.buffer_ptrs]
-        if len(ptrs) != world or not all(ptrs):
-            raise RuntimeError("peer mapping incomplete")
-        torch.cuda.synchronize(dev)
-        dist.barrier(group=group)                    # every rank's flag words are zero before anyone reads them
-    except Exception:                                # no symmetric memory here: remember, and use NCCL
+        mine = len(ptrs) == world and all(ptrs)
+    except Exception:
+        mine = False
+    # the choice of path must be the same on every rank (one rank on NCCL and the others on peer
+    # memory would wait for each other), and every rank's flag words must be zero before anyone reads them
+    torch.cuda.synchronize(dev)
+    agreed = torch.tensor([1 if mine else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+    if int(agreed.item()) == 0:                      # no symmetric memory here: remember, and use NCCL
         _peer_ws[key] = False
         return None
     arr = C.c_void_p * world
