@@ -420,6 +420,11 @@ def run_ours(args):
         extra["replicated_result_path"] = "peer memory (own kernel, plain peer loads by bulk copy)" if int(peer_used.item()) else "NCCL all-gather + widening pass"
         extra["peer_wait_status"] = bk.peer_gather_status()
         extra["replicated_result_ms"] = float(tr.item())
+        # what has to cross NVLink into every rank: the other ranks' int16 blocks; 770 GB/s per direction is
+        # the measured peer-copy rate of this pool (900 nominal)
+        inbound = (world - 1) * m * n_loc * 2
+        extra["replicated_result_link"] = {"inbound_bytes_per_rank": inbound, "floor_ms_at_770GB/s": inbound / 770e9 * 1e3,
+                                           "achieved_GB/s_over_whole_call": inbound / (float(tr.item()) * 1e-3) / 1e9}
         extra["tops_with_gather"] = macs_all / (float(tr.item()) * 1e-3) / 1e12
         extra["tops_with_plain_int32_gather"] = macs_all / ((ms_per_step + float(tg.item())) * 1e-3) / 1e12
         # this rank's columns of the replicated result are its own GEMM block, bit for bit
