@@ -58,7 +58,8 @@ def parse_args():
     ap.add_argument("--op", default="gemm",
                     help="time ONE op alone (for profiler captures): gemm | pack_sign | pack_bool | unpack_bool | "
                          "unpack_pm1 | popcount_total | hamming_total | word_popcount | xor | not | attention | mlp | "
-                         "pack_bool_4097 | unpack_bool_4097 | memset | transpose_bits | any_dim0 | flip | roll | signed_bundle")
+                         "pack_bool_4097 | unpack_bool_4097 | memset | transpose_bits | any_dim0 | flip | roll | signed_bundle | "
+                         "gather_sweep (under torchrun: the replicated result over peer memory, parameter sweep)")
     ap.add_argument("--log2-bits", type=int, default=28, help="size of the bandwidth ops under --op")
     ap.add_argument("--att", default="2,8,4096,128", help="B,H,S,D of --op attention")
     return ap.parse_args()
@@ -753,10 +754,82 @@ def run_single_op(args):
     print(json.dumps(line), flush=True)
 
 
+def run_gather_sweep(args):
+    """torchrun only (`--op gather_sweep`): the replicated result of the 16384^3 GEMM over peer memory, timed for
+    row blocks x SMs the GEMM leaves free x gather CTAs per peer (CUDA events over 5 back-to-back calls, max
+    over ranks), beside the NCCL form and its parts. One JSON line from rank 0."""
+    import torch
+    import torch.distributed as dist
+    world, rank, local_rank = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    import brute_b200  # noqa: F401
+    from brute_b200 import kernels as bk
+    ops = torch.ops.brute
+    size = args.size
+    kp = size // 64
+    g = torch.Generator(device=dev).manual_seed(1234)
+    A = torch.randint(-2 ** 63, 2 ** 63 - 1, (size, kp), generator=g, dtype=torch.int64, device=dev)
+    B = torch.randint(-2 ** 63, 2 ** 63 - 1, (size, kp), generator=g, dtype=torch.int64, device=dev)
+    lo, hi = bk.shard_bounds(size, world, rank)
+    Bl = B[lo:hi].contiguous()
+
+    def timeit(fn, n=5, w=2):
+        for _ in range(w):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return round(float(t), 4)
+
+    res = {"world": world, "size": size}
+    res["gemm_ms"] = timeit(lambda: ops.xnor_popcount_matmul(A, Bl, size))
+    c = ops.xnor_popcount_matmul(A, Bl, size)
+    s16 = ops.narrow_i32_i16(c)
+    st16 = torch.empty((world, size, hi - lo), dtype=torch.int16, device=dev)
+    res["narrow_ms"] = timeit(lambda: ops.narrow_i32_i16(c))
+    res["nccl_all_gather_int16_ms"] = timeit(lambda: dist.all_gather_into_tensor(st16.view(world * size, hi - lo).view(torch.uint8), s16.view(torch.uint8)))
+    out = torch.empty((size, size), dtype=torch.int32, device=dev)
+    res["unstack_ms"] = timeit(lambda: ops.unstack_rank_blocks(st16, out, 0))
+    del st16, out, s16, c
+    ref = bk._gather_row_blocks(A, Bl, size, world, None, None)
+    res["nccl_form_ms"] = timeit(lambda: bk._gather_row_blocks(A, Bl, size, world, None, None))
+    got = bk._gather_peer_blocks(A, Bl, size, world, rank, None, None)
+    if got is None:
+        res["peer"] = "unavailable"
+    else:
+        res["peer_equals_nccl_form"] = bool(torch.equal(ref, got))
+        res["peer_default_ms"] = timeit(lambda: bk._gather_peer_blocks(A, Bl, size, world, rank, None, None))
+        sweep = {}
+        leaves = (32, 48) if world == 2 else (40, 48, 56, 64)
+        ctas = (16, 32) if world == 2 else (5, 6, 7, 8)
+        for nb in (2, 4, 8):
+            for leave in leaves:
+                for cpp in ctas:
+                    sweep[f"blocks{nb}_leave{leave}_ctas{cpp}"] = timeit(
+                        lambda nb=nb, leave=leave, cpp=cpp: bk._gather_peer_blocks(A, Bl, size, world, rank, None, nb, leave, cpp))
+        res["peer_sweep_ms"] = sweep
+        res["peer_wait_status"] = bk.peer_gather_status()
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.op == "gather_sweep":
+        run_gather_sweep(args)
     elif args.op != "gemm":
         run_single_op(args)
     else:
