@@ -809,11 +809,11 @@ def run_gather_sweep(args):
         res["peer_equals_nccl_form"] = bool(torch.equal(ref, got))
         res["peer_default_ms"] = timeit(lambda: bk._gather_peer_blocks(A, Bl, size, world, rank, None, None))
         sweep = {}
-        leaves = (32, 48) if world == 2 else (40, 48, 56, 64)
-        ctas = (16, 32) if world == 2 else (5, 6, 7, 8)
+        leaves = (32, 48) if world == 2 else (24, 32, 40, 48, 56, 64)
         for nb in (2, 4, 8):
             for leave in leaves:
-                for cpp in ctas:
+                # around one gather CTA per SM left free (2 GPUs: the one peer takes many more)
+                for cpp in ((16, 32) if world == 2 else sorted({max(2, leave // world + d) for d in (-1, 0, 1)})):
                     sweep[f"blocks{nb}_leave{leave}_ctas{cpp}"] = timeit(
                         lambda nb=nb, leave=leave, cpp=cpp: bk._gather_peer_blocks(A, Bl, size, world, rank, None, nb, leave, cpp))
         res["peer_sweep_ms"] = sweep
