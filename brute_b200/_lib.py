@@ -14,6 +14,7 @@ LIB_PATH = _PKG / "libbrute_b200.so"
 
 # keep in step with include/brute_b200.h
 OK = 0
+UNSUPPORTED = -3        # BRUTE_ERR_UNSUPPORTED: the entry point does not take this shape
 ERR_INVALID_ARG, ERR_MISALIGNED, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_WORKSPACE, ERR_DEVICE_WAIT, ERR_DRIVER = -1, -2, -3, -4, -5, -6, -7
 SIGN_GT0, SIGN_GE0 = 0, 1
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
@@ -57,6 +58,7 @@ SIGNATURES = {
     "brute_b200_scatter_bits": [_p, _p, _p, _i32, _i64, _i64, _i64, _p],
     "brute_b200_narrow_i32_i16": [_p, _p, _i64, _p],
     "brute_b200_unstack_rank_blocks": [_p, _i32, _p, _i64, _i64, _i64, _i64, _p],
+    "brute_b200_xnor_gemm_i16": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _p],
     "brute_b200_peer_set_flag": [_p, C.c_uint32, _p],
     "brute_b200_peer_wait_flags": [_p, _p, _i32, _i32, _i32, C.c_uint32, _i64, _p],
     "brute_b200_gather_peer_widen": [_p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32, _i32, C.c_uint32, _i32, _i64, _p],

@@ -141,6 +141,18 @@ extern "C" int brute_b200_xnor_gemm_leave_sms(const uint64_t* A, const uint64_t*
     return dispatch(g, BRUTE_GEMM_AUTO, as_stream(stream));
 }
 
+extern "C" int brute_b200_xnor_gemm_i16(const uint64_t* A, const uint64_t* B, int16_t* C,
+                                        int64_t M, int64_t N, int64_t Kp, int64_t K, int64_t ldc,
+                                        int leave_sms, void* stream) {
+    BB_REQUIRE(M >= 0 && N >= 0 && Kp >= 0 && K >= 0 && K <= 64 * Kp, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE(K <= 32767 && Kp > 0 && M < (1ll << 31) && N < (1ll << 31), BRUTE_ERR_UNSUPPORTED);
+    BB_REQUIRE(leave_sms >= 0 && leave_sms <= kNumSMs - 2, BRUTE_ERR_INVALID_ARG);
+    if (M == 0 || N == 0) return BRUTE_OK;
+    BB_REQUIRE(C != nullptr && ldc >= N && A != nullptr && B != nullptr, BRUTE_ERR_INVALID_ARG);
+    BB_REQUIRE((reinterpret_cast<uintptr_t>(C) & 1u) == 0 && aligned8(A) && aligned8(B), BRUTE_ERR_MISALIGNED);
+    return tc5_pair_run_i16(A, B, M, N, Kp, K, C, ldc, as_stream(stream), leave_sms);
+}
+
 extern "C" int brute_b200_xnor_gemm_scale_sign_pack(const uint64_t* A, const uint64_t* B,
                                                     const float* scale, uint64_t* out,
                                                     int64_t M, int64_t N, int64_t Kp, int64_t K,

@@ -204,7 +204,8 @@ __device__ __forceinline__ bool tp_expand_tile(PairExpanderCtx& cx, int32_t nst)
     return true;
 }
 
-// STORE: 0 = int32 C through TMA stores (C 16-byte aligned, ldc a multiple of 4), 1 = int32 C by
+// STORE: 3 = int16 C by plain stores (`C` then points at int16 values, ldc counts them), for the exchange
+// of a column-sharded result between GPUs; 0 = int32 C through TMA stores (C 16-byte aligned, ldc a multiple of 4), 1 = int32 C by
 // plain stores from registers, 2 = fused scale/sign/pack (binarised MLP layer).
 template <int STORE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -450,6 +451,21 @@ k_xnor_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_c
                             for (int j = 0; j < 32; ++j) if (n + j < N) dst[j] = (int32_t)v[j];
                         }
                     }
+                } else if (STORE == 3) {
+                    // int16 C (exact for K <= 32767), straight from registers: a row's 32 values are 64 bytes
+                    if (m < M) {
+                        int16_t* dst = reinterpret_cast<int16_t*>(C) + m * ldc + n;
+                        if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8)
+                                *reinterpret_cast<uint4*>(dst + j) =
+                                    make_uint4((v[j] & 0xFFFFu) | (v[j + 1] << 16), (v[j + 2] & 0xFFFFu) | (v[j + 3] << 16),
+                                               (v[j + 4] & 0xFFFFu) | (v[j + 5] << 16), (v[j + 6] & 0xFFFFu) | (v[j + 7] << 16));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (n + j < N) dst[j] = (int16_t)(int32_t)v[j];
+                        }
+                    }
                 } else {
                     // bit j = (s_j * C + off_j >= 0), C = row_term - 2 pb_j + 4 a: integer only
                     const int* csp = col_s + par * TP_BN + col;
@@ -589,6 +605,18 @@ static int tc5_pair_run(const uint64_t* A, const uint64_t* B, int64_t M, int64_t
         return tc5_pair_launch<0>(tmA, tmB, tmC, M, N, nkb, (int32_t)K, tiles_m, ntiles, C, ldc, nullptr, nullptr, 0, 0, st, leave_sms);
     tmC = tmA;
     return tc5_pair_launch<1>(tmA, tmB, tmC, M, N, nkb, (int32_t)K, tiles_m, ntiles, C, ldc, nullptr, nullptr, 0, 0, st, leave_sms);
+}
+
+// C as int16 [M, ldc]: the transport form of a column-sharded result (|C| <= K <= 32767)
+static int tc5_pair_run_i16(const uint64_t* A, const uint64_t* B, int64_t M, int64_t N, int64_t Kp, int64_t K,
+                            int16_t* C, int64_t ldc, cudaStream_t st, int leave_sms) {
+    BB_REQUIRE(K <= 32767 && tc5_accepts(A, B, M, N, Kp) && tc5_pair_accepts(M, N), BRUTE_ERR_UNSUPPORTED);
+    CUtensorMap tmA, tmB;
+    BB_REQUIRE(tc5_make_map(&tmA, A, M, Kp * 8, TP_BM) && tc5_make_map(&tmB, B, N, Kp * 8, TP_BNH), BRUTE_ERR_DRIVER);
+    const int32_t tiles_m = (int32_t)((M + 2 * TP_BM - 1) / (2 * TP_BM));
+    const int32_t ntiles = tiles_m * (int32_t)((N + TP_BN - 1) / TP_BN);
+    return tc5_pair_launch<3>(tmA, tmB, tmA /* unused */, M, N, (int32_t)(Kp / 2), (int32_t)K, tiles_m, ntiles,
+                              reinterpret_cast<int32_t*>(C), ldc, nullptr, nullptr, 0, 0, st, leave_sms);
 }
 
 }  // namespace bb

@@ -240,14 +240,27 @@ def _gather_peer_blocks(a_packed, b_local, K: int, world: int, rank: int, group,
     cur = torch.cuda.current_stream(dev)
     comm = _comm_stream(dev)
     comm.wait_stream(cur)
+    fused_ok = (a_packed.is_contiguous() and b_local.is_contiguous() and a_packed.dtype == torch.int64
+                and b_local.dtype == torch.int64 and os.environ.get("BRUTE_B200_GATHER_FUSED", "1") != "0")
     with torch.cuda.device(dev):
         if e > 2:   # the peers have read what this buffer held two calls ago
             L.check(lib.brute_b200_peer_wait_flags(ws["send"][q], ws["flags"], world, rank, _PEER_DONE, e - 2,
                                                    _PEER_LIMIT_US, cur.cuda_stream), "peer_wait_flags")
         for i, (m0, m1) in enumerate(bounds):
             leave = int(leave_sms) if i > 0 else 0
-            c = _ops.xnor_popcount_matmul_out(a_packed[m0:m1], b_local, K, leave, ws["c_all"][m0:m1])
-            _ops.narrow_i32_i16_out(c, send_q[m0:m1])
+            # the GEMM writes its int16 block straight into the symmetric buffer where the pair kernel takes
+            # the operands; otherwise int32 GEMM + narrowing pass
+            a_blk = a_packed[m0:m1]
+            rc = L.UNSUPPORTED
+            if fused_ok:
+                rc = lib.brute_b200_xnor_gemm_i16(a_blk.data_ptr(), b_local.data_ptr(), send_q[m0:m1].data_ptr(), m1 - m0, n_loc,
+                                                  int(a_blk.shape[1]), int(K), n_loc, leave, cur.cuda_stream)
+            if rc == L.UNSUPPORTED:
+                fused_ok = False
+                c = _ops.xnor_popcount_matmul_out(a_blk, b_local, K, leave, ws["c_all"][m0:m1])
+                _ops.narrow_i32_i16_out(c, send_q[m0:m1])
+            else:
+                L.check(rc, "xnor_gemm_i16")
             L.check(lib.brute_b200_peer_set_flag(ws["own_flags"] + 4 * i, e, cur.cuda_stream), "peer_set_flag")
             ready = torch.cuda.Event()
             ready.record(cur)

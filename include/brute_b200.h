@@ -293,6 +293,13 @@ int brute_b200_signed_bundle_ws(const int8_t* W, const uint64_t* V, uint64_t* ou
  * (elem_bytes 2: int16, 4: int32), becomes row-major int32: out[m * ldc + r * n_loc + j] =
  * in[r, m, j]; ldc >= world * n_loc. in and out must not overlap. */
 int brute_b200_narrow_i32_i16(const int32_t* in, int16_t* out, int64_t n, void* stream);
+/* The GEMM of brute_b200_xnor_gemm_leave_sms with C written as int16 [M, ldc] straight from the
+ * epilogue (no int32 result, no narrowing pass): exact for K <= 32767. Tensor-core pair kernel only:
+ * BRUTE_ERR_UNSUPPORTED for K > 32767 and for operands that kernel does not take (the caller then uses
+ * the int32 GEMM and brute_b200_narrow_i32_i16). */
+int brute_b200_xnor_gemm_i16(const uint64_t* A, const uint64_t* B, int16_t* C,
+                             int64_t M, int64_t N, int64_t Kp, int64_t K, int64_t ldc,
+                             int leave_sms, void* stream);
 int brute_b200_unstack_rank_blocks(const void* in, int elem_bytes, int32_t* out,
                                    int64_t world, int64_t rows, int64_t n_loc, int64_t ldc, void* stream);
 

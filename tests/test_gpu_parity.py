@@ -909,3 +909,28 @@ def test_peer_wait_gives_up_and_reports_the_rank():
     L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, 0, M, world, 0, 5, 1, 2, 3000, stream), "gather")
     assert lib.brute_b200_peer_wait_status() == 0
     assert bool((out[:, n_loc:] == 2).all())
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 1024, 512), (300, 640, 700), (513, 384, 129), (1024, 16384, 2048), (2048, 32704, 256)])
+def test_gemm_int16_output_equals_the_narrowed_int32_result(ops, M, K, N):
+    """The GEMM variant that writes C as int16 from its epilogue (the transport form of a sharded result):
+    equal to the int32 GEMM narrowed, into a wider destination (ldc > N) whose other columns stay put."""
+    from brute_b200 import _lib as L
+    lib = L.load()
+    kp = (K + 63) // 64
+    a = torch.randint(-2 ** 63, 2 ** 63 - 1, (M, kp), generator=gen(M + K), dtype=torch.int64).to(DEV)
+    b = torch.randint(-2 ** 63, 2 ** 63 - 1, (N, kp), generator=gen(N + K), dtype=torch.int64).to(DEV)
+    if K % 64:
+        a[:, -1] &= (1 << (K % 64)) - 1
+        b[:, -1] &= (1 << (K % 64)) - 1
+    want = ops.xnor_popcount_matmul(a, b, K).to(torch.int16)
+    ldc = N + 8
+    for leave in (0, 32):
+        out = torch.full((M, ldc), -7, dtype=torch.int16, device=DEV)
+        rc = lib.brute_b200_xnor_gemm_i16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, kp, K, ldc, leave,
+                                          torch.cuda.current_stream().cuda_stream)
+        if rc == L.UNSUPPORTED:
+            pytest.skip("shape outside the pair kernel")
+        L.check(rc, "xnor_gemm_i16")
+        assert torch.equal(out[:, :N], want)
+        assert bool((out[:, N:] == -7).all())
