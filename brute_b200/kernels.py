@@ -198,7 +198,7 @@ def _peer_workspace(dev, M: int, n_loc: int, world: int, rank: int, group):
         "send": [arr(*[p + q * send_bytes for p in ptrs]) for q in (0, 1)],
         "flags": arr(*[p + 2 * send_bytes for p in ptrs]),
         "own_flags": ptrs[rank] + 2 * send_bytes,
-        "c_all": torch.empty((M, n_loc), dtype=torch.int32, device=dev),
+        "c_all": None,                               # int32 blocks: only when the int16 GEMM does not take the shape
     }
     _peer_ws.clear()                                 # one shape at a time, like the NCCL scratch
     _peer_ws[key] = ws
@@ -257,6 +257,8 @@ def _gather_peer_blocks(a_packed, b_local, K: int, world: int, rank: int, group,
                                                   int(a_blk.shape[1]), int(K), n_loc, leave, cur.cuda_stream)
             if rc == L.UNSUPPORTED:
                 fused_ok = False
+                if ws["c_all"] is None:
+                    ws["c_all"] = torch.empty((M, n_loc), dtype=torch.int32, device=dev)
                 c = _ops.xnor_popcount_matmul_out(a_blk, b_local, K, leave, ws["c_all"][m0:m1])
                 _ops.narrow_i32_i16_out(c, send_q[m0:m1])
             else:
