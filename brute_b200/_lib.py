@@ -61,7 +61,7 @@ SIGNATURES = {
     "brute_b200_xnor_gemm_i16": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _p],
     "brute_b200_peer_set_flag": [_p, C.c_uint32, _p],
     "brute_b200_peer_wait_flags": [_p, _p, _i32, _i32, _i32, C.c_uint32, _i64, _p],
-    "brute_b200_gather_peer_widen": [_p, _p, _p, _i64, _i64, _i64, _i64, _i32, _i32, _i32, C.c_uint32, _i32, _i64, _p],
+    "brute_b200_gather_peer_widen": [_p, _p, _p, _i64, _i64, _i32, _i64, _i64, _i32, _i32, _i32, C.c_uint32, _i32, _i64, _p],
     "brute_b200_peer_wait_status": [],
     "brute_b200_binary_attention_fwd": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _f32, _p],
 }

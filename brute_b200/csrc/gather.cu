@@ -203,6 +203,8 @@ __device__ __forceinline__ bool gp_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// EB = bytes per element of the peers' blocks: 2 (int16, widened on the way) or 4 (int32, for K > 32767)
+template <int EB>
 __global__ void __launch_bounds__(GP_THREADS)
 k_gather_peer_widen_bulk(PeerBlocks t, int32_t* __restrict__ out, int64_t ldc, int64_t n_loc,
                          int64_t m0, int64_t m1, int world, int self, int flag_index, uint32_t want, uint64_t limit_ns) {
@@ -211,9 +213,9 @@ k_gather_peer_widen_bulk(PeerBlocks t, int32_t* __restrict__ out, int64_t ldc, i
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(gp_smem);
     const uint32_t bars = ring + GP_STAGES * GP_STAGE_BYTES;                 // GP_STAGES mbarriers
     __shared__ int s_ok;
-    const int64_t block_bytes = (m1 - m0) * n_loc * 2;
+    const int64_t block_bytes = (m1 - m0) * n_loc * EB;
     const int64_t n_tiles = (block_bytes + GP_STAGE_BYTES - 1) / GP_STAGE_BYTES;
-    const uint8_t* src0 = reinterpret_cast<const uint8_t*>(t.send[p] + m0 * n_loc);
+    const uint8_t* src0 = reinterpret_cast<const uint8_t*>(t.send[p]) + m0 * n_loc * EB;
     auto tile_bytes = [&](int64_t tile) -> uint32_t {
         const int64_t left = block_bytes - tile * GP_STAGE_BYTES;
         return (uint32_t)(left < GP_STAGE_BYTES ? left : GP_STAGE_BYTES);
@@ -262,18 +264,23 @@ k_gather_peer_widen_bulk(PeerBlocks t, int32_t* __restrict__ out, int64_t ldc, i
         __syncthreads();                        // also publishes s_ok
         if (!s_ok) break;
         const uint32_t nvec = tile_bytes(tile) / 16;
-        const int64_t e0 = tile * (GP_STAGE_BYTES / 2);                       // first element of the tile inside the block
+        constexpr int EPV = 16 / EB;                                          // elements per 16-byte vector
+        const int64_t e0 = tile * (GP_STAGE_BYTES / EB);                      // first element of the tile inside the block
         for (uint32_t v = threadIdx.x; v < nvec; v += GP_THREADS) {
             const uint4 a = *reinterpret_cast<const uint4*>(gp_smem + (size_t)s * GP_STAGE_BYTES + 16u * v);
-            const int64_t e = e0 + 8ll * v;
+            const int64_t e = e0 + (int64_t)EPV * v;
             int64_t m, j;
             if (small) {                        // a 64-bit division per vector costs more than the vector's copy
                 const uint32_t mm = (uint32_t)e / (uint32_t)n_loc;
                 m = mm; j = (uint32_t)e - mm * (uint32_t)n_loc;
             } else { m = e / n_loc; j = e - m * n_loc; }
             int32_t* dst = dst0 + m * ldc + j;
-            stg_stream(dst,     make_uint4((uint32_t)sx16(a.x), (uint32_t)sx16(a.x >> 16), (uint32_t)sx16(a.y), (uint32_t)sx16(a.y >> 16)));
-            stg_stream(dst + 4, make_uint4((uint32_t)sx16(a.z), (uint32_t)sx16(a.z >> 16), (uint32_t)sx16(a.w), (uint32_t)sx16(a.w >> 16)));
+            if (EB == 2) {
+                stg_stream(dst,     make_uint4((uint32_t)sx16(a.x), (uint32_t)sx16(a.x >> 16), (uint32_t)sx16(a.y), (uint32_t)sx16(a.y >> 16)));
+                stg_stream(dst + 4, make_uint4((uint32_t)sx16(a.z), (uint32_t)sx16(a.z >> 16), (uint32_t)sx16(a.w), (uint32_t)sx16(a.w >> 16)));
+            } else {
+                stg_stream(dst, a);
+            }
         }
         __syncthreads();                        // the stage has been read by everyone
         if (threadIdx.x == 0) {
@@ -368,25 +375,32 @@ extern "C" int brute_b200_peer_wait_flags(const void* const* send_ptrs, const vo
 }
 
 extern "C" int brute_b200_gather_peer_widen(const void* const* send_ptrs, const void* const* flag_ptrs, int32_t* out,
-                                            int64_t M, int64_t n_loc, int64_t m0, int64_t m1, int world, int self,
+                                            int64_t M, int64_t n_loc, int elem_bytes, int64_t m0, int64_t m1, int world, int self,
                                             int flag_index, uint32_t want, int ctas_per_peer, int64_t limit_us, void* stream) {
     bb::PeerBlocks t;
     BB_REQUIRE(peer_table(t, send_ptrs, flag_ptrs, world) && self >= 0 && self < world, BRUTE_ERR_INVALID_ARG);
     BB_REQUIRE(out != nullptr && M >= 0 && 0 <= m0 && m0 <= m1 && m1 <= M && n_loc >= 0 && flag_index >= 0 && limit_us > 0, BRUTE_ERR_INVALID_ARG);
-    BB_REQUIRE(n_loc % 8 == 0 && aligned16(out), BRUTE_ERR_MISALIGNED);
+    BB_REQUIRE(elem_bytes == 2 || elem_bytes == 4, BRUTE_ERR_UNSUPPORTED);
+    BB_REQUIRE(n_loc % (16 / elem_bytes) == 0 && aligned16(out), BRUTE_ERR_MISALIGNED);
     for (int p = 0; p < world; ++p) BB_REQUIRE(aligned16(t.send[p]), BRUTE_ERR_MISALIGNED);
     if (m1 == m0 || n_loc == 0) return BRUTE_OK;
     if (ctas_per_peer < 1) ctas_per_peer = 8;
     const dim3 grid((unsigned)ctas_per_peer, (unsigned)world);
     static const bool use_loads = std::getenv("BRUTE_B200_PEER_LOADS") != nullptr;       // the per-thread-load form, for comparison
-    if (use_loads) {
+    if (use_loads && elem_bytes == 2) {
         bb::k_gather_peer_widen<<<grid, 256, 0, as_stream(stream)>>>(t, out, (int64_t)world * n_loc, n_loc, m0, m1, world, self,
                                                                    flag_index, want, (uint64_t)limit_us * 1000ull);
         return launch_status();
     }
-    if (!kernel_smem_ready<bb::k_gather_peer_widen_bulk>(bb::GP_SMEM)) return BRUTE_ERR_LAUNCH;
-    bb::k_gather_peer_widen_bulk<<<grid, bb::GP_THREADS, bb::GP_SMEM, as_stream(stream)>>>(
-        t, out, (int64_t)world * n_loc, n_loc, m0, m1, world, self, flag_index, want, (uint64_t)limit_us * 1000ull);
+    if (elem_bytes == 2) {
+        if (!kernel_smem_ready<bb::k_gather_peer_widen_bulk<2>>(bb::GP_SMEM)) return BRUTE_ERR_LAUNCH;
+        bb::k_gather_peer_widen_bulk<2><<<grid, bb::GP_THREADS, bb::GP_SMEM, as_stream(stream)>>>(
+            t, out, (int64_t)world * n_loc, n_loc, m0, m1, world, self, flag_index, want, (uint64_t)limit_us * 1000ull);
+    } else {
+        if (!kernel_smem_ready<bb::k_gather_peer_widen_bulk<4>>(bb::GP_SMEM)) return BRUTE_ERR_LAUNCH;
+        bb::k_gather_peer_widen_bulk<4><<<grid, bb::GP_THREADS, bb::GP_SMEM, as_stream(stream)>>>(
+            t, out, (int64_t)world * n_loc, n_loc, m0, m1, world, self, flag_index, want, (uint64_t)limit_us * 1000ull);
+    }
     return launch_status();
 }
 

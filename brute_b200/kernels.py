@@ -162,12 +162,12 @@ _PEER_DONE = 32
 _PEER_LIMIT_US = 2_000_000       # every flag wait in the kernels gives up after this long
 
 
-def _peer_workspace(dev, M: int, n_loc: int, world: int, rank: int, group):
+def _peer_workspace(dev, M: int, n_loc: int, world: int, rank: int, group, elem_bytes: int = 2):
     """Symmetric memory of this rank (two send buffers, by call parity, and the flag words), mapped by
     every peer; None when the platform offers no peer mapping (the caller then takes the NCCL path)."""
     import ctypes as C
     import torch.distributed as dist
-    key = (str(dev), M, n_loc, world, rank, id(group))
+    key = (str(dev), M, n_loc, world, rank, id(group), elem_bytes)
     ws = _peer_ws.get(key)
     if ws is not None:
         return ws or None
@@ -175,7 +175,7 @@ def _peer_workspace(dev, M: int, n_loc: int, world: int, rank: int, group):
     ptrs = []
     try:
         import torch.distributed._symmetric_memory as symm
-        send_bytes = (M * n_loc * 2 + 255) // 256 * 256
+        send_bytes = (M * n_loc * elem_bytes + 255) // 256 * 256
         total = 2 * send_bytes + 4 * _PEER_FLAG_WORDS
         buf = symm.empty(total, dtype=torch.uint8, device=dev)
         buf.zero_()
@@ -211,14 +211,16 @@ def _gather_peer_blocks(a_packed, b_local, K: int, world: int, rank: int, group,
     of its C into memory its peers have mapped and raises a flag; one kernel per row block, on a second
     stream, waits for each peer's flag, reads that peer's int16 block over NVLink and writes the widened
     values into the replicated result (``brute_b200_gather_peer_widen``). Returns None when peer
-    mapping is not available or the shape does not qualify (K > 32767, n_loc not a multiple of 8)."""
+    mapping is not available or the shard width is not a multiple of 8 (4 for K > 32767, where the blocks
+    travel as int32)."""
     from . import _lib as L
     lib = L.load()
     M, n_loc = int(a_packed.shape[0]), int(b_local.shape[0])
     dev = a_packed.device
-    if dev.type != "cuda" or int(K) > 32767 or n_loc % 8 or world > 16 or M == 0 or n_loc == 0:
+    eb = 2 if int(K) <= 32767 else 4         # int16 blocks where |C| <= K fits, else the int32 blocks as they are
+    if dev.type != "cuda" or n_loc % (16 // eb) or world > 16 or M == 0 or n_loc == 0:
         return None
-    ws = _peer_workspace(dev, M, n_loc, world, rank, group)
+    ws = _peer_workspace(dev, M, n_loc, world, rank, group, eb)
     if ws is None:
         return None
     nb = int(row_blocks) if row_blocks else max(1, min(4, M // 2048))
@@ -236,7 +238,7 @@ def _gather_peer_blocks(a_packed, b_local, K: int, world: int, rank: int, group,
     e = ws["epoch"]
     q = e & 1
     out = torch.empty((M, world * n_loc), dtype=torch.int32, device=dev)
-    send_q = ws["buf"][q * ws["send_bytes"]:q * ws["send_bytes"] + M * n_loc * 2].view(torch.int16).view(M, n_loc)
+    send_q = ws["buf"][q * ws["send_bytes"]:q * ws["send_bytes"] + M * n_loc * eb].view(torch.int16 if eb == 2 else torch.int32).view(M, n_loc)
     cur = torch.cuda.current_stream(dev)
     comm = _comm_stream(dev)
     comm.wait_stream(cur)
@@ -252,7 +254,10 @@ def _gather_peer_blocks(a_packed, b_local, K: int, world: int, rank: int, group,
             # the operands; otherwise int32 GEMM + narrowing pass
             a_blk = a_packed[m0:m1]
             rc = L.UNSUPPORTED
-            if fused_ok:
+            if eb == 4:                              # K > 32767: the int32 GEMM writes into the exchange buffer itself
+                _ops.xnor_popcount_matmul_out(a_blk, b_local, K, leave, send_q[m0:m1])
+                rc = L.OK
+            elif fused_ok:
                 rc = lib.brute_b200_xnor_gemm_i16(a_blk.data_ptr(), b_local.data_ptr(), send_q[m0:m1].data_ptr(), m1 - m0, n_loc,
                                                   int(a_blk.shape[1]), int(K), n_loc, leave, cur.cuda_stream)
             if rc == L.UNSUPPORTED:
@@ -267,7 +272,7 @@ def _gather_peer_blocks(a_packed, b_local, K: int, world: int, rank: int, group,
             ready = torch.cuda.Event()
             ready.record(cur)
             comm.wait_event(ready)                   # the own block is read without a flag
-            L.check(lib.brute_b200_gather_peer_widen(ws["send"][q], ws["flags"], out.data_ptr(), M, n_loc, m0, m1,
+            L.check(lib.brute_b200_gather_peer_widen(ws["send"][q], ws["flags"], out.data_ptr(), M, n_loc, eb, m0, m1,
                                                      world, rank, i, e, int(ctas_per_peer), _PEER_LIMIT_US,
                                                      comm.cuda_stream), "gather_peer_widen")
         L.check(lib.brute_b200_peer_set_flag(ws["own_flags"] + 4 * _PEER_DONE, e, comm.cuda_stream), "peer_set_flag")

@@ -312,8 +312,9 @@ int brute_b200_unstack_rank_blocks(const void* in, int elem_bytes, int32_t* out,
  *    the work that produced the data the flag announces (flag: this rank's own word).
  *  - gather_peer_widen: for every rank p, waits until flag_ptrs[p][flag_index] has reached `want`
  *    (the own rank's block is not waited for), then out[m, p * n_loc + j] = send_ptrs[p][m, j] for
- *    m in [m0, m1): out is this rank's row-major int32 [M, world * n_loc]. ctas_per_peer CTAs read
- *    each peer (<= 0: 8).
+ *    m in [m0, m1): out is this rank's row-major int32 [M, world * n_loc]. elem_bytes 2: the blocks
+ *    are int16 and are widened; 4: int32 blocks (K > 32767), copied. ctas_per_peer CTAs read each
+ *    peer (<= 0: 8).
  *  - peer_wait_flags: waits until word `index` of every OTHER rank has reached `want` (before a
  *    send buffer is written again).
  * Flag values are call numbers that only grow, compared as signed differences. Every wait gives up
@@ -323,7 +324,7 @@ int brute_b200_peer_set_flag(uint32_t* flag, uint32_t value, void* stream);
 int brute_b200_peer_wait_flags(const void* const* send_ptrs, const void* const* flag_ptrs, int world, int self,
                                int index, uint32_t want, int64_t limit_us, void* stream);
 int brute_b200_gather_peer_widen(const void* const* send_ptrs, const void* const* flag_ptrs, int32_t* out,
-                                 int64_t M, int64_t n_loc, int64_t m0, int64_t m1, int world, int self,
+                                 int64_t M, int64_t n_loc, int elem_bytes, int64_t m0, int64_t m1, int world, int self,
                                  int flag_index, uint32_t want, int ctas_per_peer, int64_t limit_us, void* stream);
 int brute_b200_peer_wait_status(void);
 

@@ -856,15 +856,19 @@ def _peer_tables(bufs, flags):
     return arr(*[b.data_ptr() for b in bufs]), arr(*[f.data_ptr() for f in flags])
 
 
+@pytest.mark.parametrize("eb", [2, 4])
 @pytest.mark.parametrize("world,M,n_loc,m0,m1", [(1, 40, 64, 0, 40), (2, 300, 2048, 0, 300), (4, 129, 136, 7, 120), (8, 2100, 512, 100, 2100)])
-def test_gather_peer_widen_on_one_device(world, M, n_loc, m0, m1):
+def test_gather_peer_widen_on_one_device(world, M, n_loc, m0, m1, eb):
     """The peer-memory exchange kernels with every "rank" played by a buffer of this one device: blocks of
-    int16 [M, n_loc] per rank, flags raised through the library, then rank `self`'s replicated int32
-    result must hold every rank's rows [m0, m1) in its column block and nothing else."""
+    int16 (or, for K > 32767, int32) [M, n_loc] per rank, flags raised through the library, then rank
+    `self`'s replicated int32 result must hold every rank's rows [m0, m1) in its column block and nothing else."""
     from brute_b200 import _lib as L
     lib = L.load()
     g = gen(world * M + n_loc)
-    blocks = [torch.randint(-32767, 32768, (M, n_loc), generator=g, dtype=torch.int16) for _ in range(world)]
+    if eb == 2:
+        blocks = [torch.randint(-32767, 32768, (M, n_loc), generator=g, dtype=torch.int16) for _ in range(world)]
+    else:
+        blocks = [torch.randint(-(1 << 30), 1 << 30, (M, n_loc), generator=g, dtype=torch.int32) for _ in range(world)]
     bufs = [b.to(DEV) for b in blocks]
     flags = [torch.zeros(64, dtype=torch.int32, device=DEV) for _ in range(world)]
     send, flg = _peer_tables(bufs, flags)
@@ -877,7 +881,7 @@ def test_gather_peer_widen_on_one_device(world, M, n_loc, m0, m1):
     for self_rank in {0, world - 1}:
         for ctas in (1, 5):
             out = torch.full((M, world * n_loc), 777, dtype=torch.int32, device=DEV)
-            L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, m0, m1, world, self_rank,
+            L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, eb, m0, m1, world, self_rank,
                                                      3, 9, ctas, 2_000_000, stream), "gather_peer_widen")
             assert lib.brute_b200_peer_wait_status() == 0
             got = out.cpu()
@@ -899,14 +903,14 @@ def test_peer_wait_gives_up_and_reports_the_rank():
     send, flg = _peer_tables(bufs, flags)
     stream = torch.cuda.current_stream().cuda_stream
     out = torch.zeros((M, world * n_loc), dtype=torch.int32, device=DEV)
-    L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, 0, M, world, 0, 5, 1, 2, 3000, stream), "gather")
+    L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, 2, 0, M, world, 0, 5, 1, 2, 3000, stream), "gather")
     assert lib.brute_b200_peer_wait_status() == 1 + 1           # rank 1's flag did not arrive
     assert bool((out[:, :n_loc] == 1).all()) and bool((out[:, n_loc:] == 0).all())   # the own block needs no flag
     L.check(lib.brute_b200_peer_wait_flags(send, flg, world, 0, 5, 1, 3000, stream), "wait_flags")
     assert lib.brute_b200_peer_wait_status() == 1 + 1
     assert lib.brute_b200_peer_wait_status() == 0               # reading cleared it
     L.check(lib.brute_b200_peer_set_flag(flags[1].data_ptr() + 4 * 5, 1, stream), "set_flag")
-    L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, 0, M, world, 0, 5, 1, 2, 3000, stream), "gather")
+    L.check(lib.brute_b200_gather_peer_widen(send, flg, out.data_ptr(), M, n_loc, 2, 0, M, world, 0, 5, 1, 2, 3000, stream), "gather")
     assert lib.brute_b200_peer_wait_status() == 0
     assert bool((out[:, n_loc:] == 2).all())
 
